@@ -1,0 +1,68 @@
+// Shared helpers of the hand-written sm_100a kernels.
+//
+// Every exported entry point is `extern "C"`, takes raw device pointers, sizes and a
+// cudaStream_t, launches on that stream and returns a cudaError_t-compatible int
+// (0 = launched).  Sizes a kernel cannot take are refused on the host side with
+// OE_ERR_UNSUPPORTED before anything is launched; nothing falls back to another path.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#define OE_ERR_UNSUPPORTED 100001   // size or option outside what the kernel takes
+#define OE_PAGE 64                  // tokens per cache page
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block in a fixed order (warp shuffles, then warp 0 over the warp totals);
+// every thread gets the result.  `red` holds 32 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = (lane < nwarps) ? red[lane] : 0.f;
+    t = warp_sum(t);
+    return t;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = (lane < nwarps) ? red[lane] : -INFINITY;
+    t = warp_max(t);
+    return t;
+}
+
+// Address of token `pos` of one (cache entry, K-or-V, kv head) in the paged cache.
+// Storage of one cache entry: [n_pages][2][kv_heads][OE_PAGE][head_dim].
+// Returns the element offset from the entry's base, or -1 if the page is not mapped.
+__device__ __forceinline__ long long page_row_offset(const int* __restrict__ table_row, int pos,
+                                                     int which, int kvh, int kv_heads, int head_dim) {
+    const int page = table_row[pos / OE_PAGE];
+    if (page < 0) return -1;
+    return ((((long long)page * 2 + which) * kv_heads + kvh) * OE_PAGE + (pos % OE_PAGE)) * head_dim;
+}

@@ -1,0 +1,194 @@
+// Row-wise kernels around the matrix products: embedding gather, RMSNorm, rotary
+// position encoding fused with the cache write, SwiGLU, row gather.
+//
+// The residual stream is float32 in both precisions; T is the activation / weight /
+// cache type (float for the 32-bit path, bf16 for serving).  All arithmetic is float32.
+// Every row is computed by itself in a fixed order, so a row's result does not depend on
+// which other rows are in the batch.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------
+// x[t, :] = table[ids[t], :]            (reference: core/model.cpp:352-358)
+// An id outside [0, vocab) writes zeros and raises *err (the reference clamps to 0 with a
+// warning; here it is an error the host reports).
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_gather_kernel(float* __restrict__ x, const T* __restrict__ table,
+                                    const int* __restrict__ ids, int D, int vocab, int* err) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    float* xr = x + (size_t)t * D;
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0 && err) atomicExch(err, 1);
+        for (int d = threadIdx.x; d < D; d += blockDim.x) xr[d] = 0.f;
+        return;
+    }
+    const T* row = table + (size_t)id * D;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) xr[d] = to_f32(row[d]);
+}
+
+// ---------------------------------------------------------------------------------------
+// y = (x * 1/sqrt(mean(x^2) + eps)) * w      (reference: core/ops.cpp:149-195)
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void rmsnorm_kernel(T* __restrict__ y, const float* __restrict__ x,
+                               const float* __restrict__ w, int D, float eps) {
+    __shared__ float red[32];
+    const float* xr = x + (size_t)blockIdx.x * D;
+    T* yr = y + (size_t)blockIdx.x * D;
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) { const float v = xr[d]; ss = fmaf(v, v, ss); }
+    ss = block_sum(ss, red);
+    const float s = 1.f / sqrtf(ss / (float)D + eps);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) yr[d] = from_f32<T>((xr[d] * s) * w[d]);
+}
+
+// ---------------------------------------------------------------------------------------
+// Rotary encoding of q and k (rotate-half pairs (i, i+hd/2)) at each token's absolute
+// position, from a float32 cos/sin table [max_pos, hd/2]; q is rotated in place, rotated
+// k and v go to the token's row of the paged cache.
+// (reference: core/ops.cpp:440-485 and the cache write core/model.cpp:405-408, 596-602)
+// qkv row: [H*hd | KVH*hd | KVH*hd] when has_kv, else [H*hd] only.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride,
+                                     const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
+                                     T* __restrict__ cache, const int* __restrict__ tables, int max_pages,
+                                     const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                                     int H, int KVH, int hd, int has_kv, int rotate) {
+    const int t = blockIdx.x;
+    const int b = tok_seq[t];
+    if (b < 0) return;
+    const int pos = tok_pos[t];
+    const int half = hd / 2;
+    T* row = qkv + (size_t)t * row_stride;
+    const float* cs = cos_tab + (size_t)pos * half;
+    const float* sn = sin_tab + (size_t)pos * half;
+    for (int idx = threadIdx.x; idx < H * half; idx += blockDim.x) {
+        const int h = idx / half, i = idx % half;
+        T* p = row + h * hd;
+        const float x0 = to_f32(p[i]), x1 = to_f32(p[i + half]);
+        if (rotate) {
+            const float c = cs[i], s = sn[i];
+            p[i] = from_f32<T>(x0 * c - x1 * s);
+            p[i + half] = from_f32<T>(x0 * s + x1 * c);
+        }
+    }
+    if (!has_kv) return;
+    const int* trow = tables + (size_t)b * max_pages;
+    const T* krow = row + H * hd;
+    const T* vrow = krow + KVH * hd;
+    for (int idx = threadIdx.x; idx < KVH * half; idx += blockDim.x) {
+        const int h = idx / half, i = idx % half;
+        const long long ko = page_row_offset(trow, pos, 0, h, KVH, hd);
+        const long long vo = page_row_offset(trow, pos, 1, h, KVH, hd);
+        if (ko < 0) continue;
+        const float x0 = to_f32(krow[h * hd + i]), x1 = to_f32(krow[h * hd + i + half]);
+        if (rotate) {
+            const float c = cs[i], s = sn[i];
+            cache[ko + i] = from_f32<T>(x0 * c - x1 * s);
+            cache[ko + i + half] = from_f32<T>(x0 * s + x1 * c);
+        } else {
+            cache[ko + i] = from_f32<T>(x0);
+            cache[ko + i + half] = from_f32<T>(x1);
+        }
+        cache[vo + i] = vrow[h * hd + i];
+        cache[vo + i + half] = vrow[h * hd + i + half];
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// a = g / (1 + exp(-g)) * u, with gu = [g | u] per row   (reference: core/model.cpp:638-641)
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int FF, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / FF, c = i % FF;
+        const float g = to_f32(gu[r * 2 * FF + c]);
+        const float u = to_f32(gu[r * 2 * FF + FF + c]);
+        out[i] = from_f32<T>((g / (1.f + expf(-g))) * u);
+    }
+}
+
+__global__ void gather_rows_f32_kernel(float* __restrict__ out, const float* __restrict__ x,
+                                       const int* __restrict__ rows, int D) {
+    const int r = rows[blockIdx.x];
+    for (int d = threadIdx.x; d < D; d += blockDim.x)
+        out[(size_t)blockIdx.x * D + d] = x[(size_t)r * D + d];
+}
+
+// ---------------------------------------------------------------------------------------
+// exported entry points
+// ---------------------------------------------------------------------------------------
+#define LAUNCH_CHECK() return (int)cudaGetLastError()
+
+extern "C" {
+
+int oe_embed_gather_f32(float* x, const float* table, const int* ids, int n_tokens, int D, int vocab,
+                        int* err, cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    embed_gather_kernel<float><<<n_tokens, 256, 0, st>>>(x, table, ids, D, vocab, err);
+    LAUNCH_CHECK();
+}
+int oe_embed_gather_bf16(float* x, const bf16* table, const int* ids, int n_tokens, int D, int vocab,
+                         int* err, cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    embed_gather_kernel<bf16><<<n_tokens, 256, 0, st>>>(x, table, ids, D, vocab, err);
+    LAUNCH_CHECK();
+}
+
+int oe_rmsnorm_f32(float* y, const float* x, const float* w, int rows, int D, float eps, cudaStream_t st) {
+    if (rows <= 0) return 0;
+    rmsnorm_kernel<float><<<rows, 256, 0, st>>>(y, x, w, D, eps);
+    LAUNCH_CHECK();
+}
+int oe_rmsnorm_bf16(bf16* y, const float* x, const float* w, int rows, int D, float eps, cudaStream_t st) {
+    if (rows <= 0) return 0;
+    rmsnorm_kernel<bf16><<<rows, 256, 0, st>>>(y, x, w, D, eps);
+    LAUNCH_CHECK();
+}
+
+int oe_rope_kv_write_f32(float* qkv, int row_stride, const float* cos_tab, const float* sin_tab,
+                         float* cache, const int* tables, int max_pages, const int* tok_seq,
+                         const int* tok_pos, int n_tokens, int H, int KVH, int hd, int has_kv, int rotate,
+                         cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    if (hd % 2) return OE_ERR_UNSUPPORTED;
+    rope_kv_write_kernel<float><<<n_tokens, 256, 0, st>>>(qkv, row_stride, cos_tab, sin_tab, cache, tables,
+                                                           max_pages, tok_seq, tok_pos, H, KVH, hd, has_kv, rotate);
+    LAUNCH_CHECK();
+}
+int oe_rope_kv_write_bf16(bf16* qkv, int row_stride, const float* cos_tab, const float* sin_tab,
+                          bf16* cache, const int* tables, int max_pages, const int* tok_seq,
+                          const int* tok_pos, int n_tokens, int H, int KVH, int hd, int has_kv, int rotate,
+                          cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    if (hd % 2) return OE_ERR_UNSUPPORTED;
+    rope_kv_write_kernel<bf16><<<n_tokens, 256, 0, st>>>(qkv, row_stride, cos_tab, sin_tab, cache, tables,
+                                                          max_pages, tok_seq, tok_pos, H, KVH, hd, has_kv, rotate);
+    LAUNCH_CHECK();
+}
+
+int oe_swiglu_f32(float* out, const float* gu, int rows, int FF, cudaStream_t st) {
+    const size_t total = (size_t)rows * FF;
+    if (total == 0) return 0;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    swiglu_kernel<float><<<blocks, 256, 0, st>>>(out, gu, FF, total);
+    LAUNCH_CHECK();
+}
+int oe_swiglu_bf16(bf16* out, const bf16* gu, int rows, int FF, cudaStream_t st) {
+    const size_t total = (size_t)rows * FF;
+    if (total == 0) return 0;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    swiglu_kernel<bf16><<<blocks, 256, 0, st>>>(out, gu, FF, total);
+    LAUNCH_CHECK();
+}
+
+int oe_gather_rows_f32(float* out, const float* x, const int* rows, int n_rows, int D, cudaStream_t st) {
+    if (n_rows <= 0) return 0;
+    gather_rows_f32_kernel<<<n_rows, 256, 0, st>>>(out, x, rows, D);
+    LAUNCH_CHECK();
+}
+
+}  // extern "C"

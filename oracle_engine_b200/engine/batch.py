@@ -1,0 +1,164 @@
+"""A step's batch: the host-side plan and the device-side context the parts read.
+
+A step brings, for each of its sequences, the next tokens (a whole prompt, a piece of
+one, or one decoded token) and the places among them whose logits are wanted.  The plan
+packs all tokens into one list (no padding between sequences) with, per token, the index
+of its sequence in the batch and its absolute position, and per sequence its slot, the
+length its cache had before the step, and its token count.  Rows can be padded up to a
+fixed size for a captured CUDA graph: padding tokens carry sequence index -1, which every
+kernel skips, so padding changes no result.
+
+All integers go to the device in ONE copy from pinned host memory (`StepBuffers`).
+The reference has no batch: `forward(token, pos)` and `forward_prefill(tokens, n,
+start_pos)` take one sequence (core/model.hpp:74-89).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+
+@dataclass
+class SequenceStep:
+    """One sequence's share of a step."""
+    slot: int
+    tokens: list
+    want: list = field(default_factory=list)      # indices into `tokens`
+
+
+@dataclass
+class StepPlan:
+    n_seqs: int
+    n_tokens: int                   # with padding
+    n_real_tokens: int
+    token_ids: np.ndarray           # [T] int32
+    tok_seq: np.ndarray             # [T] int32, -1 for padding
+    tok_pos: np.ndarray             # [T] int32
+    seq_slot: np.ndarray            # [B] int32, -1 for padding
+    seq_start: np.ndarray           # [B] int32 cache length before the step
+    seq_qlen: np.ndarray            # [B] int32
+    cu_q: np.ndarray                # [B+1] int32
+    want_rows: np.ndarray           # [n_want] int32 rows of the packed token list
+    max_qlen: int
+    max_kvlen: int
+    all_decode: bool                # every sequence brings exactly one token
+
+
+def build_plan(seqs: list, starts: list, pad_seqs: int = 0, pad_tokens: int = 0,
+               want_all_rows: bool = False) -> StepPlan:
+    """seqs: SequenceStep list; starts: each sequence's cache length before the step."""
+    B = len(seqs)
+    qlens = [len(s.tokens) for s in seqs]
+    T_real = sum(qlens)
+    Bp = max(B, pad_seqs)
+    Tp = max(T_real, pad_tokens)
+    token_ids = np.zeros(Tp, dtype=np.int32)
+    tok_seq = np.full(Tp, -1, dtype=np.int32)
+    tok_pos = np.zeros(Tp, dtype=np.int32)
+    seq_slot = np.full(Bp, -1, dtype=np.int32)
+    seq_start = np.zeros(Bp, dtype=np.int32)
+    seq_qlen = np.zeros(Bp, dtype=np.int32)
+    cu_q = np.zeros(Bp + 1, dtype=np.int32)
+    want = []
+    row = 0
+    for b, (s, st, n) in enumerate(zip(seqs, starts, qlens)):
+        token_ids[row:row + n] = s.tokens
+        tok_seq[row:row + n] = b
+        tok_pos[row:row + n] = np.arange(st, st + n, dtype=np.int32)
+        seq_slot[b], seq_start[b], seq_qlen[b] = s.slot, st, n
+        cu_q[b + 1] = row + n
+        for w in s.want:
+            if not 0 <= w < n:
+                raise ValueError(f"sequence {b}: wanted place {w} is outside its {n} tokens")
+            want.append(row + w)
+        row += n
+    cu_q[B + 1:] = row
+    if want_all_rows:
+        want = list(range(Tp))
+    return StepPlan(
+        n_seqs=Bp, n_tokens=Tp, n_real_tokens=T_real, token_ids=token_ids, tok_seq=tok_seq, tok_pos=tok_pos,
+        seq_slot=seq_slot, seq_start=seq_start, seq_qlen=seq_qlen, cu_q=cu_q,
+        want_rows=np.asarray(want, dtype=np.int32), max_qlen=max(qlens, default=0),
+        max_kvlen=max((st + n for st, n in zip(starts, qlens)), default=0),
+        all_decode=all(n == 1 for n in qlens) and B > 0)
+
+
+@dataclass
+class StepContext:
+    """Device-side view of a step, handed to every part."""
+    n_tokens: int
+    n_seqs: int
+    n_want: int
+    token_ids: torch.Tensor
+    tok_seq: torch.Tensor
+    tok_pos: torch.Tensor
+    seq_slot: torch.Tensor
+    seq_start: torch.Tensor
+    seq_qlen: torch.Tensor
+    cu_q: torch.Tensor
+    want_rows: torch.Tensor
+    tables: list                    # per cache group: [B, max_pages] int32
+    max_qlen: int
+    max_kvlen: int
+    all_decode: bool
+
+
+class StepBuffers:
+    """Pinned host staging and its device mirror for a step of fixed (padded) sizes."""
+
+    def __init__(self, n_tokens: int, n_seqs: int, n_want: int, table_shapes: list, device):
+        self.n_tokens, self.n_seqs, self.n_want = n_tokens, n_seqs, n_want
+        self.table_shapes = list(table_shapes)
+        sizes = [n_tokens, n_tokens, n_tokens, n_seqs, n_seqs, n_seqs, n_seqs + 1, n_want] + \
+                [a * b for a, b in table_shapes]
+        # 16-byte aligned sections so that vector loads of any section are legal
+        self.offsets = []
+        off = 0
+        for s in sizes:
+            self.offsets.append(off)
+            off += (s + 3) // 4 * 4
+        self.total = max(off, 4)
+        self.host = torch.empty(self.total, dtype=torch.int32, pin_memory=torch.cuda.is_available())
+        self.dev = torch.empty(self.total, dtype=torch.int32, device=device)
+        self.sizes = sizes
+        self._copied = torch.cuda.Event() if torch.cuda.is_available() else None
+        self._pending = False
+
+    def _host_view(self, i):
+        return self.host[self.offsets[i]: self.offsets[i] + self.sizes[i]].numpy()
+
+    def _dev_view(self, i):
+        return self.dev[self.offsets[i]: self.offsets[i] + self.sizes[i]]
+
+    def upload(self, plan: StepPlan, tables: list) -> StepContext:
+        """Fills the staging buffer from the plan and copies it to the device (one
+        asynchronous copy on the current stream)."""
+        if self._pending:                     # the previous copy must have read the staging buffer
+            self._copied.synchronize()
+        fields = [plan.token_ids, plan.tok_seq, plan.tok_pos, plan.seq_slot, plan.seq_start, plan.seq_qlen,
+                  plan.cu_q, plan.want_rows]
+        for i, arr in enumerate(fields):
+            if arr.size != self.sizes[i]:
+                raise ValueError(f"step buffer section {i} holds {self.sizes[i]} values, the plan has {arr.size}")
+            if arr.size:
+                self._host_view(i)[:] = arr
+        for j, tb in enumerate(tables):
+            self._host_view(8 + j)[:] = tb.reshape(-1)
+        self.dev.copy_(self.host, non_blocking=True)
+        if self._copied is not None:
+            self._copied.record()
+            self._pending = True
+        return self.context(plan)
+
+    def bytes(self) -> int:
+        return self.total * 4
+
+    def context(self, plan: StepPlan) -> StepContext:
+        v = [self._dev_view(i) for i in range(8)]
+        tabs = [self._dev_view(8 + j).view(*self.table_shapes[j]) for j in range(len(self.table_shapes))]
+        return StepContext(
+            n_tokens=self.n_tokens, n_seqs=self.n_seqs, n_want=self.n_want, token_ids=v[0], tok_seq=v[1],
+            tok_pos=v[2], seq_slot=v[3], seq_start=v[4], seq_qlen=v[5], cu_q=v[6], want_rows=v[7], tables=tabs,
+            max_qlen=plan.max_qlen, max_kvlen=plan.max_kvlen, all_decode=plan.all_decode)

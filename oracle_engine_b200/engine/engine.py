@@ -1,0 +1,141 @@
+"""Engine: a loaded model with its cache, step function, sampler and generation loop.
+
+The Python entry point of the library, in the manner of the reference's `Engine`
+(core/engine.hpp:35-76: load, then generate with `GenParams`), working on token ids:
+
+    engine = Engine.from_pretrained("model_dir", dtype="bfloat16", max_tokens=65536)
+    outs = engine.generate([[1, 2, 3], [4, 5]], GenParams(n_predict=16, temperature=0.0))
+
+One engine drives one CUDA stream and is not re-entrant (the reference serialises
+`generate` with a mutex, core/engine.cpp:86).
+"""
+from __future__ import annotations
+
+from pathlib import Path
+
+import torch
+
+from .. import models  # noqa: F401  (registers the architectures)
+from ..cache.kv_cache import KVCache
+from ..cache.state import StateStore
+from ..config.base import get_architecture, load_config
+from ..csrc import ops
+from ..parts.model import DecoderModel
+from ..sampling.params import GenParams
+from ..sampling.sampler import Sampler
+from ..weights.loader import load_weights
+from ..weights.random_init import RandomSource
+from ..weights.safetensors_io import ModelFiles
+from .batch import SequenceStep
+from .generate import GenerationResult, run_generation
+from .runtime import Runtime, parse_dtype
+from .step import Stepper
+
+
+class Engine:
+    def __init__(self, config, arch, source, dtype="bfloat16", max_tokens: int = 8192,
+                 max_seq_len: int | None = None, device="cuda:0", use_graphs: bool = True,
+                 tensor_cores: bool = True, n_slots: int | None = None):
+        ops.require_cuda()
+        self.config = config
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        self.rt = Runtime(parse_dtype(dtype), self.device, tensor_cores)
+        page = ops.PAGE
+        max_tokens = max(page, (int(max_tokens) + page - 1) // page * page)
+        limit = getattr(config, "max_position_embeddings", max_tokens)
+        self.max_seq_len = min(int(max_seq_len or limit), limit, max_tokens)
+        self.spec = arch.build_spec(config, self.max_seq_len)
+        self.model = DecoderModel(self.spec, self.rt)
+        load_weights(self.model, source(self.model) if callable(source) else source)
+        self.cache = KVCache(self.model.cache_needs(), max_tokens, self.max_seq_len, self.rt.dtype, self.device,
+                             n_slots=n_slots)
+        self.state = StateStore(self.cache.n_slots, self.device)
+        for e, needs in enumerate(self.model.state_needs()):
+            for name, need in needs.items():
+                self.state.add(e, name, need)
+        self.sampler = Sampler(self.state, self.device)
+        self.stepper = Stepper(self.model, self.cache, self.state, self.rt, use_graphs)
+        self._row_slot = torch.empty(self.cache.n_slots, dtype=torch.int32, device=self.device)
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def from_pretrained(cls, folder, **kw) -> "Engine":
+        """A model folder (config.json + model.safetensors or shards)."""
+        config, arch = load_config(folder)
+        files = ModelFiles(folder)
+        try:
+            return cls(config, arch, files, **kw)
+        finally:
+            files.close()
+
+    @classmethod
+    def from_config(cls, config, seed: int = 0, std: float = 0.02, norm_std: float = 0.1, **kw) -> "Engine":
+        """Seeded random weights generated on the device (the same values that
+        `write_model_folder` writes for this configuration and seed)."""
+        arch = get_architecture(config.architecture)
+        device = kw.get("device", "cuda:0")
+        return cls(config, arch, lambda model: RandomSource(model.tensors(), seed, torch.bfloat16, device, std,
+                                                            norm_std), **kw)
+
+    # ------------------------------------------------------------------ slots and steps
+    def alloc(self) -> int:
+        slot = self.cache.alloc_slot()
+        self.state.reset(slot)
+        return slot
+
+    def free(self, slot: int) -> None:
+        self.cache.free_slot(slot)
+
+    def step(self, seqs: list[SequenceStep]):
+        """Float32 logits [wanted, vocab] on the device, or None; see Stepper.step."""
+        return self.stepper.step(seqs)
+
+    def check_device_errors(self) -> None:
+        err = self.model.embedding.err
+        if err is not None and int(err.item()) != 0:
+            err.zero_()
+            raise RuntimeError("a token id outside the vocabulary reached the embedding kernel")
+
+    # ------------------------------------------------------------------ generation
+    def generate(self, prompts, params: GenParams | None = None, batch_size: int | None = None,
+                 on_token=None, return_results: bool = False):
+        """prompts: lists of token ids.  Returns the new tokens of each request (or
+        GenerationResult objects with the finish reason)."""
+        params = params or GenParams()
+        results = run_generation(_Backend(self), prompts, params, batch_size, self.spec.stop_ids, on_token)
+        return results if return_results else [r.tokens for r in results]
+
+
+class _Backend:
+    """The engine as the generation loop sees it."""
+
+    def __init__(self, engine: Engine):
+        self.e = engine
+        self.max_seq_len = engine.max_seq_len
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    def alloc(self, request_index, prompt, params):
+        slot = self.e.alloc()
+        self.e.sampler.start_sequence(slot, params.seed + request_index, prompt, params)
+        return slot
+
+    def free(self, slot):
+        self.e.free(slot)
+
+    def step(self, seqs):
+        logits = self.e.step(seqs)
+        self.h2d_bytes += self.e.stepper.last_h2d_bytes
+        return logits
+
+    def sample(self, logits, slots, params):
+        e = self.e
+        rows = len(slots)
+        row_slot = e._row_slot[:rows]
+        host = torch.tensor(slots, dtype=torch.int32)
+        row_slot.copy_(host)
+        self.h2d_bytes += rows * 4
+        out = e.sampler.sample(logits[:rows], row_slot, params)
+        self.d2h_bytes += rows * 4
+        return out.tolist()

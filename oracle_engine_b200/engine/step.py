@@ -1,0 +1,161 @@
+"""The step function: runs a batch's next tokens through the model from the cache.
+
+`Stepper.step(seqs)` takes, per sequence, its slot, its next tokens and the places whose
+logits are wanted.  It runs exactly those tokens as one packed batch: a sequence's new
+keys and values are written at positions start..start+n-1 of its slot, every token
+attends to its own sequence's cache up to its own position, and the final norm and the
+head run only on the wanted rows.  Prompts of unequal length and single decoded tokens
+go through the same code; the sequences of a step need not be aligned in any way.
+
+Steps in which every sequence brings one token are replayed from a CUDA graph, captured
+per padded batch size, when every part of the model allows it.
+
+Reference: `Model::forward` (one token, core/model.cpp:340-495) and
+`Model::forward_prefill` (n tokens of one sequence from start_pos, reading keys and
+values from the cache, core/model.cpp:510-674).
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..cache.kv_cache import CacheView
+from .batch import SequenceStep, StepBuffers, build_plan
+
+_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+
+
+class StepError(ValueError):
+    """A step that cannot run; raised before anything is launched."""
+
+
+def _bucket(n: int) -> int:
+    for b in _BUCKETS:
+        if n <= b:
+            return b
+    return (n + 63) // 64 * 64
+
+
+class _DecodeGraph:
+    def __init__(self, bucket: int, buffers: StepBuffers):
+        self.bucket = bucket
+        self.buffers = buffers
+        self.graph = None
+        self.logits = None
+        self.runs = 0
+
+
+class Stepper:
+    def __init__(self, model, cache, state, runtime, use_graphs: bool = True):
+        self.model = model
+        self.cache = cache
+        self.state = state
+        self.rt = runtime
+        self.vocab = model.spec.vocab_size
+        self.n_entries = len(model.schedule)
+        self._views_storage = [cache.storage_of(e) if e in cache.entry_group else None
+                               for e in range(self.n_entries)]
+        self._entry_group = [cache.group_of(e) if e in cache.entry_group else -1 for e in range(self.n_entries)]
+        self._state_views = [state.views(e) for e in range(self.n_entries)]
+        parts_ok = all(getattr(p, "graph_safe", False) for layer in model.layers for p in layer.parts())
+        self.use_graphs = bool(use_graphs and parts_ok)
+        self._graphs: dict[int, _DecodeGraph] = {}
+        self._eager_buffers: dict[tuple, StepBuffers] = {}
+        self.launch_counter = None         # set by the bench to count kernel launches
+
+    # ------------------------------------------------------------------ helpers
+    def _table_shapes(self, n_seqs: int):
+        return [(n_seqs, self.cache.max_pages_per_seq) for _ in self.cache.groups]
+
+    def _cache_views(self, ctx):
+        return [CacheView(self._views_storage[e], ctx.tables[g], g) if g >= 0 else CacheView(None, None, -1)
+                for e, g in enumerate(self._entry_group)]
+
+    def _validate(self, seqs):
+        if not seqs:
+            raise StepError("a step needs at least one sequence")
+        seen = set()
+        for i, s in enumerate(seqs):
+            if not self.cache.slots.is_held(s.slot):
+                raise StepError(f"sequence {i}: slot {s.slot} is not allocated")
+            if s.slot in seen:
+                raise StepError(f"sequence {i}: slot {s.slot} appears twice in one step")
+            seen.add(s.slot)
+            if len(s.tokens) < 1:
+                raise StepError(f"sequence {i}: a step needs at least one token per sequence")
+            bad = [t for t in s.tokens if not 0 <= int(t) < self.vocab]
+            if bad:
+                raise StepError(f"sequence {i}: token id {bad[0]} is outside the vocabulary [0, {self.vocab})")
+            if self.cache.length(s.slot) + len(s.tokens) > self.model.spec.max_positions:
+                raise StepError(f"sequence {i}: {self.cache.length(s.slot)} + {len(s.tokens)} tokens exceed the "
+                                f"{self.model.spec.max_positions} positions the model was built for")
+
+    # ------------------------------------------------------------------ the step
+    def step(self, seqs: list[SequenceStep]) -> torch.Tensor | None:
+        """Returns float32 logits [wanted, vocab] on the device (order: sequences, then
+        each sequence's `want`), or None if nothing is wanted.  The tensor may be reused
+        by the next step."""
+        self._validate(seqs)
+        starts = [self.cache.length(s.slot) for s in seqs]
+        for s, st in zip(seqs, starts):
+            self.cache.reserve(s.slot, st + len(s.tokens))
+        decode = all(len(s.tokens) == 1 for s in seqs)
+        if decode and self.use_graphs:
+            logits = self._step_graph(seqs, starts)
+        else:
+            logits = self._step_eager(seqs, starts)
+        for s, st in zip(seqs, starts):
+            self.cache.commit(s.slot, st + len(s.tokens))
+        return logits
+
+    def _step_eager(self, seqs, starts):
+        plan = build_plan(seqs, starts)
+        key = (plan.n_tokens, plan.n_seqs, plan.want_rows.size)
+        buf = self._eager_buffers.get(key)
+        if buf is None:
+            if len(self._eager_buffers) > 64:
+                self._eager_buffers.clear()
+            buf = StepBuffers(plan.n_tokens, plan.n_seqs, plan.want_rows.size, self._table_shapes(plan.n_seqs),
+                              self.rt.device)
+            self._eager_buffers[key] = buf
+        tables = [self.cache.tables_for(g.index, plan.seq_slot) for g in self.cache.groups]
+        ctx = buf.upload(plan, tables)
+        self.last_h2d_bytes = buf.bytes()
+        return self.model.forward(ctx, self._cache_views(ctx), self._state_views)
+
+    def _step_graph(self, seqs, starts):
+        B = len(seqs)
+        bucket = _bucket(B)
+        g = self._graphs.get(bucket)
+        if g is None:
+            g = _DecodeGraph(bucket, StepBuffers(bucket, bucket, bucket, self._table_shapes(bucket), self.rt.device))
+            self._graphs[bucket] = g
+        plan = build_plan(seqs, starts, pad_seqs=bucket, pad_tokens=bucket, want_all_rows=True)
+        tables = [self.cache.tables_for(gr.index, plan.seq_slot) for gr in self.cache.groups]
+        ctx = g.buffers.upload(plan, tables)
+        self.last_h2d_bytes = g.buffers.bytes()
+        g.runs += 1
+        if g.graph is None and g.runs == 1:
+            # first use of this batch size: run directly (loads the kernels' modules)
+            all_logits = self.model.forward(ctx, self._cache_views(ctx), self._state_views)
+        else:
+            if g.graph is None:
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    g.logits = self.model.forward(ctx, self._cache_views(ctx), self._state_views)
+                g.graph = graph
+            g.graph.replay()
+            all_logits = g.logits
+        # rows wanted by the caller, in order
+        rows = [b for b, s in enumerate(seqs) if s.want]
+        for b, s in enumerate(seqs):
+            if s.want and list(s.want) != [0]:
+                raise StepError(f"sequence {b}: a one-token step can only want place 0")
+        if not rows:
+            return None
+        if rows == list(range(all_logits.shape[0])):
+            return all_logits
+        if rows == list(range(len(rows))):
+            return all_logits[:len(rows)]
+        return all_logits[torch.as_tensor(rows, device=all_logits.device)]

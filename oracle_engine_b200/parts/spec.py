@@ -1,0 +1,97 @@
+"""The data description of a model: which parts make each layer, and in what order the
+layers run.
+
+An architecture's `build_spec(config)` returns a `ModelSpec`.  Nothing below it knows
+which model it is in: every part gets its sizes and constants from its `PartSpec`.
+
+* `PartSpec(kind, params)` names a registered part (parts/registry.py) and its parameters.
+* `LayerSpec` puts a mixer, a feed-forward and their norms together in an arrangement
+  (`block`), under a tensor-name prefix.  Layers may differ from one another.
+* `ModelSpec.schedule` is the order in which layers run: a list of `ScheduleEntry`.  An
+  entry may name a layer that another entry also names (the weights are shared; each entry
+  still has a cache of its own), and `cache_from` lets an entry read the cache that an
+  earlier entry wrote instead of writing one (it then computes no keys or values).
+
+The reference has one fixed arrangement, x += Attn(RMSNorm(x)); x += FFN(RMSNorm(x)),
+L times (core/model.cpp:361-474); here that order is the data a Llama spec holds.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Optional
+
+
+@dataclass(frozen=True)
+class TensorDecl:
+    """A weight a part needs: full name in the file, shape, and how random weights fill it
+    ("normal": N(0, std); "ones_normal": 1 + N(0, norm_std))."""
+    name: str
+    shape: tuple[int, ...]
+    init: str = "normal"
+
+
+@dataclass(frozen=True)
+class PartSpec:
+    kind: str
+    params: dict = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class LayerSpec:
+    prefix: str                        # e.g. "model.layers.3."
+    mixer: PartSpec
+    feed_forward: Optional[PartSpec]
+    mixer_norm: PartSpec
+    ffn_norm: Optional[PartSpec]
+    block: str = "pre_norm"            # arrangement of the four (parts/block.py)
+
+
+@dataclass(frozen=True)
+class ScheduleEntry:
+    layer: int                         # index into ModelSpec.layers
+    cache_from: Optional[int] = None   # index of an earlier schedule entry whose cache is read
+
+
+@dataclass(frozen=True)
+class CacheNeed:
+    """What a mixer keeps per token: `kind` "full" (every key and value) or "window" (the
+    last `window` of them); entries with equal needs share one group of storage."""
+    kind: str
+    kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """Per-sequence state of fixed size that a part keeps: one tensor of `shape` per
+    sequence, zeroed when a sequence starts."""
+    shape: tuple[int, ...]
+    dtype: Any                         # torch dtype
+
+
+@dataclass(frozen=True)
+class ModelSpec:
+    architecture: str
+    hidden_size: int
+    vocab_size: int
+    max_positions: int
+    embedding: PartSpec
+    final_norm: PartSpec
+    head: PartSpec
+    positions: dict                    # name -> PartSpec of a position encoding
+    layers: tuple
+    schedule: tuple
+    stop_ids: tuple = ()
+    bos_id: Optional[int] = None
+    ignored_tensors: tuple = ()        # name suffixes a file may hold that the model does not read
+
+    def __post_init__(self):
+        for i, e in enumerate(self.schedule):
+            if not 0 <= e.layer < len(self.layers):
+                raise ValueError(f"schedule[{i}] names layer {e.layer}, there are {len(self.layers)}")
+            if e.cache_from is not None:
+                if not 0 <= e.cache_from < i:
+                    raise ValueError(f"schedule[{i}].cache_from must name an earlier entry, got {e.cache_from}")
+                if self.schedule[e.cache_from].cache_from is not None:
+                    raise ValueError(f"schedule[{i}].cache_from names an entry that owns no cache")

@@ -68,8 +68,12 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+LAUNCHES = [0]          # kernels launched through this module (or captured into a graph)
+
+
 def _check(code: int, what: str) -> None:
     if code == 0:
+        LAUNCHES[0] += 1
         return
     if code == ERR_UNSUPPORTED:
         raise KernelError(f"{what}: sizes outside what this kernel takes")

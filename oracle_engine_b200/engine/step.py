@@ -20,6 +20,7 @@ import numpy as np
 import torch
 
 from ..cache.kv_cache import CacheView
+from ..csrc import ops
 from .batch import SequenceStep, StepBuffers, build_plan
 
 _BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
@@ -43,6 +44,7 @@ class _DecodeGraph:
         self.graph = None
         self.logits = None
         self.runs = 0
+        self.n_kernels = 0
 
 
 class Stepper:
@@ -142,10 +144,14 @@ class Stepper:
             if g.graph is None:
                 torch.cuda.synchronize()
                 graph = torch.cuda.CUDAGraph()
+                before = ops.LAUNCHES[0]
                 with torch.cuda.graph(graph):
                     g.logits = self.model.forward(ctx, self._cache_views(ctx), self._state_views)
+                g.n_kernels = ops.LAUNCHES[0] - before
+                ops.LAUNCHES[0] = before          # captured, not launched
                 g.graph = graph
             g.graph.replay()
+            ops.LAUNCHES[0] += g.n_kernels
             all_logits = g.logits
         # rows wanted by the caller, in order
         rows = [b for b, s in enumerate(seqs) if s.want]

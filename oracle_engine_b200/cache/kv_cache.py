@@ -45,7 +45,7 @@ class CacheGroup:
 
     def allocate(self, dtype, device) -> None:
         n = self.need
-        self.storage = torch.empty((len(self.entries), self.pool.n, 2, n.kv_heads, PAGE, n.head_dim),
+        self.storage = torch.zeros((len(self.entries), self.pool.n, 2, n.kv_heads, PAGE, n.head_dim),
                                    dtype=dtype, device=device)
 
     def bytes_per_page(self, itemsize: int) -> int:

@@ -1,0 +1,362 @@
+// bf16 grouped-query attention over the paged cache on the tensor cores, for prompts
+// (causal, ragged batches) and for decoded tokens (split over the keys), compiled for one
+// head size: -DOE_HD=<head_dim>, a multiple of 16 up to 256.
+//
+// A CTA works on one (sequence, KV head) and a tile of query rows; a row is a (token,
+// query head of the group) pair, so the G = H/KVH query heads that share a KV head also
+// share every K/V tile the CTA loads.  Each warp owns 16 rows.  Key blocks are cache
+// pages (64 keys): a page's K and V panels are contiguous [64][head_dim] and are staged
+// in shared memory with cp.async, double buffered.  S = Q K^T and O += P V run on
+// mma.sync m16n8k16 (bf16 in, float32 accumulate) with ldmatrix fragments; the softmax is
+// online, in float32 (running maximum and sum per row).  Causal mask: key <= the row's
+// absolute position; window > 0 keeps only the last `window` keys.
+// For decoded tokens the page range of a sequence is split over `n_splits` CTAs; each
+// writes an unnormalised partial (o, m, l) and attn_merge_kernel combines them in split
+// order.
+// Reference: core/model.cpp:411-435 and :605-626 (scores, softmax, weighted values).
+#include "common.cuh"
+
+#ifndef OE_HD
+#define OE_HD 128
+#endif
+
+namespace {
+
+constexpr int HD = OE_HD;
+constexpr int BN = OE_PAGE;                     // keys per block = one page
+constexpr int ROW_BYTES = HD * 2 + 16;          // padded row: ldmatrix without bank conflicts
+constexpr int TILE_BYTES = BN * ROW_BYTES;
+constexpr int KS = HD / 16;                     // k-steps of Q K^T; pairs of 8-wide output tiles of P V
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head_dim must be a multiple of 16 up to 256");
+
+struct AttnArgs {
+    bf16* out;                 // [T, H*HD]
+    const bf16* q;             // rows of q_stride elements, head h at h*HD
+    long long q_stride;
+    const bf16* cache;         // one cache entry [pages][2][KVH][64][HD]
+    const int* tables;         // [B, max_pages]
+    int max_pages;
+    const int* cu_q;           // [B+1] first packed row of each sequence
+    const int* seq_start;      // [B] cache length before the step
+    const int* seq_qlen;       // [B]
+    int H, KVH, window;
+    float scale_log2;          // scale * log2(e)
+    int tokens_per_tile;
+    int n_splits;
+    float* partial;            // [T, H, n_splits, HD + 2] when n_splits > 1
+};
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(smem)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(smem)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *(uint32_t*)&h;
+}
+
+// Stages the K and V panels of `page` for KV head `kvh` into shared memory.
+template <int NTHREADS>
+__device__ __forceinline__ void load_page(uint8_t* ks, uint8_t* vs, const bf16* cache, int page, int kvh, int KVH) {
+    const bf16* kg = cache + (((size_t)page * 2 + 0) * KVH + kvh) * (size_t)(BN * HD);
+    const bf16* vg = cache + (((size_t)page * 2 + 1) * KVH + kvh) * (size_t)(BN * HD);
+    constexpr int CHUNKS = BN * HD / 8;                 // 16-byte chunks per panel
+    for (int c = threadIdx.x; c < CHUNKS; c += NTHREADS) {
+        const int row = c / (HD / 8), col = c % (HD / 8);
+        cp_async16(ks + row * ROW_BYTES + col * 16, kg + (size_t)c * 8);
+        cp_async16(vs + row * ROW_BYTES + col * 16, vg + (size_t)c * 8);
+    }
+}
+
+template <int NWARPS>
+__global__ void __launch_bounds__(NWARPS * 32)
+attn_mma_kernel(const AttnArgs a) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int b = blockIdx.z, kvh = blockIdx.y;
+    const int qlen = a.seq_qlen[b];
+    if (qlen <= 0) return;
+    const int start = a.seq_start[b];
+    const int G = a.H / a.KVH;
+    const int tpt = a.tokens_per_tile;
+    const int n_q_tiles = (qlen + tpt - 1) / tpt;
+    const int q_tile = a.n_splits > 1 ? 0 : blockIdx.x;
+    const int split = a.n_splits > 1 ? blockIdx.x : 0;
+    if (q_tile >= n_q_tiles) return;
+    const int t0 = q_tile * tpt;
+    const int nt = min(tpt, qlen - t0);
+    const int pos_lo = start + t0, pos_hi = start + t0 + nt - 1;
+    const int key_lo = a.window > 0 ? max(0, pos_lo - a.window + 1) : 0;
+    int j_lo = key_lo / BN, j_hi = pos_hi / BN;
+    if (a.n_splits > 1) {
+        const int per = (j_hi - j_lo + a.n_splits) / a.n_splits;
+        j_lo = j_lo + split * per;
+        j_hi = min(j_hi, j_lo + per - 1);
+    }
+    const int* trow = a.tables + (size_t)b * a.max_pages;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int row0 = warp * 16 + gid;                   // this thread's rows: row0 and row0 + 8
+    const long long packed0 = a.cu_q[b] + t0;
+
+    int tok[2], pos[2], head[2];
+    bool valid[2];
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        const int r = row0 + i * 8;
+        tok[i] = r / G;
+        head[i] = kvh * G + r % G;
+        valid[i] = tok[i] < nt;
+        pos[i] = start + t0 + tok[i];
+    }
+
+    // Q fragments (A operand), kept in registers for the whole kernel
+    uint32_t qf[KS][4];
+#pragma unroll
+    for (int ks = 0; ks < KS; ks++) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            if (valid[i]) {
+                const bf16* qr = a.q + (packed0 + tok[i]) * a.q_stride + (size_t)head[i] * HD + ks * 16 + tig * 2;
+                qf[ks][i] = *(const uint32_t*)qr;
+                qf[ks][i + 2] = *(const uint32_t*)(qr + 8);
+            } else {
+                qf[ks][i] = 0u;
+                qf[ks][i + 2] = 0u;
+            }
+        }
+    }
+
+    float oacc[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; n++) { oacc[n][0] = oacc[n][1] = oacc[n][2] = oacc[n][3] = 0.f; }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+    const int n_blocks = j_hi - j_lo + 1;
+    if (n_blocks > 0) {
+        load_page<NWARPS * 32>(smem, smem + TILE_BYTES, a.cache, trow[j_lo], kvh, a.KVH);
+    }
+    cp_async_commit();
+    for (int it = 0; it < n_blocks; it++) {
+        const int j = j_lo + it;
+        uint8_t* ks_cur = smem + (size_t)(it & 1) * 2 * TILE_BYTES;
+        uint8_t* vs_cur = ks_cur + TILE_BYTES;
+        if (it + 1 < n_blocks) {
+            uint8_t* nxt = smem + (size_t)((it + 1) & 1) * 2 * TILE_BYTES;
+            load_page<NWARPS * 32>(nxt, nxt + TILE_BYTES, a.cache, trow[j + 1], kvh, a.KVH);
+        }
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+
+        // S = Q K^T for this warp's 16 rows and the block's 64 keys
+        float sacc[BN / 8][4];
+#pragma unroll
+        for (int n = 0; n < BN / 8; n++) { sacc[n][0] = sacc[n][1] = sacc[n][2] = sacc[n][3] = 0.f; }
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++) {
+#pragma unroll
+            for (int np = 0; np < BN / 16; np++) {
+                uint32_t kb[4];
+                const int m = lane >> 3, r = lane & 7;
+                ldmatrix_x4(kb, ks_cur + (np * 16 + (m >> 1) * 8 + r) * ROW_BYTES + (ks * 2 + (m & 1)) * 16);
+                mma_bf16(sacc[2 * np], qf[ks], kb[0], kb[1]);
+                mma_bf16(sacc[2 * np + 1], qf[ks], kb[2], kb[3]);
+            }
+        }
+        // scale, mask, online softmax
+        float rmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < BN / 8; n++) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int i = e >> 1;
+                const int key = j * BN + n * 8 + tig * 2 + (e & 1);
+                const bool ok = valid[i] && key <= pos[i] && (a.window <= 0 || key > pos[i] - a.window);
+                const float s = ok ? sacc[n][e] * a.scale_log2 : -INFINITY;
+                sacc[n][e] = s;
+                rmax[i] = fmaxf(rmax[i], s);
+            }
+        }
+        float alpha[2], m_use[2];
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            rmax[i] = fmaxf(rmax[i], __shfl_xor_sync(0xffffffffu, rmax[i], 1));
+            rmax[i] = fmaxf(rmax[i], __shfl_xor_sync(0xffffffffu, rmax[i], 2));
+            const float m_new = fmaxf(m_run[i], rmax[i]);
+            m_use[i] = (m_new == -INFINITY) ? 0.f : m_new;
+            alpha[i] = exp2f(m_run[i] - m_use[i]);
+            m_run[i] = m_new;
+        }
+        float rsum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int n = 0; n < BN / 8; n++) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float p = exp2f(sacc[n][e] - m_use[e >> 1]);
+                sacc[n][e] = p;
+                rsum[e >> 1] += p;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 2; i++) l_run[i] = l_run[i] * alpha[i] + rsum[i];
+#pragma unroll
+        for (int n = 0; n < HD / 8; n++) {
+            oacc[n][0] *= alpha[0]; oacc[n][1] *= alpha[0];
+            oacc[n][2] *= alpha[1]; oacc[n][3] *= alpha[1];
+        }
+        // O += P V
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; kk++) {
+            uint32_t pa[4];
+            pa[0] = pack_bf16(sacc[2 * kk][0], sacc[2 * kk][1]);
+            pa[1] = pack_bf16(sacc[2 * kk][2], sacc[2 * kk][3]);
+            pa[2] = pack_bf16(sacc[2 * kk + 1][0], sacc[2 * kk + 1][1]);
+            pa[3] = pack_bf16(sacc[2 * kk + 1][2], sacc[2 * kk + 1][3]);
+#pragma unroll
+            for (int dp = 0; dp < KS; dp++) {
+                uint32_t vb[4];
+                const int m = lane >> 3, r = lane & 7;
+                ldmatrix_x4_trans(vb, vs_cur + (kk * 16 + (m & 1) * 8 + r) * ROW_BYTES + (dp * 2 + (m >> 1)) * 16);
+                mma_bf16(oacc[2 * dp], pa, vb[0], vb[1]);
+                mma_bf16(oacc[2 * dp + 1], pa, vb[2], vb[3]);
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+    }
+    if (a.n_splits <= 1) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            if (!valid[i]) continue;
+            const float inv = l_run[i] > 0.f ? 1.f / l_run[i] : 0.f;
+            bf16* o = a.out + (packed0 + tok[i]) * (long long)(a.H * HD) + (size_t)head[i] * HD + tig * 2;
+#pragma unroll
+            for (int n = 0; n < HD / 8; n++)
+                *(uint32_t*)(o + n * 8) = pack_bf16(oacc[n][2 * i] * inv, oacc[n][2 * i + 1] * inv);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            if (!valid[i]) continue;
+            float* p = a.partial + (((packed0 + tok[i]) * a.H + head[i]) * a.n_splits + split) * (long long)(HD + 2);
+#pragma unroll
+            for (int n = 0; n < HD / 8; n++) {
+                p[n * 8 + tig * 2] = oacc[n][2 * i];
+                p[n * 8 + tig * 2 + 1] = oacc[n][2 * i + 1];
+            }
+            if (tig == 0) { p[HD] = m_run[i]; p[HD + 1] = l_run[i]; }
+        }
+    }
+}
+
+// out[row, head] = sum_s o_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), splits taken in order.
+__global__ void attn_merge_kernel(bf16* __restrict__ out, const float* __restrict__ partial,
+                                  const int* __restrict__ tok_seq, int H, int n_splits) {
+    const int t = blockIdx.x, h = blockIdx.y;
+    bf16* o = out + ((size_t)t * H + h) * HD;
+    if (tok_seq[t] < 0) {
+        for (int d = threadIdx.x; d < HD; d += blockDim.x) o[d] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const float* p = partial + ((size_t)t * H + h) * n_splits * (HD + 2);
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; s++) m = fmaxf(m, p[s * (HD + 2) + HD]);
+    float l = 0.f;
+    for (int s = 0; s < n_splits; s++) {
+        const float ms = p[s * (HD + 2) + HD];
+        if (ms != -INFINITY) l += p[s * (HD + 2) + HD + 1] * exp2f(ms - m);
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < n_splits; s++) {
+            const float ms = p[s * (HD + 2) + HD];
+            if (ms != -INFINITY) acc += p[s * (HD + 2) + d] * exp2f(ms - m);
+        }
+        o[d] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+template <int NWARPS>
+int launch(const AttnArgs& a, int n_seqs, int grid_x, cudaStream_t st) {
+    const size_t smem = 4 * (size_t)TILE_BYTES;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(attn_mma_kernel<NWARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    dim3 grid(grid_x, a.KVH, n_seqs);
+    attn_mma_kernel<NWARPS><<<grid, NWARPS * 32, smem, st>>>(a);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" {
+
+int oe_attn_mma_head_dim() { return HD; }
+
+// Floats of scratch the split path needs for a step of n_tokens rows.
+long long oe_attn_mma_partial_floats(int n_tokens, int H, int n_splits) {
+    return (long long)n_tokens * H * n_splits * (HD + 2);
+}
+
+// max_qlen: the most tokens any sequence brings (sizes the grid); n_splits > 1 only when
+// every sequence's tokens fit one tile (decode).  zero_rows: tok_seq for the merge kernel.
+int oe_attn_mma_bf16(bf16* out, const bf16* q, long long q_stride, const bf16* cache, const int* tables, int max_pages,
+                     const int* cu_q, const int* seq_start, const int* seq_qlen, const int* tok_seq, int n_seqs,
+                     int n_tokens, int max_qlen, int H, int KVH, int window, float scale, int n_splits, float* partial,
+                     cudaStream_t st) {
+    if (n_seqs <= 0 || n_tokens <= 0) return 0;
+    if (H % KVH || ((uintptr_t)q & 3) || (q_stride & 1)) return OE_ERR_UNSUPPORTED;
+    const int G = H / KVH;
+    if (G > 64) return OE_ERR_UNSUPPORTED;
+    AttnArgs a;
+    a.out = out; a.q = q; a.q_stride = q_stride; a.cache = cache; a.tables = tables; a.max_pages = max_pages;
+    a.cu_q = cu_q; a.seq_start = seq_start; a.seq_qlen = seq_qlen; a.H = H; a.KVH = KVH; a.window = window;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    a.partial = partial;
+    // rows per sequence tile: 16 per warp; few rows (decode) use fewer warps
+    const long long rows_needed = (long long)max_qlen * G;
+    int nwarps = rows_needed <= 16 ? 1 : (rows_needed <= 32 ? 2 : 4);
+    while (nwarps * 16 < G) nwarps *= 2;
+    a.tokens_per_tile = (nwarps * 16) / G;
+    const int n_q_tiles = (max_qlen + a.tokens_per_tile - 1) / a.tokens_per_tile;
+    if (n_splits > 1 && (n_q_tiles > 1 || partial == nullptr)) n_splits = 1;
+    a.n_splits = n_splits < 1 ? 1 : n_splits;
+    const int grid_x = a.n_splits > 1 ? a.n_splits : n_q_tiles;
+    int rc;
+    if (nwarps == 1) rc = launch<1>(a, n_seqs, grid_x, st);
+    else if (nwarps == 2) rc = launch<2>(a, n_seqs, grid_x, st);
+    else rc = launch<4>(a, n_seqs, grid_x, st);
+    if (rc) return rc;
+    if (a.n_splits > 1) {
+        attn_merge_kernel<<<dim3(n_tokens, H), HD >= 128 ? 128 : 64, 0, st>>>(out, partial, tok_seq, H, a.n_splits);
+        rc = (int)cudaGetLastError();
+    }
+    return rc;
+}
+
+}  // extern "C"

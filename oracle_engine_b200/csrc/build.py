@@ -83,15 +83,27 @@ def _digest(source: Path, flags: list[str]) -> str:
     return h.hexdigest()[:16]
 
 
-def library_path(name: str) -> Path:
-    src, flags = LIBRARIES[name]
-    return _build_dir() / f"liboe_{name}_{_digest(CSRC / src, flags)}.so"
+def _define_flags(defines) -> tuple[str, list[str]]:
+    """(tag for the file name, nvcc flags) of a dict of -D macros."""
+    if not defines:
+        return "", []
+    items = sorted(defines.items())
+    return "_" + "_".join(f"{k.lower()}{v}" for k, v in items), [f"-D{k}={v}" for k, v in items]
 
 
-def build(name: str, verbose: bool = True) -> Path:
-    """Builds library `name` if its .so is not there yet; returns the path."""
+def library_path(name: str, defines=None) -> Path:
     src, flags = LIBRARIES[name]
-    out = library_path(name)
+    tag, dflags = _define_flags(defines)
+    return _build_dir() / f"liboe_{name}{tag}_{_digest(CSRC / src, flags + dflags)}.so"
+
+
+def build(name: str, verbose: bool = True, defines=None) -> Path:
+    """Builds library `name` (specialised by the -D macros of `defines`) if its .so is not
+    there yet; returns the path."""
+    src, flags = LIBRARIES[name]
+    tag, dflags = _define_flags(defines)
+    flags = flags + dflags
+    out = library_path(name, defines)
     if out.is_file():
         return out
     cmd = [_nvcc()] + ARCH_FLAGS + NVCC_FLAGS + flags + ["-I", str(CSRC), "-o", None, str(CSRC / src)]
@@ -116,41 +128,53 @@ def build(name: str, verbose: bool = True) -> Path:
         raise BuildError(f"nvcc failed on {src} (exit {proc.returncode}):\n{' '.join(cmd)}\n{log}")
     os.replace(tmp, out)
     # drop stale builds of the same library
-    for old in out.parent.glob(f"liboe_{name}_*.so"):
-        if old != out:
+    for old in out.parent.glob(f"liboe_{name}{tag}_*.so"):
+        if old != out and len(old.name) == len(out.name):
             old.unlink(missing_ok=True)
     if verbose:
         print(f"[oracle_engine_b200] built {out.name} in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
     return out
 
 
-def load(name: str) -> ctypes.CDLL:
+def load(name: str, defines=None) -> ctypes.CDLL:
     """The loaded library `name`, built first if needed."""
+    key = name + _define_flags(defines)[0]
     with _lock:
-        lib = _loaded.get(name)
+        lib = _loaded.get(key)
         if lib is None:
-            lib = ctypes.CDLL(str(build(name)))
-            _loaded[name] = lib
+            lib = ctypes.CDLL(str(build(name, defines=defines)))
+            _loaded[key] = lib
         return lib
+
+
+# head sizes the build check compiles the specialised attention for (others are built on demand)
+DEFAULT_HEAD_DIMS = (16, 32, 48, 64, 128)
 
 
 def build_all(names=None, verbose: bool = True) -> list[Path]:
     """Builds every library (in parallel processes of nvcc); used by the build check."""
     names = list(names or [n for n, (src, _) in LIBRARIES.items() if (CSRC / src).is_file()])
-    results: dict[str, object] = {}
+    jobs = []
+    for n in names:
+        if n == "attention_tc":
+            jobs.extend((n, {"OE_HD": hd}) for hd in DEFAULT_HEAD_DIMS)
+        else:
+            jobs.append((n, None))
+    results: dict[object, object] = {}
 
-    def work(n):
+    def work(job):
         try:
-            results[n] = build(n, verbose)
+            results[id(job)] = build(job[0], verbose, job[1])
         except Exception as e:           # noqa: BLE001 - reported below
-            results[n] = e
+            results[id(job)] = e
 
+    names = jobs
     threads = [threading.Thread(target=work, args=(n,)) for n in names]
     for t in threads:
         t.start()
     for t in threads:
         t.join()
-    errors = [f"{n}: {r}" for n, r in results.items() if isinstance(r, Exception)]
+    errors = [f"{j[0]}: {results[id(j)]}" for j in jobs if isinstance(results[id(j)], Exception)]
     if errors:
         raise BuildError("\n".join(errors))
-    return [results[n] for n in names]
+    return [results[id(j)] for j in jobs]

@@ -1,0 +1,450 @@
+// bf16 matrix product C (+)= A . W^T on the 5th-generation tensor cores (sm_100a):
+// TMA (cp.async.bulk.tensor) stages K-major operand tiles in 128B-swizzled shared memory,
+// one thread issues tcgen05.mma with float32 accumulators in tensor memory, four warps
+// read the accumulators back with tcgen05.ld and store.
+//
+// Both operands are [rows, K] row-major (activations [tokens, K], weights [out, K]), which
+// is the K-major form the instruction takes without a transpose.  The kernel works on an
+// "A" operand whose tile is 128 rows (the M of the instruction) and a "B" operand whose
+// tile is n_tile rows (16..256, the N of the instruction):
+//   * many tokens (prompts): A = activations, B = weights, n_tile = 128 or 256;
+//   * few tokens (decode):   A = weights, B = activations ("swap"), n_tile = tokens rounded
+//     up to 16, the output tile is stored transposed, and K is split over several CTAs so
+//     that all SMs stream weights.  The partial sums of a split go through a float32
+//     workspace and the CTA that finishes last adds them in split order (deterministic).
+// Roles per CTA (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocation and MMA
+// issue, warps 2-5 = epilogue.  Every wait on an mbarrier is bounded in time; a wait that
+// runs out sets an error flag, lets every role leave its loop, waits a fixed time for
+// copies in flight, frees the tensor memory and returns.  The host reads the flag with
+// oe_gemm_tc_error().
+// Takes the place of the reference's gemm_q / gemv_q (core/gguf_parser.cpp:868-997).
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include "common.cuh"
+#include <mutex>
+#include <unordered_map>
+
+namespace {
+
+constexpr int BLOCK_M = 128;       // rows of the A tile = UMMA M
+constexpr int BLOCK_K = 64;        // bf16 per k-block = one 128-byte swizzled row
+constexpr int UMMA_K = 16;
+constexpr int A_TILE_BYTES = BLOCK_M * BLOCK_K * 2;      // 16 KB
+constexpr int THREADS = 192;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s
+
+__device__ int g_error = 0;        // 0 = ok; else code of the wait that ran out
+
+struct SharedCtl {
+    uint64_t full[12];
+    uint64_t empty[12];
+    uint64_t tmem_full;
+    uint32_t tmem_base;
+    int abort_flag;
+    int is_last;
+    int epi_ok;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Waits for the phase with `parity` to complete; gives up after WAIT_LIMIT_NS or when
+// another role has given up, and then returns false.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, SharedCtl* ctl, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (uint32_t spin = 0;; spin++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 255u) == 255u) {
+            if (*(volatile int*)&ctl->abort_flag) return false;
+            if (global_ns() - t0 > WAIT_LIMIT_NS) {
+                atomicExch(&ctl->abort_flag, 1);
+                atomicCAS(&g_error, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c_inner, int c_outer) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(c_inner), "r"(c_outer)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle,
+// 8-row groups 1024 bytes apart (stride byte offset), descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;                    // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset
+    d |= (uint64_t)1 << 46;                    // version
+    d |= (uint64_t)2 << 61;                    // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor of tcgen05.mma.kind::f16: D float32, A and B bf16, both K-major.
+__device__ __forceinline__ uint32_t umma_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct GemmArgs {
+    void* C;
+    long long ldc;
+    int rows_a, rows_b, K;      // valid rows of the A (128-row) and B (n_tile-row) operands
+    int n_tile;                 // rows of the B tile, multiple of 16, <= 256
+    int stages;
+    int swap;                   // 1: C[b_row, a_row] (A = weights); 0: C[a_row, b_row] (A = activations)
+    int out_kind;               // 0 bf16 store, 1 float32 store, 2 float32 accumulate
+    int splits;
+    float* workspace;           // [splits][tiles_a][tiles_b][n_tile][128] float32 when splits > 1
+    int* counters;              // [tiles_a * tiles_b], zero between launches
+};
+
+__device__ __forceinline__ void store_out(const GemmArgs& g, long long idx, float v) {
+    if (g.out_kind == 0) ((bf16*)g.C)[idx] = __float2bfloat16_rn(v);
+    else if (g.out_kind == 1) ((float*)g.C)[idx] = v;
+    else ((float*)g.C)[idx] += v;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // tiles first (1024-byte aligned for the 128-byte swizzle), control block after them
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int b_tile_bytes = g.n_tile * BLOCK_K * 2;
+    const int stage_bytes = A_TILE_BYTES + ((b_tile_bytes + 1023) & ~1023);
+    SharedCtl* ctl = (SharedCtl*)(smem + (size_t)g.stages * stage_bytes);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_a = blockIdx.x, tile_b = blockIdx.y, split = blockIdx.z;
+    const int n_kb_total = (g.K + BLOCK_K - 1) / BLOCK_K;
+    const int kb_per = (n_kb_total + g.splits - 1) / g.splits;
+    const int kb0 = split * kb_per;
+    const int kb1 = min(n_kb_total, kb0 + kb_per);
+    const int n_kb = max(0, kb1 - kb0);
+    uint32_t tmem_cols = 32;
+    while ((int)tmem_cols < g.n_tile) tmem_cols <<= 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < g.stages; s++) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
+        mbar_init(&ctl->tmem_full, 1);
+        ctl->abort_flag = 0;
+        ctl->is_last = 0;
+        ctl->epi_ok = 1;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *(volatile uint32_t*)&ctl->tmem_base;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            for (int i = 0; i < n_kb; i++) {
+                const int s = i % g.stages;
+                const uint32_t phase = (uint32_t)(i / g.stages) & 1u;
+                if (!mbar_wait(&ctl->empty[s], phase ^ 1u, ctl, 1)) break;
+                uint8_t* a_dst = smem + (size_t)s * stage_bytes;
+                uint8_t* b_dst = a_dst + A_TILE_BYTES;
+                mbar_expect_tx(&ctl->full[s], (uint32_t)(A_TILE_BYTES + b_tile_bytes));
+                tma_load_2d(a_dst, &map_a, &ctl->full[s], (kb0 + i) * BLOCK_K, tile_a * BLOCK_M);
+                tma_load_2d(b_dst, &map_b, &ctl->full[s], (kb0 + i) * BLOCK_K, tile_b * g.n_tile);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issue ----------------
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(BLOCK_M, g.n_tile);
+            bool ok = true;
+            for (int i = 0; i < n_kb && ok; i++) {
+                const int s = i % g.stages;
+                const uint32_t phase = (uint32_t)(i / g.stages) & 1u;
+                ok = mbar_wait(&ctl->full[s], phase, ctl, 2);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = smem_u32(smem + (size_t)s * stage_bytes);
+                const uint32_t b_addr = a_addr + A_TILE_BYTES;
+#pragma unroll
+                for (int k = 0; k < BLOCK_K / UMMA_K; k++) {
+                    umma_bf16(tmem_base, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc,
+                              (i > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(&ctl->empty[s]);          // frees the stage when these MMAs have read it
+            }
+            umma_commit(&ctl->tmem_full);             // accumulator complete (also arrives if n_kb == 0)
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5 ----------------
+        const int quarter = warp & 3;                 // TMEM lanes 32*quarter .. +31 belong to this warp
+        const int row = quarter * 32 + lane;          // row of the A tile
+        const int a_row = tile_a * BLOCK_M + row;
+        // every epilogue thread takes the same decision, so that all of them reach the
+        // named barriers below
+        if (!mbar_wait(&ctl->tmem_full, 0, ctl, 3)) atomicExch(&ctl->epi_ok, 0);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const bool ok = *(volatile int*)&ctl->epi_ok != 0;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            const int tiles_a = gridDim.x, tiles_b = gridDim.y;
+            float* part = g.splits > 1
+                ? g.workspace + ((((size_t)split * tiles_a + tile_a) * tiles_b + tile_b) * (size_t)g.n_tile) * BLOCK_M
+                : nullptr;
+            for (int c0 = 0; c0 < g.n_tile; c0 += 16) {
+                uint32_t v[16];
+                if (n_kb > 0) {
+                    tmem_ld16(taddr + (uint32_t)c0, v);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) v[j] = 0u;
+                }
+                if (g.splits > 1) {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) part[(size_t)(c0 + j) * BLOCK_M + row] = __uint_as_float(v[j]);
+                } else if (a_row < g.rows_a) {
+                    if (g.swap) {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            const int b_row = tile_b * g.n_tile + c0 + j;
+                            if (b_row < g.rows_b) store_out(g, (long long)b_row * g.ldc + a_row, __uint_as_float(v[j]));
+                        }
+                    } else {
+                        const int b_row0 = tile_b * g.n_tile + c0;
+                        const long long base = (long long)a_row * g.ldc + b_row0;
+                        if (b_row0 + 16 <= g.rows_b && g.out_kind == 0 && (base & 7) == 0) {
+                            uint32_t p[8];
+#pragma unroll
+                            for (int j = 0; j < 8; j++) {
+                                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                                p[j] = *(uint32_t*)&h;
+                            }
+                            uint4* dst = (uint4*)((bf16*)g.C + base);
+                            dst[0] = make_uint4(p[0], p[1], p[2], p[3]);
+                            dst[1] = make_uint4(p[4], p[5], p[6], p[7]);
+                        } else if (b_row0 + 16 <= g.rows_b && g.out_kind != 0 && (base & 3) == 0) {
+                            float4* dst = (float4*)((float*)g.C + base);
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                float4 o = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                       __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                                if (g.out_kind == 2) {
+                                    const float4 old = dst[j];
+                                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                                }
+                                dst[j] = o;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; j++)
+                                if (b_row0 + j < g.rows_b) store_out(g, base + j, __uint_as_float(v[j]));
+                        }
+                    }
+                }
+            }
+            if (g.splits > 1) {
+                // the CTA that arrives last adds the partial sums in split order
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const int tile_id = tile_a * tiles_b + tile_b;
+                if (warp == 2 && lane == 0) {
+                    const int old = atomicAdd(&g.counters[tile_id], 1);
+                    ctl->is_last = (old == g.splits - 1) ? 1 : 0;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (*(volatile int*)&ctl->is_last) {
+                    __threadfence();
+                    if (a_row < g.rows_a) {
+                        for (int c = 0; c < g.n_tile; c++) {
+                            const int b_row = tile_b * g.n_tile + c;
+                            if (b_row >= g.rows_b) break;
+                            float sum = 0.f;
+                            for (int s = 0; s < g.splits; s++)
+                                sum += __ldcg(g.workspace + ((((size_t)s * tiles_a + tile_a) * tiles_b + tile_b) * (size_t)g.n_tile + c) * BLOCK_M + row);
+                            const long long idx = g.swap ? (long long)b_row * g.ldc + a_row : (long long)a_row * g.ldc + b_row;
+                            store_out(g, idx, sum);
+                        }
+                    }
+                    if (warp == 2 && lane == 0) g.counters[tile_id] = 0;
+                }
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+
+    __syncthreads();
+    if (*(volatile int*)&ctl->abort_flag) {
+        // a wait ran out: give copies and MMAs in flight a fixed time to land before the
+        // shared and tensor memory of this CTA are released
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------
+PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+std::mutex g_mutex;
+
+int get_encode() {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (g_encode) return 0;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || fn == nullptr) return e != cudaSuccess ? (int)e : 999;
+    g_encode = (PFN_cuTensorMapEncodeTiled_v12000)fn;
+    return 0;
+}
+
+// [rows, K] bf16 row-major with leading dimension ld (elements); box = BLOCK_K x box_rows
+int make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, long long ld, int box_rows) {
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+}
+
+}  // namespace
+
+extern "C" {
+
+// 1 if the tensor-core kernel takes these operands (TMA needs 16-byte aligned rows).
+int oe_gemm_tc_supported(const void* A, const void* W, int M, int N, int K, long long lda) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if ((K % 8) || (lda % 8)) return 0;
+    if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return 0;
+    return 1;
+}
+
+// Workspace bytes and counters the split-K path may need for any call with up to
+// `max_tokens` rows on the swapped path.
+long long oe_gemm_tc_workspace_bytes() { return 64ll << 20; }
+int oe_gemm_tc_counters() { return 4096; }
+
+// C[M,N] (+)= A[M,K] . W[N,K]^T ; out_kind: 0 bf16, 1 float32, 2 float32 accumulate.
+// workspace: float32 scratch of ws_bytes bytes, counters: n_counters zeroed ints (both may be null: no split).
+int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, long long lda, long long ldc,
+                    int out_kind, float* workspace, long long ws_bytes, int* counters, int n_counters,
+                    int sm_count, cudaStream_t st) {
+    if (!oe_gemm_tc_supported(A, W, M, N, K, lda)) return OE_ERR_UNSUPPORTED;
+    int rc = get_encode();
+    if (rc) return rc;
+    GemmArgs g;
+    g.C = C; g.ldc = ldc; g.K = K; g.out_kind = out_kind;
+    g.workspace = workspace; g.counters = counters; g.splits = 1;
+    CUtensorMap map_a, map_b;
+    dim3 grid;
+    const int n_kb = (K + BLOCK_K - 1) / BLOCK_K;
+    if (M <= 128) {
+        // few tokens: weights fill the 128 rows of the instruction, tokens are its N
+        g.swap = 1;
+        g.n_tile = ((M + 15) / 16) * 16;
+        g.rows_a = N; g.rows_b = M;
+        const int tiles_a = (N + BLOCK_M - 1) / BLOCK_M;
+        int splits = 1;
+        if (workspace && counters && tiles_a <= n_counters) {
+            splits = (sm_count + tiles_a - 1) / tiles_a;
+            if (splits > n_kb / 4) splits = n_kb / 4;
+            if (splits < 1) splits = 1;
+            const long long need = (long long)splits * tiles_a * g.n_tile * BLOCK_M * 4;
+            if (need > ws_bytes) splits = 1;
+            const int kb_per = (n_kb + splits - 1) / splits;
+            splits = (n_kb + kb_per - 1) / kb_per;          // no split without work
+        }
+        g.splits = splits;
+        if ((rc = make_map(&map_a, W, N, K, K, BLOCK_M))) return rc;
+        if ((rc = make_map(&map_b, A, M, K, lda, g.n_tile))) return rc;
+        grid = dim3(tiles_a, 1, splits);
+    } else {
+        g.swap = 0;
+        g.n_tile = N >= 256 ? 256 : ((N + 15) / 16) * 16;
+        g.rows_a = M; g.rows_b = N;
+        if ((rc = make_map(&map_a, A, M, K, lda, BLOCK_M))) return rc;
+        if ((rc = make_map(&map_b, W, N, K, K, g.n_tile))) return rc;
+        grid = dim3((M + BLOCK_M - 1) / BLOCK_M, (N + g.n_tile - 1) / g.n_tile, 1);
+        if (grid.y > 65535) return OE_ERR_UNSUPPORTED;
+    }
+    const int b_tile_bytes = g.n_tile * BLOCK_K * 2;
+    const int stage_bytes = A_TILE_BYTES + ((b_tile_bytes + 1023) & ~1023);
+    int stages = (200 * 1024) / stage_bytes;
+    if (stages > 10) stages = 10;
+    if (stages > n_kb && n_kb > 0) stages = n_kb < 2 ? 2 : n_kb;
+    if (stages < 2) stages = 2;
+    g.stages = stages;
+    const size_t smem = (size_t)stages * stage_bytes + sizeof(SharedCtl) + 1024;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    gemm_tc_kernel<<<grid, THREADS, smem, st>>>(map_a, map_b, g);
+    return (int)cudaGetLastError();
+}
+
+// Reads and clears the device-side error flag (0 = no wait ran out).
+int oe_gemm_tc_error() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(g_error, &zero, sizeof(int));
+    return v;
+}
+
+}  // extern "C"

@@ -1,10 +1,157 @@
-"""Entry points of the tensor-core kernels (bfloat16 serving path)."""
+"""Entry points of the tensor-core kernels of the bfloat16 serving path.
+
+`gemm`: csrc/gemm_tcgen05.cu (tcgen05.mma + TMA).  Shapes the kernel cannot take (rows
+not 16-byte aligned: K or the row stride not a multiple of 8) are reported by
+`gemm_supported`, and the caller uses the CUDA-core kernel for them; that choice depends
+on shapes only.
+"""
 from __future__ import annotations
 
+from ctypes import c_int, c_longlong, c_void_p
 
-def gemm_supported(a, w, out) -> bool:
-    return False
+import torch
+
+from . import build as _build
+from . import ops
+from .ops import KernelError
+
+_state: dict = {}
 
 
-def attention_supported(head_dim, n_heads, n_kv_heads) -> bool:
-    return False
+def _lib():
+    lib = _state.get("gemm")
+    if lib is None:
+        lib = _build.load("gemm_tc")
+        lib.oe_gemm_tc_supported.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_longlong]
+        lib.oe_gemm_tc_supported.restype = c_int
+        lib.oe_gemm_tc_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong,
+                                        c_int, c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p]
+        lib.oe_gemm_tc_bf16.restype = c_int
+        lib.oe_gemm_tc_error.argtypes = []
+        lib.oe_gemm_tc_error.restype = c_int
+        lib.oe_gemm_tc_workspace_bytes.restype = c_longlong
+        lib.oe_gemm_tc_counters.restype = c_int
+        _state["gemm"] = lib
+    return lib
+
+
+def _scratch(device):
+    """Split-K workspace and tile counters of `device` (allocated once, zeroed once)."""
+    key = ("scratch", device.index)
+    sc = _state.get(key)
+    if sc is None:
+        lib = _lib()
+        ws = torch.empty(lib.oe_gemm_tc_workspace_bytes() // 4, dtype=torch.float32, device=device)
+        counters = torch.zeros(lib.oe_gemm_tc_counters(), dtype=torch.int32, device=device)
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        sc = (ws, counters, sms)
+        _state[key] = sc
+    return sc
+
+
+def gemm_supported(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        return False
+    K = a.shape[1]
+    return (K % 8 == 0 and a.stride(0) % 8 == 0 and a.stride(1) == 1 and w.is_contiguous()
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.stride(1) == 1)
+
+
+def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool = False, split_k: bool = True) -> None:
+    """out (+)= a @ w.T, a [M, K] and w [N, K] bfloat16; out bfloat16 or float32 [M, N]."""
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"gemm: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not agree")
+    if not gemm_supported(a, w, out):
+        raise KernelError("gemm: the tensor-core kernel needs bfloat16 operands with 16-byte aligned rows")
+    if accumulate:
+        if out.dtype != torch.float32:
+            raise KernelError("gemm: accumulate needs a float32 output")
+        kind = 2
+    elif out.dtype == torch.bfloat16:
+        kind = 0
+    elif out.dtype == torch.float32:
+        kind = 1
+    else:
+        raise KernelError("gemm: output must be bfloat16 or float32")
+    ws, counters, sms = _scratch(a.device)
+    code = _lib().oe_gemm_tc_bf16(out.data_ptr(), a.data_ptr(), w.data_ptr(), M, N, K, a.stride(0), out.stride(0), kind,
+                                  ws.data_ptr() if split_k else None, ws.numel() * 4,
+                                  counters.data_ptr() if split_k else None, counters.numel(), sms,
+                                  torch.cuda.current_stream().cuda_stream)
+    ops._check(code, "gemm_tc")
+
+
+def device_error() -> int:
+    """The code of a bounded wait that ran out inside a tensor-core kernel since the last
+    call (0 = none).  Synchronises the device."""
+    if "gemm" not in _state:
+        return 0
+    return int(_lib().oe_gemm_tc_error())
+
+
+# ----------------------------------------------------------------------------------------
+# attention (csrc/attention_mma.cu, one library per head size)
+# ----------------------------------------------------------------------------------------
+from ctypes import c_float  # noqa: E402
+
+
+def attention_supported(head_dim: int, n_heads: int, n_kv_heads: int) -> bool:
+    return head_dim % 16 == 0 and 16 <= head_dim <= 256 and n_heads % n_kv_heads == 0 \
+        and n_heads // n_kv_heads <= 64
+
+
+def _attn_lib(head_dim: int):
+    key = ("attn", head_dim)
+    lib = _state.get(key)
+    if lib is None:
+        lib = _build.load("attention_tc", {"OE_HD": head_dim})
+        lib.oe_attn_mma_bf16.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                         c_void_p, c_void_p]
+        lib.oe_attn_mma_bf16.restype = c_int
+        lib.oe_attn_mma_partial_floats.argtypes = [c_int, c_int, c_int]
+        lib.oe_attn_mma_partial_floats.restype = c_longlong
+        _state[key] = lib
+    return lib
+
+
+def decode_splits(n_seqs: int, n_kv_heads: int, sm_count: int, max_pages: int) -> int:
+    """How many CTAs share one (sequence, KV head) of a decode step: enough to occupy the
+    GPU about twice, never more than the pages a sequence can have.  Depends on the batch
+    size and the cache geometry only, so a captured graph stays valid."""
+    ctas = max(1, n_seqs * n_kv_heads)
+    return max(1, min(max_pages, 32, (2 * sm_count + ctas - 1) // ctas))
+
+
+def attention(out, qkv, cache, tables, ctx, n_heads: int, n_kv_heads: int, head_dim: int, window: int,
+              scale: float) -> None:
+    """out[t] = attention of the step's tokens over their sequences' paged cache (bfloat16).
+
+    qkv [T, >= H hd] (queries first), out [T, H hd], cache [pages, 2, KVH, PAGE, hd]."""
+    T = out.shape[0]
+    if out.dtype != torch.bfloat16 or qkv.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
+        raise KernelError("attention: bfloat16 tensors expected")
+    if not out.is_contiguous() or out.shape[1] != n_heads * head_dim or qkv.stride(1) != 1 or not cache.is_contiguous():
+        raise KernelError("attention: out must be contiguous [T, H hd]; cache contiguous")
+    if tuple(cache.shape[1:]) != (2, n_kv_heads, ops.PAGE, head_dim):
+        raise KernelError("attention: cache entry must be [pages, 2, KVH, PAGE, head_dim]")
+    lib = _attn_lib(head_dim)
+    n_splits, partial = 1, None
+    group = n_heads // n_kv_heads
+    if ctx.all_decode and group <= 16:
+        sms = torch.cuda.get_device_properties(out.device).multi_processor_count
+        n_splits = decode_splits(ctx.n_seqs, n_kv_heads, sms, tables.shape[1])
+        if n_splits > 1:
+            partial = torch.empty(lib.oe_attn_mma_partial_floats(T, n_heads, n_splits), dtype=torch.float32,
+                                  device=out.device)
+    code = lib.oe_attn_mma_bf16(out.data_ptr(), qkv.data_ptr(), qkv.stride(0), cache.data_ptr(), tables.data_ptr(),
+                                tables.shape[1], ctx.cu_q.data_ptr(), ctx.seq_start.data_ptr(),
+                                ctx.seq_qlen.data_ptr(), ctx.tok_seq.data_ptr(), ctx.n_seqs, T, max(1, ctx.max_qlen),
+                                n_heads, n_kv_heads, int(window), float(scale), n_splits,
+                                None if partial is None else partial.data_ptr(),
+                                torch.cuda.current_stream().cuda_stream)
+    ops._check(code, "attention_mma")
+    if n_splits > 1:
+        ops.LAUNCHES[0] += 1

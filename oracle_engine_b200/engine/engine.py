@@ -96,6 +96,11 @@ class Engine:
         if err is not None and int(err.item()) != 0:
             err.zero_()
             raise RuntimeError("a token id outside the vocabulary reached the embedding kernel")
+        from ..csrc import ops_tc
+        code = ops_tc.device_error()
+        if code:
+            raise RuntimeError(f"a bounded wait inside a tensor-core kernel ran out (code {code}); "
+                               f"the results of the last steps are not valid")
 
     # ------------------------------------------------------------------ generation
     def generate(self, prompts, params: GenParams | None = None, batch_size: int | None = None,

@@ -1,0 +1,277 @@
+"""Each CUDA kernel alone against a plain float32/float64 restatement, at sizes other than
+the engine's (tails, sizes that are no power of two, length 1, several head sizes)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as pl
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _rand(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed_rmsnorm_swiglu_gather(dtype):
+    from oracle_engine_b200.csrc import ops
+    V, D, n = 77, 200, 9
+    table = _rand(V, D, dtype=dtype)
+    ids = torch.tensor([0, 76, 5, 5, 33, 1, 2, 3, 70], dtype=torch.int32, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    x = torch.empty(n, D, device=DEV)
+    ops.embed_gather(x, table, ids, err)
+    assert torch.equal(x, table.float()[ids.long()]) and err.item() == 0
+    bad = torch.tensor([3, 77, -1], dtype=torch.int32, device=DEV)
+    xb = torch.empty(3, D, device=DEV)
+    ops.embed_gather(xb, table, bad, err)
+    assert err.item() == 1 and torch.equal(xb[1], torch.zeros(D, device=DEV)) and torch.equal(xb[0], table.float()[3])
+
+    for D2, eps in ((200, 1e-5), (3, 1e-6), (1031, 1e-2)):
+        xr = _rand(5, D2, scale=3.0, seed=1)
+        w = _rand(D2, seed=2)
+        y = torch.empty(5, D2, dtype=dtype, device=DEV)
+        ops.rmsnorm(y, xr, w, eps)
+        want = pl.rms_norm(xr.double().cpu(), w.double().cpu(), eps)
+        tol = 1e-5 if dtype == torch.float32 else 2e-2
+        assert (y.double().cpu() - want).abs().max() < tol * max(1.0, want.abs().max())
+
+    for FF in (160, 7, 515):
+        gu = _rand(6, 2 * FF, dtype=dtype, scale=2.0, seed=3)
+        out = torch.empty(6, FF, dtype=dtype, device=DEV)
+        ops.swiglu(out, gu)
+        g, u = gu.double().cpu()[:, :FF], gu.double().cpu()[:, FF:]
+        want = g / (1 + torch.exp(-g)) * u
+        tol = 1e-6 if dtype == torch.float32 else 1e-2
+        assert (out.double().cpu() - want).abs().max() < tol * max(1.0, want.abs().max())
+
+    rows = torch.tensor([4, 0, 4], dtype=torch.int32, device=DEV)
+    src = _rand(5, 33, seed=4)
+    dst = torch.empty(3, 33, device=DEV)
+    ops.gather_rows_f32(dst, src, rows)
+    assert torch.equal(dst, src[rows.long()])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K", [(1, 5, 3), (7, 65, 130), (130, 64, 17), (64, 200, 256)])
+def test_gemm_simple(dtype, M, N, K):
+    from oracle_engine_b200.csrc import ops
+    a, w = _rand(M, K, dtype=dtype, seed=1), _rand(N, K, dtype=dtype, seed=2)
+    want = a.double() @ w.double().T
+    tol = 1e-5 * math.sqrt(K)
+    out = torch.empty(M, N, dtype=dtype, device=DEV)
+    ops.gemm_simple(out, a, w)
+    assert (out.double() - want).abs().max() < (tol if dtype == torch.float32 else 0.01 * want.abs().max() + tol)
+    out32 = torch.empty(M, N, device=DEV)
+    ops.gemm_simple(out32, a, w)
+    assert (out32.double() - want).abs().max() < tol
+    base = _rand(M, N, seed=3)
+    acc = base.clone()
+    ops.gemm_simple(acc, a, w, accumulate=True)
+    assert (acc.double() - (base.double() + want)).abs().max() < tol
+    # a row's result does not depend on the other rows (bit for bit)
+    one = torch.empty(1, N, device=DEV)
+    ops.gemm_simple(one, a[M - 1:M], w)
+    assert torch.equal(one[0], out32[M - 1])
+    # a view with a row stride
+    wide = _rand(M, K + 8, dtype=dtype, seed=5)
+    outv = torch.empty(M, N, device=DEV)
+    ops.gemm_simple(outv, wide[:, :K], w)
+    assert (outv.double() - wide[:, :K].double() @ w.double().T).abs().max() < tol
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 3072, 1024), (5, 136, 72), (64, 520, 4096), (100, 333, 200),
+                                   (128, 48, 64), (129, 48, 200), (300, 1000, 520), (1000, 264, 72)])
+def test_gemm_tcgen05(M, N, K):
+    from oracle_engine_b200.csrc import ops_tc
+    a, w = _rand(M, K, dtype=torch.bfloat16, scale=0.5, seed=1), _rand(N, K, dtype=torch.bfloat16, scale=0.5, seed=2)
+    want = a.double() @ w.double().T
+    tol = 2e-6 * K + 1e-5
+    out32 = torch.full((M, N), 9.0, device=DEV)
+    ops_tc.gemm(out32, a, w)
+    assert (out32.double() - want).abs().max() < tol
+    out16 = torch.full((M, N), 9.0, dtype=torch.bfloat16, device=DEV)
+    ops_tc.gemm(out16, a, w)
+    assert (out16.double() - want).abs().max() < 0.005 * want.abs().max() + tol
+    base = _rand(M, N, seed=3)
+    acc = base.clone()
+    ops_tc.gemm(acc, a, w, accumulate=True)
+    assert (acc.double() - (base.double() + want)).abs().max() < tol
+    nosplit = torch.empty(M, N, device=DEV)
+    ops_tc.gemm(nosplit, a, w, split_k=False)
+    assert (nosplit.double() - want).abs().max() < tol
+    again = torch.empty(M, N, device=DEV)
+    ops_tc.gemm(again, a, w)
+    assert torch.equal(again, out32)                     # split sums are added in a fixed order
+    assert ops_tc.device_error() == 0
+    assert not ops_tc.gemm_supported(a[:, :K - 1], w[:, :K - 1].contiguous(), out32)      # rows not 16-byte aligned
+
+
+def _paged(k, v, lens, dtype, extra_pages=3, seed=0):
+    """Dense per-sequence K/V [len, KVH, hd] -> one cache entry [pages, 2, KVH, 64, hd] with
+    shuffled pages, and the page tables."""
+    KVH, hd = k[0].shape[1], k[0].shape[2]
+    need = [(n + 63) // 64 for n in lens]
+    total = sum(need) + extra_pages
+    rng = np.random.RandomState(seed)
+    order = rng.permutation(total).tolist()
+    cache = torch.full((total, 2, KVH, 64, hd), 1e4, dtype=dtype)      # stale values must never be read
+    tables = np.full((len(lens), max(need) + 1), -1, dtype=np.int32)
+    for b, n in enumerate(lens):
+        for p in range(need[b]):
+            page = order.pop()
+            tables[b, p] = page
+            rows = slice(p * 64, min(n, p * 64 + 64))
+            cnt = rows.stop - rows.start
+            cache[page, 0, :, :cnt] = k[b][rows].transpose(0, 1).to(dtype)
+            cache[page, 1, :, :cnt] = v[b][rows].transpose(0, 1).to(dtype)
+    return cache.to(DEV), torch.from_numpy(tables).to(DEV)
+
+
+def _attn_case(H, KVH, hd, lens, qlens, dtype, seed):
+    """Queries for the last qlen tokens of each sequence; returns tensors and the plain result."""
+    g = torch.Generator().manual_seed(seed)
+    k = [torch.randn(n, KVH, hd, generator=g) for n in lens]
+    v = [torch.randn(n, KVH, hd, generator=g) for n in lens]
+    q = [torch.randn(n, H, hd, generator=g) * 2.0 for n in lens]
+    rd = (lambda t: t.to(dtype).double())
+    want = []
+    return k, v, q, rd
+
+
+@pytest.mark.parametrize("dtype,kernel", [(torch.float32, "paged"), (torch.bfloat16, "paged"),
+                                          (torch.bfloat16, "mma")])
+@pytest.mark.parametrize("H,KVH,hd,window", [(4, 2, 16, 0), (6, 2, 32, 0), (5, 1, 48, 0), (8, 8, 64, 0),
+                                             (24, 8, 128, 0), (6, 3, 32, 70), (4, 4, 16, 5)])
+def test_attention_kernels(dtype, kernel, H, KVH, hd, window):
+    """Ragged prompts and decoded tokens over a shuffled paged cache with stale pages."""
+    from types import SimpleNamespace
+    from oracle_engine_b200.csrc import ops, ops_tc
+    lens = [1, 64, 65, 200, 130, 17]
+    g = torch.Generator().manual_seed(H * 100 + hd)
+    k = [torch.randn(n, KVH, hd, generator=g) for n in lens]
+    v = [torch.randn(n, KVH, hd, generator=g) for n in lens]
+    q = [torch.randn(n, H, hd, generator=g) * 1.5 for n in lens]
+    cache, tables = _paged(k, v, lens, dtype)
+    rd = lambda t: t.to(dtype).double()                                  # noqa: E731
+    full = [pl.causal_attention(rd(q[b]), rd(k[b]), rd(v[b]), window or None) for b in range(len(lens))]
+    tol = 1e-5 if dtype == torch.float32 else 2.5e-2
+    for mode, qlens in (("prompt", [1, 64, 30, 200, 67, 17]), ("decode", [1] * len(lens))):
+        tok_seq, tok_pos, rows_q, want = [], [], [], []
+        cu, starts = [0], []
+        for b, (n, ql) in enumerate(zip(lens, qlens)):
+            starts.append(n - ql)
+            for i in range(n - ql, n):
+                tok_seq.append(b)
+                tok_pos.append(i)
+                rows_q.append(q[b][i].reshape(-1))
+                want.append(full[b][i])
+            cu.append(len(tok_seq))
+        # a padding row and a padding sequence at the end
+        tok_seq.append(-1)
+        tok_pos.append(0)
+        rows_q.append(torch.zeros(H * hd))
+        T = len(tok_seq)
+        # queries live in a wider buffer (as in the fused qkv projection)
+        qbuf = torch.zeros(T, H * hd + 2 * KVH * hd)
+        qbuf[:, :H * hd] = torch.stack(rows_q)
+        qbuf = qbuf.to(dtype).to(DEV)
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)    # noqa: E731
+        out = torch.full((T, H * hd), 7.0, dtype=dtype, device=DEV)
+        tab = torch.cat([tables, torch.full((1, tables.shape[1]), -1, dtype=torch.int32, device=DEV)])
+        if kernel == "paged":
+            ops.attn_paged(out, qbuf, cache, tab, i32(tok_seq), i32(tok_pos), H, KVH, hd, window, 1 / math.sqrt(hd))
+        else:
+            ctx = SimpleNamespace(cu_q=i32(cu + [cu[-1]]), seq_start=i32(starts + [0]), seq_qlen=i32(qlens + [0]),
+                                  tok_seq=i32(tok_seq), n_seqs=len(lens) + 1, max_qlen=max(qlens),
+                                  all_decode=(mode == "decode"))
+            ops_tc.attention(out, qbuf, cache, tab, ctx, H, KVH, hd, window, 1 / math.sqrt(hd))
+        got = out[:T - 1].double().cpu()
+        err = (got - torch.stack(want)).abs().max().item()
+        assert err < tol, f"{kernel} {mode}: {err}"
+
+
+def test_rope_kv_write():
+    from oracle_engine_b200.csrc import ops
+    from oracle_engine_b200.parts.positions import rotary_inv_freq
+    H, KVH, hd, T = 3, 2, 24, 6
+    for dtype in (torch.float32, torch.bfloat16):
+        inv = rotary_inv_freq(hd, 10000.0, {"factor": 4.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                                            "original_max_position_embeddings": 16})
+        assert torch.allclose(inv, pl.rope_inv_freq(hd, 10000.0, {"rope_type": "llama3", "factor": 4.0,
+                              "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                              "original_max_position_embeddings": 16}), rtol=0, atol=0)
+        ang = torch.arange(300, dtype=torch.float64)[:, None] * inv[None]
+        cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
+        qkv = _rand(T, (H + 2 * KVH) * hd, dtype=dtype, seed=9)
+        orig = qkv.clone()
+        cache = torch.zeros(5, 2, KVH, 64, hd, dtype=dtype, device=DEV)
+        tables = torch.tensor([[3, 1, -1], [4, -1, -1]], dtype=torch.int32, device=DEV)
+        tok_seq = torch.tensor([0, 0, 1, -1, 0, 1], dtype=torch.int32, device=DEV)
+        tok_pos = torch.tensor([63, 64, 0, 0, 127, 1], dtype=torch.int32, device=DEV)
+        ops.rope_kv_write(qkv, cos, sin, cache, tables, tok_seq, tok_pos, H, KVH, hd, True)
+        tol = 1e-5 if dtype == torch.float32 else 2e-2
+        for t in range(T):
+            if tok_seq[t] < 0:
+                assert torch.equal(qkv[t], orig[t])
+                continue
+            p = torch.tensor([int(tok_pos[t])])
+            o = orig[t].double().cpu()
+            qw = pl.rope_rotate(o[:H * hd].reshape(1, H, hd), p, inv)
+            kw = pl.rope_rotate(o[H * hd:(H + KVH) * hd].reshape(1, KVH, hd), p, inv)
+            assert (qkv[t, :H * hd].double().cpu() - qw.reshape(-1)).abs().max() < tol
+            page = int(tables[int(tok_seq[t]), int(tok_pos[t]) // 64])
+            r = int(tok_pos[t]) % 64
+            assert (cache[page, 0, :, r].double().cpu() - kw[0]).abs().max() < tol
+            assert torch.equal(cache[page, 1, :, r].cpu(), orig[t, (H + KVH) * hd:].reshape(KVH, hd).cpu())
+        assert cache[0].abs().max() == 0 and cache[2].abs().max() == 0          # unmapped pages untouched
+        # no rotation (a mixer without position encoding), queries only
+        q_only = orig[:, :H * hd].clone()
+        ops.rope_kv_write(q_only, None, None, None, tables, tok_seq, tok_pos, H, KVH, hd, False)
+        assert torch.equal(q_only, orig[:, :H * hd])
+
+
+def test_argmax_and_sampling():
+    from oracle_engine_b200.csrc import ops
+    V, R = 1003, 6
+    g = torch.Generator().manual_seed(5)
+    logits = (torch.randn(R, V, generator=g) * 3).to(DEV)
+    logits[2, 100] = logits[2, 900] = 50.0                      # a tie: the first maximum wins
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    ops.argmax_rows(logits, out)
+    assert out.tolist() == [pl.greedy(logits[r].cpu()) for r in range(R)] and out[2].item() == 100
+
+    n_slots = 8
+    seeds = torch.arange(100, 100 + n_slots, dtype=torch.int64, device=DEV)
+    row_slot = torch.tensor([5, 0, 7, 2, 3, 1], dtype=torch.int32, device=DEV)
+    cases = [dict(temperature=0.8, top_k=0, top_p=1.0, penalty=1.0), dict(temperature=1.0, top_k=40, top_p=0.9, penalty=1.15),
+             dict(temperature=0.7, top_k=5, top_p=1.0, penalty=1.0), dict(temperature=1.3, top_k=0, top_p=0.5, penalty=1.0),
+             dict(temperature=0.0, top_k=40, top_p=0.9, penalty=1.5)]
+    for c in cases:
+        counters = torch.zeros(n_slots, dtype=torch.int32, device=DEV)
+        hist = torch.zeros(n_slots, 16, dtype=torch.int32, device=DEV)
+        hist_count = torch.zeros(n_slots, dtype=torch.int32, device=DEV)
+        history = {int(s): [] for s in row_slot.tolist()}
+        for s in history:                                           # some recorded tokens, with a repeat
+            toks = [(s * 37 + j * 11) % V for j in range(5)] + [int(logits[row_slot.tolist().index(s)].argmax())] * 2
+            history[s] = toks
+            for j, t in enumerate(toks):
+                hist[s, j % 16] = t
+            hist_count[s] = len(toks)
+        for draw in range(3):
+            work = logits.clone()
+            ops.sample_rows(work, out, row_slot, c["temperature"], c["top_k"], c["top_p"], c["penalty"], 6, seeds,
+                            counters, hist, hist_count, record=True)
+            got = out.tolist()
+            for r, s in enumerate(row_slot.tolist()):
+                u = pl.uniform_from_counter(100 + s, draw)
+                want = pl.sample(logits[r].cpu(), c["temperature"], c["top_k"], c["top_p"], u, history[s],
+                                 c["penalty"], 6)
+                assert got[r] == want, f"{c} draw {draw} row {r}: {got[r]} vs {want}"
+                history[s].append(got[r])
+        assert counters[5].item() == (3 if c["temperature"] > 0 else 0) and hist_count[5].item() == 10

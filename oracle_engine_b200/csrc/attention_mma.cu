@@ -360,3 +360,52 @@ int oe_attn_mma_bf16(bf16* out, const bf16* q, long long q_stride, const bf16* c
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------
+// The entry point that allocates nothing (see attention_noalloc.h).
+// ---------------------------------------------------------------------------------------
+#include "attention_noalloc.h"
+
+namespace {
+// Split-key partials of one call; shared by all calls on this device.
+static __device__ __align__(256) float g_noalloc_scratch[OE_ATTN_NOALLOC_MAX_FLOATS];
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not a device
+// address; the address is looked up once per device and kept here.
+float* g_noalloc_addr[64] = {nullptr};
+}  // namespace
+
+extern "C" {
+
+int oe_attn_mma_bf16_noalloc(bf16* out, const bf16* q, long long q_stride, const bf16* cache, const int* tables,
+                             int max_pages, const int* cu_q, const int* seq_start, const int* seq_qlen,
+                             const int* tok_seq, int n_seqs, int n_tokens, int max_qlen, int H, int KVH, int window,
+                             float scale, int n_splits, cudaStream_t stream) {
+    if (n_seqs <= 0 || n_tokens <= 0) return 0;
+    if (n_splits < 1) n_splits = 1;
+    if (n_splits > 1 && oe_attn_mma_partial_floats(n_tokens, H, n_splits) > OE_ATTN_NOALLOC_MAX_FLOATS)
+        return OE_ERR_SCRATCH_TOO_SMALL;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return OE_ERR_UNSUPPORTED;
+    if (g_noalloc_addr[dev] == nullptr) {
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);      // first call on this device
+        if (e != cudaSuccess) return (int)e;
+        g_noalloc_addr[dev] = p;
+    }
+    return oe_attn_mma_bf16(out, q, q_stride, cache, tables, max_pages, cu_q, seq_start, seq_qlen, tok_seq, n_seqs,
+                            n_tokens, max_qlen, H, KVH, window, scale, n_splits, g_noalloc_addr[dev], stream);
+}
+
+const char* oe_attn_mma_error_string(int code) {
+    if (code == 0) return "ok";
+    if (code == OE_ERR_SCRATCH_TOO_SMALL)
+        return "the call needs more split-key scratch than the library's fixed array holds "
+               "(n_tokens * H * n_splits * (head_dim + 2) floats > OE_ATTN_NOALLOC_MAX_FLOATS); "
+               "use fewer splits or fewer tokens per call";
+    if (code == OE_ERR_UNSUPPORTED) return "sizes or alignment outside what the attention kernel takes";
+    return cudaGetErrorString((cudaError_t)code);
+}
+
+}  // extern "C"

@@ -1,0 +1,173 @@
+"""Generation through the Python entry point: greedy and temperature against the plain
+implementation, stop tokens, batches one after another with slots used again, long
+decoding, and the first tokens of a sequence."""
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_llama as pl
+from helpers import TOL
+
+pytestmark = pytest.mark.gpu
+
+
+def _engine(model_dirs, name, dtype, **kw):
+    from oracle_engine_b200.engine.engine import Engine
+    return Engine.from_pretrained(model_dirs[name], dtype=dtype, **kw)
+
+
+def _check_greedy(plain, prompt, got, margin):
+    """Every generated token is the plain model's argmax, or within `margin` of it."""
+    seq = list(prompt)
+    for tok in got:
+        lg = plain.logits(seq)[-1]
+        assert lg.max().item() - lg[tok].item() <= margin, f"token {tok} at position {len(seq)}"
+        seq.append(tok)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_workload_a(model_dirs, plain_models, dtype):
+    """Tiny A: prompts of 5, 11 and 17 tokens, 8 greedy steps each."""
+    from oracle_engine_b200 import GenParams
+    eng = _engine(model_dirs, "A", dtype, max_tokens=256)
+    plain = plain_models["A"]
+    prompts = [helpers.random_tokens(n, 256, 20 + i) for i, n in enumerate((5, 11, 17))]
+    got = eng.generate(prompts, GenParams.greedy(8, ignore_eos=True))
+    assert [len(g) for g in got] == [8, 8, 8]
+    if dtype == "float32":
+        assert got == [pl.generate(plain, p, 8) for p in prompts]
+    for p, g in zip(prompts, got):
+        _check_greedy(plain, p, g, 0.0 if dtype == "float32" else 2 * TOL[dtype])
+    eng.cache.check()
+    assert eng.cache.slots.n_free == eng.cache.n_slots
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_temperature_workload_b(model_dirs, plain_models, dtype):
+    """Tiny B: prompts of 1, 9, 40 and 100 tokens, 12 steps at temperature 0.8, each
+    sequence drawing from its own generator."""
+    from oracle_engine_b200 import GenParams
+    eng = _engine(model_dirs, "B", dtype, max_tokens=512)
+    plain = plain_models["B"]
+    prompts = [helpers.random_tokens(n, 384, 30 + i) for i, n in enumerate((1, 9, 40, 100))]
+    params = GenParams(n_predict=12, temperature=0.8, top_k=0, top_p=1.0, repeat_penalty=1.0, seed=77, ignore_eos=True)
+    got = eng.generate(prompts, params)
+    for i, (p, g) in enumerate(zip(prompts, got)):
+        seq = list(p)
+        for step, tok in enumerate(g):
+            lg = plain.logits(seq)[-1]
+            u = pl.uniform_from_counter(77 + i, step)
+            want = pl.sample(lg, 0.8, 0, 1.0, u)
+            if tok != want:
+                # allowed only when u falls within rounding of the boundary between the two tokens
+                prob = pl.softmax_rows(lg / 0.8)
+                c = torch.cumsum(prob, 0)
+                edge = min(abs(float(c[min(tok, want)]) - u), abs(float(c[max(tok, want)]) - u))
+                assert edge < (1e-5 if dtype == "float32" else 2e-2), f"request {i} step {step}: {tok} vs {want}"
+            seq.append(tok)
+    eng.cache.check()
+
+
+def test_temperature_seed_is_per_request(model_dirs):
+    from oracle_engine_b200 import GenParams
+    eng = _engine(model_dirs, "B", "float32", max_tokens=256)
+    p = helpers.random_tokens(9, 384, 31)
+    params = GenParams(n_predict=10, temperature=1.0, top_k=0, top_p=1.0, repeat_penalty=1.0, seed=5, ignore_eos=True)
+    a = eng.generate([p, p, p], params)
+    assert a[0] != a[1] or a[1] != a[2]                    # same prompt, seeds 5, 6, 7
+    b = eng.generate([p], params)                          # alone: the same draws as request 0 in the batch
+    assert b[0] == a[0]
+    c = eng.generate([p, p], GenParams(n_predict=10, temperature=1.0, top_k=0, top_p=1.0, repeat_penalty=1.0,
+                                       seed=6, ignore_eos=True), batch_size=1)
+    assert c[0] == a[1] and c[1] == a[2]                   # batches one after another reuse slot 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_full_chain_repeat_penalty_topk_topp(model_dirs, plain_models, dtype):
+    from oracle_engine_b200 import GenParams
+    eng = _engine(model_dirs, "C", dtype, max_tokens=256)
+    plain = plain_models["C"]
+    prompts = [helpers.random_tokens(n, 331, 40 + i) for i, n in enumerate((3, 20))]
+    params = GenParams(n_predict=10, temperature=0.9, top_k=12, top_p=0.8, repeat_penalty=1.3, repeat_last_n=8, seed=3,
+                       ignore_eos=True)
+    got = eng.generate(prompts, params)
+    for i, (p, g) in enumerate(zip(prompts, got)):
+        seq = list(p)
+        for step, tok in enumerate(g):
+            lg = plain.logits(seq)[-1]
+            hist = list(p[:-1]) + g[:step]
+            want = pl.sample(lg, 0.9, 12, 0.8, pl.uniform_from_counter(3 + i, step), hist, 1.3, 8)
+            if dtype == "float32":
+                assert tok == want, f"request {i} step {step}"
+            else:
+                kept = pl.repeat_penalty(lg.double(), hist, 1.3, 8)
+                assert kept[tok] >= kept.topk(14).values[-1] - 0.1        # inside (about) the top-k set
+            seq.append(tok)
+
+
+def test_stop_tokens_batches_and_slot_reuse(model_dirs, plain_models):
+    """Seven requests in batches of three with a cache for one batch only: sequences that
+    hit a stop id end earlier (the stop id is not emitted), slots and pages are used again."""
+    from oracle_engine_b200 import GenParams
+    eng = _engine(model_dirs, "A", "float32", max_tokens=320, n_slots=3)
+    plain = plain_models["A"]
+    prompts = [helpers.random_tokens(n, 256, 60 + i) for i, n in enumerate((5, 1, 30, 64, 9, 65, 2))]
+    free_run = [pl.generate(plain, p, 20) for p in prompts]
+    stop = {free_run[0][3], free_run[4][0], free_run[5][10]}
+    want = [pl.generate(plain, p, 20, stop_ids=stop) for p in prompts]
+    res = eng.generate(prompts, GenParams.greedy(20, stop_ids=tuple(stop)), batch_size=3, return_results=True)
+    assert [r.tokens for r in res] == want
+    assert [r.finish_reason for r in res] == ["stop" if len(w) < 20 else "length" for w in want]
+    assert any(len(w) < 20 for w in want) and any(len(w) == 20 for w in want)
+    eng.cache.check()
+    assert eng.cache.slots.n_free == 3
+    # the model's own eos ids stop a sequence unless told otherwise
+    eos = plain.cfg["eos_token_id"]
+    forced = [t for t in range(256) if t != eos][:3]
+    assert eng.spec.stop_ids == (eos,)
+    out = eng.generate([forced], GenParams.greedy(30))
+    assert eos not in out[0]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_from_the_first_token(model_dirs, plain_models, tmp_path, dtype):
+    """A one-token prompt, then 300 tokens one by one (five pages, graph replay), two
+    sequences of different phase in one batch."""
+    from oracle_engine_b200.engine.engine import Engine
+    plain = plain_models["B"]
+    eng = Engine.from_pretrained(model_dirs["B"], dtype=dtype, max_tokens=704)
+    requests = [helpers.random_tokens(n, 384, 80 + i) for i, n in enumerate((301, 260))]
+    steps = helpers.batched_steps(requests, [1, 3], 2)
+    out = helpers.TraceRunner(eng, tmp_path / "long").run(steps)
+    got = helpers.collect(steps, out, requests)
+    for i, toks in enumerate(requests):
+        want = plain.logits(toks).numpy()
+        err = np.abs(got[i] - want).max(axis=1)
+        assert err.max() < TOL[dtype], f"request {i}: first bad position {int((err >= TOL[dtype]).argmax())}"
+    assert eng.stepper.use_graphs and eng.stepper._graphs[2].graph is not None
+    eng.cache.check()
+
+
+def test_refusals(model_dirs):
+    from oracle_engine_b200 import GenParams, SequenceStep
+    from oracle_engine_b200.cache.slots import CacheFull
+    from oracle_engine_b200.engine.step import StepError
+    eng = _engine(model_dirs, "A", "float32", max_tokens=128)
+    with pytest.raises(ValueError, match="exceeds the context"):
+        eng.generate([[1] * 200], GenParams.greedy(2))
+    slot = eng.alloc()
+    with pytest.raises(StepError, match="outside the vocabulary"):
+        eng.step([SequenceStep(slot, [1, 256], [0])])
+    with pytest.raises(StepError, match="not allocated"):
+        eng.step([SequenceStep(slot + 1, [1], [0])])
+    with pytest.raises(StepError, match="twice"):
+        eng.step([SequenceStep(slot, [1], [0]), SequenceStep(slot, [2], [0])])
+    eng.step([SequenceStep(slot, [1] * 100, [])])
+    other = eng.alloc()
+    with pytest.raises(CacheFull):
+        eng.step([SequenceStep(other, [1] * 100, [])])       # 128 tokens of cache: two pages, both taken
+    eng.free(slot)
+    eng.step([SequenceStep(other, [1] * 100, [99])])
+    eng.free(other)
+    eng.cache.check()

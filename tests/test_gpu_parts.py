@@ -1,0 +1,309 @@
+"""Each part alone against the plain implementation, and the generality of the parts: a toy
+architecture, defined here, with a mixer that keeps state of its own, a windowed mixer, a
+layer without feed-forward, a layer that runs twice and an entry that reads another
+entry's cache.  Nothing in the package is changed for it."""
+import math
+from dataclasses import asdict, dataclass
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as pl
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+TOL = {torch.float32: 2e-4, torch.bfloat16: 5e-2}
+
+
+def _rt(dtype):
+    from oracle_engine_b200.engine.runtime import Runtime
+    return Runtime(dtype, DEV)
+
+
+def _weights(part, seed):
+    from oracle_engine_b200.weights.random_init import RandomSource
+    src = RandomSource(part.tensors(), seed, torch.bfloat16, "cpu", std=0.08)
+    w = {n: src.read(n) for n in src.names()}
+    part.load(lambda n: w[n].to(DEV))
+    return {n: t.double() for n, t in w.items()}
+
+
+def _step(cache, seqs):
+    """Uploads a step for `seqs` [(slot, n_new_tokens)] and returns (ctx, view of entry 0)."""
+    from oracle_engine_b200.cache.kv_cache import CacheView
+    from oracle_engine_b200.engine.batch import SequenceStep, StepBuffers, build_plan
+    steps = [SequenceStep(s, [0] * n, []) for s, n in seqs]
+    starts = [cache.length(s) for s, _ in seqs]
+    for (s, n), st in zip(seqs, starts):
+        cache.reserve(s, st + n)
+    plan = build_plan(steps, starts)
+    buf = StepBuffers(plan.n_tokens, plan.n_seqs, 0, [(plan.n_seqs, cache.max_pages_per_seq)] * len(cache.groups), DEV)
+    ctx = buf.upload(plan, [cache.tables_for(g.index, plan.seq_slot) for g in cache.groups])
+    for (s, n), st in zip(seqs, starts):
+        cache.commit(s, st + n)
+    return ctx, CacheView(cache.storage_of(0), ctx.tables[0], 0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_positions_feedforward_embedding_alone(dtype):
+    from oracle_engine_b200.parts.registry import EMBEDDINGS, FEED_FORWARDS, HEADS, NORMS, POSITIONS
+    rt = _rt(dtype)
+    g = torch.Generator().manual_seed(0)
+    x = (torch.randn(7, 72, generator=g) * 2).to(DEV)
+
+    norm = NORMS.get("rms_norm")({"size": 72, "eps": 3e-4, "name": "n.weight"}, "p.", rt)
+    w = _weights(norm, 1)
+    assert [d.name for d in norm.tensors()] == ["p.n.weight"]
+    want = pl.rms_norm(x.double().cpu(), w["p.n.weight"], 3e-4)
+    assert (norm.forward(x).double().cpu() - want).abs().max() < TOL[dtype] * 4
+
+    sc = {"rope_type": "llama3", "factor": 4.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+          "original_max_position_embeddings": 32}
+    rope = POSITIONS.get("rotary")({"head_dim": 24, "theta": 5000.0, "scaling": sc, "max_positions": 90}, "", rt)
+    cos, sin = rope.tables()
+    ang = torch.arange(90, dtype=torch.float64)[:, None] * pl.rope_inv_freq(24, 5000.0, sc)[None]
+    assert cos.shape == (90, 12) and (cos.double().cpu() - torch.cos(ang)).abs().max() < 1e-6
+    assert (sin.double().cpu() - torch.sin(ang)).abs().max() < 1e-6
+    assert POSITIONS.get("none")({}, "", rt).tables() == (None, None)
+
+    ffn = FEED_FORWARDS.get("swiglu")({"hidden_size": 72, "intermediate_size": 200}, "l.", rt)
+    w = _weights(ffn, 2)
+    h = x.to(dtype)
+    res = torch.ones(7, 72, device=DEV)
+    ffn.forward(h, res, None)
+    want = 1.0 + pl.swiglu_ffn(h.double().cpu(), w["l.mlp.gate_proj.weight"], w["l.mlp.up_proj.weight"],
+                               w["l.mlp.down_proj.weight"])
+    assert (res.double().cpu() - want).abs().max() < TOL[dtype] * 4
+
+    emb = EMBEDDINGS.get("token_embedding")({"vocab_size": 50, "hidden_size": 72, "name": "e.weight"}, "", rt)
+    w = _weights(emb, 3)
+    ids = torch.tensor([3, 49, 0, 3], dtype=torch.int32, device=DEV)
+    assert torch.equal(emb.forward(ids, 4).double().cpu(), w["e.weight"][ids.long().cpu()])
+    for tied in (True, False):
+        head = HEADS.get("lm_head")({"vocab_size": 50, "hidden_size": 72, "tied": tied, "name": "h.weight",
+                                     "embedding": emb}, "", rt)
+        hw = _weights(head, 4)
+        table = w["e.weight"] if tied else hw["h.weight"]
+        assert len(head.tensors()) == (0 if tied else 1)
+        logits = head.forward(h)
+        assert logits.dtype == torch.float32
+        assert (logits.double().cpu() - h.double().cpu() @ table.T).abs().max() < TOL[dtype] * 4
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window,rotary", [(0, True), (20, False)])
+def test_attention_mixer_alone(dtype, window, rotary):
+    """The mixer over its own cache: two sequences, a prompt step and then single tokens."""
+    from oracle_engine_b200.cache.kv_cache import KVCache
+    from oracle_engine_b200.parts.registry import MIXERS, POSITIONS
+    rt = _rt(dtype)
+    D, H, KVH, hd = 48, 6, 2, 16
+    rope = POSITIONS.get("rotary")({"head_dim": hd, "theta": 10000.0, "scaling": None, "max_positions": 256}, "", rt)
+    mixer = MIXERS.get("gqa_attention")({"hidden_size": D, "num_heads": H, "num_kv_heads": KVH, "head_dim": hd,
+                                         "position": rope if rotary else None, "window": window}, "m.", rt)
+    w = _weights(mixer, 5)
+    need = mixer.cache_need()
+    assert need.kind == ("window" if window else "full") and need.kv_heads == KVH and need.head_dim == hd
+    cache = KVCache([need], 512, 256, dtype, DEV)
+    lens = [70, 9]
+    g = torch.Generator().manual_seed(6)
+    xs = [torch.randn(n, D, generator=g).to(dtype) for n in lens]
+    slots = [cache.alloc_slot() for _ in lens]
+    outs = [torch.zeros(n, D) for n in lens]
+    # step 1: all but the last 3 tokens of each; then 3 steps of one token each
+    cuts = [[(0, n - 3)] + [(n - 3 + i, n - 2 + i) for i in range(3)] for n in lens]
+    for step in range(4):
+        ctx, view = _step(cache, [(s, c[step][1] - c[step][0]) for s, c in zip(slots, cuts)])
+        h = torch.cat([x[c[step][0]:c[step][1]] for x, c in zip(xs, cuts)]).to(DEV)
+        res = torch.zeros(h.shape[0], D, device=DEV)
+        mixer.forward(h, res, ctx, view, {}, True)
+        row = 0
+        for b, c in enumerate(cuts):
+            n = c[step][1] - c[step][0]
+            outs[b][c[step][0]:c[step][1]] = res[row:row + n].cpu()
+            row += n
+    inv = pl.rope_inv_freq(hd, 10000.0, None)
+    for b, n in enumerate(lens):
+        x = xs[b].double()
+        q = (x @ w["m.self_attn.q_proj.weight"].T).reshape(n, H, hd)
+        k = (x @ w["m.self_attn.k_proj.weight"].T).reshape(n, KVH, hd)
+        v = (x @ w["m.self_attn.v_proj.weight"].T).reshape(n, KVH, hd)
+        if rotary:
+            q, k = pl.rope_rotate(q, torch.arange(n), inv), pl.rope_rotate(k, torch.arange(n), inv)
+        want = pl.causal_attention(q, k, v, window or None) @ w["m.self_attn.o_proj.weight"].T
+        assert (outs[b].double() - want).abs().max() < TOL[dtype], f"sequence {b}"
+    cache.check()
+
+
+# ------------------------------------------------------------------------------------------
+# a toy architecture, registered from here
+# ------------------------------------------------------------------------------------------
+
+@dataclass(frozen=True)
+class ToyConfig:
+    architecture: str = "ToyForCausalLM"
+    vocab_size: int = 61
+    hidden_size: int = 32
+    max_position_embeddings: int = 192
+    decay: float = 0.5
+
+    @staticmethod
+    def from_dict(raw):
+        return ToyConfig(raw["architectures"][0], raw["vocab_size"], raw["hidden_size"],
+                         raw["max_position_embeddings"], raw["decay"])
+
+    def to_dict(self):
+        d = asdict(self)
+        d["architectures"] = [d.pop("architecture")]
+        return d
+
+
+def _toy_spec(cfg, max_positions=None):
+    from oracle_engine_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    D = cfg.hidden_size
+    max_pos = min(max_positions or cfg.max_position_embeddings, cfg.max_position_embeddings)
+    norm = lambda name: PartSpec("rms_norm", {"size": D, "eps": 1e-5, "name": name})         # noqa: E731
+    attn = lambda **kw: PartSpec("gqa_attention", {"hidden_size": D, "num_heads": 2, "num_kv_heads": 1,  # noqa: E731
+                                                   "head_dim": 16, **kw})
+    ffn = PartSpec("swiglu", {"hidden_size": D, "intermediate_size": 40})
+    layers = (
+        LayerSpec("t.0.", attn(position="rope", window=0), ffn, norm("n1.weight"), norm("n2.weight")),
+        LayerSpec("t.1.", PartSpec("toy_ema", {"hidden_size": D, "decay": cfg.decay}), None, norm("n1.weight"), None),
+        LayerSpec("t.2.", attn(position=None, window=20), ffn, norm("n1.weight"), norm("n2.weight")),
+        LayerSpec("t.3.", attn(position="rope", window=0), None, norm("n1.weight"), None),
+    )
+    # layer 0 runs twice (entries 0 and 3, each with its own cache); entry 4 reads entry 0's cache
+    schedule = (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2), ScheduleEntry(0), ScheduleEntry(3, cache_from=0))
+    return ModelSpec(
+        architecture=cfg.architecture, hidden_size=D, vocab_size=cfg.vocab_size, max_positions=max_pos,
+        embedding=PartSpec("token_embedding", {"vocab_size": cfg.vocab_size, "hidden_size": D, "name": "emb.weight"}),
+        final_norm=norm("final.weight"),
+        head=PartSpec("lm_head", {"vocab_size": cfg.vocab_size, "hidden_size": D, "tied": False, "name": "out.weight"}),
+        positions={"rope": PartSpec("rotary", {"head_dim": 16, "theta": 100.0, "scaling": None,
+                                               "max_positions": max_pos})},
+        layers=layers, schedule=schedule)
+
+
+@pytest.fixture(scope="module")
+def toy_registered():
+    from oracle_engine_b200.config.base import ARCHITECTURES, register_architecture
+    from oracle_engine_b200.parts.registry import MIXERS, Part
+    from oracle_engine_b200.parts.spec import StateNeed, TensorDecl
+
+    @MIXERS.register("toy_ema")
+    class ToyEMA(Part):
+        """y_t = W x_t + s_{t-1};  s_t = decay * s_{t-1} + x_t, with s a per-sequence state."""
+        graph_safe = False
+
+        def tensors(self):
+            D = self.params["hidden_size"]
+            return [TensorDecl(self.prefix + "toy.weight", (D, D))]
+
+        def load(self, get):
+            self.w = get(self.prefix + "toy.weight").float()
+
+        def state_need(self):
+            return {"s": StateNeed((self.params["hidden_size"],), torch.float32)}
+
+        def forward(self, h, residual, ctx, cache, state, owns_cache=True):
+            s = state["s"]
+            cu, slots = ctx.cu_q.tolist(), ctx.seq_slot.tolist()
+            for b, slot in enumerate(slots):
+                for t in range(cu[b], cu[b + 1]):
+                    x = h[t].float()
+                    residual[t] += self.w @ x + s[slot]
+                    s[slot] = self.params["decay"] * s[slot] + x
+
+    register_architecture("ToyForCausalLM", ToyConfig, _toy_spec)
+    yield
+    MIXERS.unregister("toy_ema")
+    ARCHITECTURES.pop("ToyForCausalLM", None)
+
+
+def _toy_plain(w, cfg, tokens):
+    """Whole sequence, no cache: the toy model's logits at every position."""
+    D, n = cfg.hidden_size, len(tokens)
+    inv = pl.rope_inv_freq(16, 100.0, None)
+    pos = torch.arange(n)
+    x = w["emb.weight"][torch.tensor(tokens)]
+
+    def attn(p, h, rotary, window, kv=None):
+        q = (h @ w[p + "self_attn.q_proj.weight"].T).reshape(n, 2, 16)
+        if rotary:
+            q = pl.rope_rotate(q, pos, inv)
+        if kv is None:
+            k = (h @ w[p + "self_attn.k_proj.weight"].T).reshape(n, 1, 16)
+            v = (h @ w[p + "self_attn.v_proj.weight"].T).reshape(n, 1, 16)
+            if rotary:
+                k = pl.rope_rotate(k, pos, inv)
+            kv = (k, v)
+        return pl.causal_attention(q, kv[0], kv[1], window) @ w[p + "self_attn.o_proj.weight"].T, kv
+
+    def ffn(p, h):
+        return pl.swiglu_ffn(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+
+    kv0 = None
+    for entry, (p, kind) in enumerate([("t.0.", "a"), ("t.1.", "toy"), ("t.2.", "w"), ("t.0.", "a"), ("t.3.", "share")]):
+        h = pl.rms_norm(x, w[p + "n1.weight"], 1e-5)
+        if kind == "toy":
+            s = torch.zeros(D, dtype=x.dtype)
+            y = torch.zeros_like(x)
+            for t in range(n):
+                y[t] = w[p + "toy.weight"] @ h[t] + s
+                s = cfg.decay * s + h[t]
+            x = x + y
+            continue
+        if kind == "share":
+            o, _ = attn(p, h, True, None, kv0)
+        else:
+            o, kv = attn(p, h, kind == "a", 20 if kind == "w" else None)
+            if entry == 0:
+                kv0 = kv
+        x = x + o
+        if kind != "share":
+            x = x + ffn(p, pl.rms_norm(x, w[p + "n2.weight"], 1e-5))
+    return pl.rms_norm(x, w["final.weight"], 1e-5) @ w["out.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_with_state_window_repeat_and_shared_cache(toy_registered, tmp_path, dtype):
+    import json
+    import helpers
+    from oracle_engine_b200 import write_model_folder
+    from oracle_engine_b200.engine.engine import Engine
+    cfg = ToyConfig()
+    write_model_folder(tmp_path / "toy", cfg, seed=11, std=0.15)
+    assert json.loads((tmp_path / "toy" / "config.json").read_text())["architectures"] == ["ToyForCausalLM"]
+    eng = Engine.from_pretrained(str(tmp_path / "toy"), dtype=dtype, max_tokens=448)
+    # cache groups: the full-attention entries (0, 3) share one, the windowed entry (2) has its own;
+    # entries 1 (state only) and 4 (reads entry 0) own none
+    assert [g.entries for g in eng.cache.groups] == [[0, 3], [2]]
+    assert [g.need.kind for g in eng.cache.groups] == ["full", "window"]
+    assert not eng.stepper.use_graphs                       # the toy mixer is not graph safe
+    w = pl.read_safetensors(tmp_path / "toy" / "model.safetensors")
+    requests = [helpers.random_tokens(n, cfg.vocab_size, 70 + i) for i, n in enumerate([1, 30, 150, 65, 90])]
+    runs = {"whole": helpers.whole_steps(requests), "tail": helpers.tail_steps(requests, 32),
+            "batched": helpers.batched_steps(requests, [1, 10, 100, 64, 33], 2)}
+    got = {}
+    for name, steps in runs.items():
+        out = helpers.TraceRunner(eng, tmp_path / name).run(steps)
+        got[name] = helpers.collect(steps, out, requests)
+        eng.cache.check()
+        assert eng.cache.slots.n_free == eng.cache.n_slots
+    tol = 2e-4 if dtype == "float32" else 6e-2
+    for i, toks in enumerate(requests):
+        want = _toy_plain(w, cfg, toks).numpy()
+        for name in runs:
+            err = np.abs(got[name][i] - want).max()
+            assert err < tol, f"{name} request {i}: {err}"
+    # the window group gives pages back as the sequence moves on; the full group keeps all
+    from oracle_engine_b200 import SequenceStep
+    slot = eng.alloc()
+    eng.step([SequenceStep(slot, requests[2], [])])
+    eng.step([SequenceStep(slot, [1], [0])])
+    full, win = eng.cache.groups
+    assert win.tables[slot][:2].tolist() == [-1, -1] and win.tables[slot][2] >= 0
+    assert (full.tables[slot][:3] >= 0).all()
+    eng.free(slot)
+    eng.cache.check()

@@ -171,3 +171,28 @@ def test_refusals(model_dirs):
     eng.step([SequenceStep(other, [1] * 100, [99])])
     eng.free(other)
     eng.cache.check()
+
+
+def test_command_line_generates_the_same_tokens(model_dirs, plain_models, tmp_path):
+    """bin/oracle with token ids: greedy tokens of a batch, and seeded random weights from a config."""
+    import json
+    import subprocess
+    import sys
+    exe = [sys.executable, str(helpers.ROOT / "bin" / "oracle")]
+    plain = plain_models["A"]
+    prompts = [[3, 4, 5, 6], [9, 8]]
+    r = subprocess.run(exe + ["-m", model_dirs["A"], "--tokens", "3,4,5,6", "--tokens", "9,8", "-n", "6", "--temp", "0",
+                              "--dtype", "float32", "--ignore-eos"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    got = [[int(t) for t in line.split()] for line in r.stdout.strip().splitlines()]
+    assert got == [pl.generate(plain, p, 6) for p in prompts]
+    # streaming a single request prints the ids as they come
+    r = subprocess.run(exe + ["-m", model_dirs["A"], "--tokens", "3,4,5,6", "-n", "6", "--temp", "0", "--dtype", "float32",
+                              "--ignore-eos"], capture_output=True, text=True)
+    assert r.returncode == 0 and [int(t) for t in r.stdout.split()] == got[0]
+    cfg = tmp_path / "c.json"
+    cfg.write_text((helpers.Path(model_dirs["A"]) / "config.json").read_text())
+    r = subprocess.run(exe + ["--random-weights", "0", "--config", str(cfg), "--tokens", "3,4,5,6", "-n", "6", "--temp", "0",
+                              "--dtype", "float32", "--ignore-eos", "--no-stream"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    assert [int(t) for t in r.stdout.split()] == got[0]          # seed 0 is the seed the folder was written with

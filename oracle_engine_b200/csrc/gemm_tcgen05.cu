@@ -136,7 +136,7 @@ struct GemmArgs {
     int n_tile;                 // rows of the B tile, multiple of 16, <= 256
     int stages;
     int swap;                   // 1: C[b_row, a_row] (A = weights); 0: C[a_row, b_row] (A = activations)
-    int out_kind;               // 0 bf16 store, 1 float32 store, 2 float32 accumulate
+    int out_kind;               // 0 bf16 store, 1 float32 store, 2 float32 accumulate, 3 bf16 silu(gate)*up
     int splits;
     float* workspace;           // [splits][tiles_a][tiles_b][n_tile][128] float32 when splits > 1
     int* counters;              // [tiles_a * tiles_b], zero between launches
@@ -146,6 +146,82 @@ __device__ __forceinline__ void store_out(const GemmArgs& g, long long idx, floa
     if (g.out_kind == 0) ((bf16*)g.C)[idx] = __float2bfloat16_rn(v);
     else if (g.out_kind == 1) ((float*)g.C)[idx] = v;
     else ((float*)g.C)[idx] += v;
+}
+
+__device__ __forceinline__ float silu_mul(float gate, float up) { return (gate / (1.f + expf(-gate))) * up; }
+
+// Stores NC consecutive B-rows (b_row0 ..) of A-row `a_row` of the output tile.  Called by all
+// 32 lanes of a warp together (out_kind 3 exchanges values between neighbouring lanes).
+// out_kind 3: rows of the weight matrix alternate gate, up (g0, u0, g1, u1, ...); the output
+// is silu(gate) * up as bf16, half as many features.
+template <int NC>
+__device__ __forceinline__ void emit(const GemmArgs& g, int a_row, int b_row0, const float (&v)[NC]) {
+    const bool a_ok = a_row < g.rows_a;
+    if (g.swap) {
+        if (g.out_kind == 3) {
+#pragma unroll
+            for (int j = 0; j < NC; j++) {
+                const float other = __shfl_xor_sync(0xffffffffu, v[j], 1);
+                const int b_row = b_row0 + j;
+                if (a_ok && !(a_row & 1) && b_row < g.rows_b)
+                    ((bf16*)g.C)[(long long)b_row * g.ldc + (a_row >> 1)] = __float2bfloat16_rn(silu_mul(v[j], other));
+            }
+        } else if (a_ok) {
+#pragma unroll
+            for (int j = 0; j < NC; j++) {
+                const int b_row = b_row0 + j;
+                if (b_row < g.rows_b) store_out(g, (long long)b_row * g.ldc + a_row, v[j]);
+            }
+        }
+        return;
+    }
+    if (!a_ok) return;
+    const bool full = b_row0 + NC <= g.rows_b;
+    if (g.out_kind == 3) {
+        const long long base = (long long)a_row * g.ldc + (b_row0 >> 1);
+        if (full && NC == 16 && (base & 7) == 0) {
+            uint32_t p[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(silu_mul(v[4 * j], v[4 * j + 1]), silu_mul(v[4 * j + 2], v[4 * j + 3]));
+                p[j] = *(uint32_t*)&h;
+            }
+            *(uint4*)((bf16*)g.C + base) = make_uint4(p[0], p[1], p[2], p[3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < NC / 2; j++)
+                if (b_row0 + 2 * j + 1 < g.rows_b) ((bf16*)g.C)[base + j] = __float2bfloat16_rn(silu_mul(v[2 * j], v[2 * j + 1]));
+        }
+        return;
+    }
+    const long long base = (long long)a_row * g.ldc + b_row0;
+    if (full && g.out_kind == 0 && (base & 7) == 0) {
+#pragma unroll
+        for (int q = 0; q < NC / 8; q++) {
+            uint32_t p[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * q + 2 * j], v[8 * q + 2 * j + 1]);
+                p[j] = *(uint32_t*)&h;
+            }
+            *(uint4*)((bf16*)g.C + base + 8 * q) = make_uint4(p[0], p[1], p[2], p[3]);
+        }
+    } else if (full && g.out_kind != 0 && (base & 3) == 0) {
+        float4* dst = (float4*)((float*)g.C + base);
+#pragma unroll
+        for (int j = 0; j < NC / 4; j++) {
+            float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            if (g.out_kind == 2) {
+                const float4 old = dst[j];
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+            }
+            dst[j] = o;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < NC; j++)
+            if (b_row0 + j < g.rows_b) store_out(g, base + j, v[j]);
+    }
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -234,58 +310,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (ok) {
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
             const int tiles_a = gridDim.x, tiles_b = gridDim.y;
-            float* part = g.splits > 1
-                ? g.workspace + ((((size_t)split * tiles_a + tile_a) * tiles_b + tile_b) * (size_t)g.n_tile) * BLOCK_M
-                : nullptr;
+            const size_t tile_off = (((size_t)tile_a * tiles_b + tile_b) * (size_t)g.n_tile) * BLOCK_M + row;
+            const size_t split_stride = (size_t)tiles_a * tiles_b * g.n_tile * BLOCK_M;
             for (int c0 = 0; c0 < g.n_tile; c0 += 16) {
-                uint32_t v[16];
+                float v[16];
                 if (n_kb > 0) {
-                    tmem_ld16(taddr + (uint32_t)c0, v);
+                    uint32_t r[16];
+                    tmem_ld16(taddr + (uint32_t)c0, r);
+#pragma unroll
+                    for (int j = 0; j < 16; j++) v[j] = __uint_as_float(r[j]);
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 16; j++) v[j] = 0u;
+                    for (int j = 0; j < 16; j++) v[j] = 0.f;
                 }
                 if (g.splits > 1) {
+                    float* part = g.workspace + (size_t)split * split_stride + tile_off + (size_t)c0 * BLOCK_M;
 #pragma unroll
-                    for (int j = 0; j < 16; j++) part[(size_t)(c0 + j) * BLOCK_M + row] = __uint_as_float(v[j]);
-                } else if (a_row < g.rows_a) {
-                    if (g.swap) {
-#pragma unroll
-                        for (int j = 0; j < 16; j++) {
-                            const int b_row = tile_b * g.n_tile + c0 + j;
-                            if (b_row < g.rows_b) store_out(g, (long long)b_row * g.ldc + a_row, __uint_as_float(v[j]));
-                        }
-                    } else {
-                        const int b_row0 = tile_b * g.n_tile + c0;
-                        const long long base = (long long)a_row * g.ldc + b_row0;
-                        if (b_row0 + 16 <= g.rows_b && g.out_kind == 0 && (base & 7) == 0) {
-                            uint32_t p[8];
-#pragma unroll
-                            for (int j = 0; j < 8; j++) {
-                                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
-                                p[j] = *(uint32_t*)&h;
-                            }
-                            uint4* dst = (uint4*)((bf16*)g.C + base);
-                            dst[0] = make_uint4(p[0], p[1], p[2], p[3]);
-                            dst[1] = make_uint4(p[4], p[5], p[6], p[7]);
-                        } else if (b_row0 + 16 <= g.rows_b && g.out_kind != 0 && (base & 3) == 0) {
-                            float4* dst = (float4*)((float*)g.C + base);
-#pragma unroll
-                            for (int j = 0; j < 4; j++) {
-                                float4 o = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                                       __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-                                if (g.out_kind == 2) {
-                                    const float4 old = dst[j];
-                                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                                }
-                                dst[j] = o;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 16; j++)
-                                if (b_row0 + j < g.rows_b) store_out(g, base + j, __uint_as_float(v[j]));
-                        }
-                    }
+                    for (int j = 0; j < 16; j++) part[(size_t)j * BLOCK_M] = v[j];
+                } else {
+                    emit<16>(g, a_row, tile_b * g.n_tile + c0, v);
                 }
             }
             if (g.splits > 1) {
@@ -300,16 +343,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (*(volatile int*)&ctl->is_last) {
                     __threadfence();
-                    if (a_row < g.rows_a) {
-                        for (int c = 0; c < g.n_tile; c++) {
-                            const int b_row = tile_b * g.n_tile + c;
-                            if (b_row >= g.rows_b) break;
-                            float sum = 0.f;
-                            for (int s = 0; s < g.splits; s++)
-                                sum += __ldcg(g.workspace + ((((size_t)s * tiles_a + tile_a) * tiles_b + tile_b) * (size_t)g.n_tile + c) * BLOCK_M + row);
-                            const long long idx = g.swap ? (long long)b_row * g.ldc + a_row : (long long)a_row * g.ldc + b_row;
-                            store_out(g, idx, sum);
+                    for (int c0 = 0; c0 < g.n_tile; c0 += 8) {
+                        if (tile_b * g.n_tile + c0 >= g.rows_b) break;
+                        float acc[8];
+#pragma unroll
+                        for (int u = 0; u < 8; u++) acc[u] = 0.f;
+                        const float* src = g.workspace + tile_off + (size_t)c0 * BLOCK_M;
+#pragma unroll 4
+                        for (int sp = 0; sp < g.splits; sp++) {
+                            float t[8];
+#pragma unroll
+                            for (int u = 0; u < 8; u++) t[u] = __ldcg(src + (size_t)sp * split_stride + (size_t)u * BLOCK_M);
+#pragma unroll
+                            for (int u = 0; u < 8; u++) acc[u] += t[u];
                         }
+                        emit<8>(g, a_row, tile_b * g.n_tile + c0, acc);
                     }
                     if (warp == 2 && lane == 0) g.counters[tile_id] = 0;
                 }
@@ -378,12 +426,14 @@ int oe_gemm_tc_supported(const void* A, const void* W, int M, int N, int K, long
 long long oe_gemm_tc_workspace_bytes() { return 64ll << 20; }
 int oe_gemm_tc_counters() { return 4096; }
 
-// C[M,N] (+)= A[M,K] . W[N,K]^T ; out_kind: 0 bf16, 1 float32, 2 float32 accumulate.
+// C[M,N] (+)= A[M,K] . W[N,K]^T ; out_kind: 0 bf16, 1 float32, 2 float32 accumulate,
+// 3: W's rows alternate gate/up and C[M,N/2] = silu(gate) * up as bf16 (ldc counts C's elements).
 // workspace: float32 scratch of ws_bytes bytes, counters: n_counters zeroed ints (both may be null: no split).
 int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, long long lda, long long ldc,
                     int out_kind, float* workspace, long long ws_bytes, int* counters, int n_counters,
                     int sm_count, cudaStream_t st) {
     if (!oe_gemm_tc_supported(A, W, M, N, K, lda)) return OE_ERR_UNSUPPORTED;
+    if (out_kind < 0 || out_kind > 3 || (out_kind == 3 && (N & 1))) return OE_ERR_UNSUPPORTED;
     int rc = get_encode();
     if (rc) return rc;
     GemmArgs g;
@@ -400,7 +450,7 @@ int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, 
         const int tiles_a = (N + BLOCK_M - 1) / BLOCK_M;
         int splits = 1;
         if (workspace && counters && tiles_a <= n_counters) {
-            splits = (sm_count + tiles_a - 1) / tiles_a;
+            splits = sm_count / tiles_a;                      // one wave of CTAs
             if (splits > n_kb / 4) splits = n_kb / 4;
             if (splits < 1) splits = 1;
             const long long need = (long long)splits * tiles_a * g.n_tile * BLOCK_M * 4;

@@ -57,15 +57,23 @@ def gemm_supported(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.stride(1) == 1)
 
 
-def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool = False, split_k: bool = True) -> None:
-    """out (+)= a @ w.T, a [M, K] and w [N, K] bfloat16; out bfloat16 or float32 [M, N]."""
+def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool = False, split_k: bool = True,
+         swiglu: bool = False) -> None:
+    """out (+)= a @ w.T, a [M, K] and w [N, K] bfloat16; out bfloat16 or float32 [M, N].
+
+    swiglu: w's rows alternate gate and up rows (g0, u0, g1, u1, ...) and out [M, N/2]
+    bfloat16 receives silu(gate) * up, computed in float32 in the epilogue."""
     M, K = a.shape
     N = w.shape[0]
-    if w.shape[1] != K or out.shape != (M, N):
+    if w.shape[1] != K or out.shape != (M, N // 2 if swiglu else N):
         raise KernelError(f"gemm: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not agree")
     if not gemm_supported(a, w, out):
         raise KernelError("gemm: the tensor-core kernel needs bfloat16 operands with 16-byte aligned rows")
-    if accumulate:
+    if swiglu:
+        if out.dtype != torch.bfloat16 or accumulate or N % 2:
+            raise KernelError("gemm: the swiglu epilogue writes bfloat16 and needs an even number of weight rows")
+        kind = 3
+    elif accumulate:
         if out.dtype != torch.float32:
             raise KernelError("gemm: accumulate needs a float32 output")
         kind = 2

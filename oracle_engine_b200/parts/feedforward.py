@@ -31,13 +31,24 @@ class SwiGLU(Part):
 
     def load(self, get):
         to = self.rt.to_compute
-        self.w_gu = torch.cat([to(get(self.names["gate"])), to(get(self.names["up"]))], 0)
+        gate, up = to(get(self.names["gate"])), to(get(self.names["up"]))
+        # On the tensor-core path the activation is fused into the product's epilogue, which
+        # wants gate and up rows of a feature side by side: rows g0, u0, g1, u1, ...
+        self.fused = self.rt.dtype == torch.bfloat16 and self.rt.tensor_cores and self.D % 8 == 0
+        if self.fused:
+            self.w_gu = torch.stack([gate, up], 1).reshape(2 * self.FF, self.D).contiguous()
+        else:
+            self.w_gu = torch.cat([gate, up], 0)
         self.w_down = to(get(self.names["down"]))
 
     def forward(self, h, residual, ctx):
         T = h.shape[0]
-        gu = self.rt.empty(T, 2 * self.FF)
-        matmul_nt(self.rt, gu, h, self.w_gu)
         a = self.rt.empty(T, self.FF)
-        ops.swiglu(a, gu)
+        if self.fused:
+            from ..csrc import ops_tc
+            ops_tc.gemm(a, h, self.w_gu, swiglu=True)
+        else:
+            gu = self.rt.empty(T, 2 * self.FF)
+            matmul_nt(self.rt, gu, h, self.w_gu)
+            ops.swiglu(a, gu)
         matmul_nt(self.rt, residual, a, self.w_down, accumulate=True)

@@ -108,6 +108,13 @@ def test_gemm_tcgen05(M, N, K):
     again = torch.empty(M, N, device=DEV)
     ops_tc.gemm(again, a, w)
     assert torch.equal(again, out32)                     # split sums are added in a fixed order
+    if N % 2 == 0:
+        # fused activation: weight rows alternate gate, up
+        act = torch.full((M, N // 2), 9.0, dtype=torch.bfloat16, device=DEV)
+        ops_tc.gemm(act, a, w, swiglu=True)
+        gate, up = want[:, 0::2], want[:, 1::2]
+        ref = gate / (1 + torch.exp(-gate)) * up
+        assert (act.double() - ref).abs().max() < 0.005 * ref.abs().max() + 10 * tol
     assert ops_tc.device_error() == 0
     assert not ops_tc.gemm_supported(a[:, :K - 1], w[:, :K - 1].contiguous(), out32)      # rows not 16-byte aligned
 

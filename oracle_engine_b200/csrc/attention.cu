@@ -25,6 +25,8 @@ attn_paged_kernel(T* __restrict__ out, const T* __restrict__ q, int q_stride,
                   int n_tokens, int H, int KVH, int hd, int window, float scale) {
     extern __shared__ float qs_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+    pdl_wait();
     const long long item = (long long)blockIdx.x * WARPS + warp;
     if (item >= (long long)n_tokens * H) return;
     const int t = (int)(item / H), h = (int)(item % H);
@@ -99,9 +101,9 @@ int launch(T* out, const T* q, int q_stride, const T* cache, const int* tables, 
     const long long items = (long long)n_tokens * H;
     const long long blocks = (items + WARPS - 1) / WARPS;
     if (blocks > 2147483647LL) return OE_ERR_UNSUPPORTED;
-    attn_paged_kernel<T><<<(unsigned)blocks, WARPS * 32, WARPS * hd * sizeof(float), st>>>(
+    const int launch_rc = oe_launch(attn_paged_kernel<T>, dim3((unsigned)blocks), dim3(WARPS * 32), WARPS * hd * sizeof(float), st, 
         out, q, q_stride, cache, tables, max_pages, tok_seq, tok_pos, n_tokens, H, KVH, hd, window, scale);
-    return (int)cudaGetLastError();
+    return launch_rc;
 }
 
 }  // namespace

@@ -87,6 +87,8 @@ template <int NWARPS>
 __global__ void __launch_bounds__(NWARPS * 32)
 attn_mma_kernel(const AttnArgs a) {
     extern __shared__ __align__(16) uint8_t smem[];
+    pdl_launch_dependents();
+    pdl_wait();
     const int b = blockIdx.z, kvh = blockIdx.y;
     const int qlen = a.seq_qlen[b];
     if (qlen <= 0) return;
@@ -273,6 +275,8 @@ attn_mma_kernel(const AttnArgs a) {
 // out[row, head] = sum_s o_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), splits taken in order.
 __global__ void attn_merge_kernel(bf16* __restrict__ out, const float* __restrict__ partial,
                                   const int* __restrict__ tok_seq, int H, int n_splits) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x, h = blockIdx.y;
     bf16* o = out + ((size_t)t * H + h) * HD;
     if (tok_seq[t] < 0) {
@@ -308,8 +312,8 @@ int launch(const AttnArgs& a, int n_seqs, int grid_x, cudaStream_t st) {
         attr_set = true;
     }
     dim3 grid(grid_x, a.KVH, n_seqs);
-    attn_mma_kernel<NWARPS><<<grid, NWARPS * 32, smem, st>>>(a);
-    return (int)cudaGetLastError();
+    const int launch_rc = oe_launch(attn_mma_kernel<NWARPS>, dim3(grid), dim3(NWARPS * 32), smem, st, a);
+    return launch_rc;
 }
 
 }  // namespace
@@ -353,8 +357,8 @@ int oe_attn_mma_bf16(bf16* out, const bf16* q, long long q_stride, const bf16* c
     else rc = launch<4>(a, n_seqs, grid_x, st);
     if (rc) return rc;
     if (a.n_splits > 1) {
-        attn_merge_kernel<<<dim3(n_tokens, H), HD >= 128 ? 128 : 64, 0, st>>>(out, partial, tok_seq, H, a.n_splits);
-        rc = (int)cudaGetLastError();
+        const int launch_rc = oe_launch(attn_merge_kernel, dim3(n_tokens, H), dim3(HD >= 128 ? 128 : 64), 0, st, out, partial, tok_seq, H, a.n_splits);
+        rc = launch_rc;
     }
     return rc;
 }

@@ -8,11 +8,61 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define OE_ERR_UNSUPPORTED 100001   // size or option outside what the kernel takes
 #define OE_PAGE 64                  // tokens per cache page
 
 typedef __nv_bfloat16 bf16;
+
+// ---------------------------------------------------------------------------------------
+// Programmatic dependent launch.  Every kernel of this library is launched with the
+// programmatic-stream-serialization attribute: it may start while the kernel before it in
+// the stream is still draining, does whatever does not depend on that kernel (set-up,
+// prefetch of weights), and calls pdl_wait() before it first touches memory that an
+// earlier kernel of the stream may have written (or may still read, for buffers it
+// overwrites).  pdl_wait() returns when every earlier kernel has completed and its
+// writes are visible.  Every kernel calls it, so completion is transitive along the
+// stream.  pdl_launch_dependents() lets the next kernel be scheduled early.
+// Set OE_PDL=0 in the environment to launch without the attribute.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#ifndef __CUDA_ARCH__
+static inline int oe_pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("OE_PDL");
+        v = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return v;
+}
+#endif
+
+template <typename... KArgs, typename... Args>
+static inline int oe_launch_ex(bool early, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                               Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+#ifndef __CUDA_ARCH__
+    attr[0].val.programmaticStreamSerializationAllowed = early ? oe_pdl_enabled() : 0;
+#endif
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// early = true: the kernel may start before the one before it has finished (see above).
+template <typename... KArgs, typename... Args>
+static inline int oe_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    return oe_launch_ex(true, kernel, grid, block, smem, st, args...);
+}
 
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }

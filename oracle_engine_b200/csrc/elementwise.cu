@@ -15,6 +15,8 @@
 template <typename T>
 __global__ void embed_gather_kernel(float* __restrict__ x, const T* __restrict__ table,
                                     const int* __restrict__ ids, int D, int vocab, int* err) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* xr = x + (size_t)t * D;
@@ -34,6 +36,8 @@ template <typename T>
 __global__ void rmsnorm_kernel(T* __restrict__ y, const float* __restrict__ x,
                                const float* __restrict__ w, int D, float eps) {
     __shared__ float red[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const float* xr = x + (size_t)blockIdx.x * D;
     T* yr = y + (size_t)blockIdx.x * D;
     float ss = 0.f;
@@ -56,6 +60,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride,
                                      T* __restrict__ cache, const int* __restrict__ tables, int max_pages,
                                      const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                                      int H, int KVH, int hd, int has_kv, int rotate) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int b = tok_seq[t];
     if (b < 0) return;
@@ -102,6 +108,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride,
 // ---------------------------------------------------------------------------------------
 template <typename T>
 __global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int FF, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (size_t)gridDim.x * blockDim.x) {
         const size_t r = i / FF, c = i % FF;
@@ -113,6 +121,8 @@ __global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int
 
 __global__ void gather_rows_f32_kernel(float* __restrict__ out, const float* __restrict__ x,
                                        const int* __restrict__ rows, int D) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = rows[blockIdx.x];
     for (int d = threadIdx.x; d < D; d += blockDim.x)
         out[(size_t)blockIdx.x * D + d] = x[(size_t)r * D + d];
@@ -128,25 +138,25 @@ extern "C" {
 int oe_embed_gather_f32(float* x, const float* table, const int* ids, int n_tokens, int D, int vocab,
                         int* err, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
-    embed_gather_kernel<float><<<n_tokens, 256, 0, st>>>(x, table, ids, D, vocab, err);
-    LAUNCH_CHECK();
+    const int launch_rc = oe_launch(embed_gather_kernel<float>, dim3(n_tokens), dim3(256), 0, st, x, table, ids, D, vocab, err);
+    return launch_rc;
 }
 int oe_embed_gather_bf16(float* x, const bf16* table, const int* ids, int n_tokens, int D, int vocab,
                          int* err, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
-    embed_gather_kernel<bf16><<<n_tokens, 256, 0, st>>>(x, table, ids, D, vocab, err);
-    LAUNCH_CHECK();
+    const int launch_rc = oe_launch(embed_gather_kernel<bf16>, dim3(n_tokens), dim3(256), 0, st, x, table, ids, D, vocab, err);
+    return launch_rc;
 }
 
 int oe_rmsnorm_f32(float* y, const float* x, const float* w, int rows, int D, float eps, cudaStream_t st) {
     if (rows <= 0) return 0;
-    rmsnorm_kernel<float><<<rows, 256, 0, st>>>(y, x, w, D, eps);
-    LAUNCH_CHECK();
+    const int launch_rc = oe_launch(rmsnorm_kernel<float>, dim3(rows), dim3(256), 0, st, y, x, w, D, eps);
+    return launch_rc;
 }
 int oe_rmsnorm_bf16(bf16* y, const float* x, const float* w, int rows, int D, float eps, cudaStream_t st) {
     if (rows <= 0) return 0;
-    rmsnorm_kernel<bf16><<<rows, 256, 0, st>>>(y, x, w, D, eps);
-    LAUNCH_CHECK();
+    const int launch_rc = oe_launch(rmsnorm_kernel<bf16>, dim3(rows), dim3(256), 0, st, y, x, w, D, eps);
+    return launch_rc;
 }
 
 int oe_rope_kv_write_f32(float* qkv, int row_stride, const float* cos_tab, const float* sin_tab,
@@ -155,9 +165,9 @@ int oe_rope_kv_write_f32(float* qkv, int row_stride, const float* cos_tab, const
                          cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (hd % 2) return OE_ERR_UNSUPPORTED;
-    rope_kv_write_kernel<float><<<n_tokens, 256, 0, st>>>(qkv, row_stride, cos_tab, sin_tab, cache, tables,
+    const int launch_rc = oe_launch(rope_kv_write_kernel<float>, dim3(n_tokens), dim3(256), 0, st, qkv, row_stride, cos_tab, sin_tab, cache, tables,
                                                            max_pages, tok_seq, tok_pos, H, KVH, hd, has_kv, rotate);
-    LAUNCH_CHECK();
+    return launch_rc;
 }
 int oe_rope_kv_write_bf16(bf16* qkv, int row_stride, const float* cos_tab, const float* sin_tab,
                           bf16* cache, const int* tables, int max_pages, const int* tok_seq,
@@ -165,30 +175,30 @@ int oe_rope_kv_write_bf16(bf16* qkv, int row_stride, const float* cos_tab, const
                           cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (hd % 2) return OE_ERR_UNSUPPORTED;
-    rope_kv_write_kernel<bf16><<<n_tokens, 256, 0, st>>>(qkv, row_stride, cos_tab, sin_tab, cache, tables,
+    const int launch_rc = oe_launch(rope_kv_write_kernel<bf16>, dim3(n_tokens), dim3(256), 0, st, qkv, row_stride, cos_tab, sin_tab, cache, tables,
                                                           max_pages, tok_seq, tok_pos, H, KVH, hd, has_kv, rotate);
-    LAUNCH_CHECK();
+    return launch_rc;
 }
 
 int oe_swiglu_f32(float* out, const float* gu, int rows, int FF, cudaStream_t st) {
     const size_t total = (size_t)rows * FF;
     if (total == 0) return 0;
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    swiglu_kernel<float><<<blocks, 256, 0, st>>>(out, gu, FF, total);
-    LAUNCH_CHECK();
+    const int launch_rc = oe_launch(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, st, out, gu, FF, total);
+    return launch_rc;
 }
 int oe_swiglu_bf16(bf16* out, const bf16* gu, int rows, int FF, cudaStream_t st) {
     const size_t total = (size_t)rows * FF;
     if (total == 0) return 0;
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    swiglu_kernel<bf16><<<blocks, 256, 0, st>>>(out, gu, FF, total);
-    LAUNCH_CHECK();
+    const int launch_rc = oe_launch(swiglu_kernel<bf16>, dim3(blocks), dim3(256), 0, st, out, gu, FF, total);
+    return launch_rc;
 }
 
 int oe_gather_rows_f32(float* out, const float* x, const int* rows, int n_rows, int D, cudaStream_t st) {
     if (n_rows <= 0) return 0;
-    gather_rows_f32_kernel<<<n_rows, 256, 0, st>>>(out, x, rows, D);
-    LAUNCH_CHECK();
+    const int launch_rc = oe_launch(gather_rows_f32_kernel, dim3(n_rows), dim3(256), 0, st, out, x, rows, D);
+    return launch_rc;
 }
 
 }  // extern "C"

@@ -25,6 +25,8 @@ gemm_nt_kernel(TC* __restrict__ C, const TA* __restrict__ A, const TA* __restric
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int lr = tid / 4, lk = (tid % 4) * 4;      // loader: row lr, k lk..lk+3
 
+    pdl_launch_dependents();
+    pdl_wait();
     float acc[TM][TN];
 #pragma unroll
     for (int i = 0; i < TM; i++)
@@ -76,8 +78,8 @@ int launch(TC* C, const TA* A, const TA* W, int M, int N, int K, long long lda, 
     if (K <= 0) return OE_ERR_UNSUPPORTED;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (grid.y > 65535) return OE_ERR_UNSUPPORTED;
-    gemm_nt_kernel<TA, TC, MODE><<<grid, 256, 0, st>>>(C, A, W, M, N, K, lda, ldc);
-    return (int)cudaGetLastError();
+    const int launch_rc = oe_launch(gemm_nt_kernel<TA, TC, MODE>, dim3(grid), dim3(256), 0, st, C, A, W, M, N, K, lda, ldc);
+    return launch_rc;
 }
 
 }  // namespace

@@ -260,10 +260,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *(volatile uint32_t*)&ctl->tmem_base;
 
+    pdl_launch_dependents();
     if (warp == 0) {
         // ---------------- TMA producer ----------------
+        // The weight operand (A when swapped, else B) does not depend on earlier kernels:
+        // its first tiles are requested before pdl_wait(), the activation tiles after it.
         if (lane == 0) {
-            for (int i = 0; i < n_kb; i++) {
+            const int first = min(n_kb, g.stages);
+            for (int i = 0; i < first; i++) {
+                uint8_t* a_dst = smem + (size_t)i * stage_bytes;
+                mbar_expect_tx(&ctl->full[i], (uint32_t)(A_TILE_BYTES + b_tile_bytes));
+                if (g.swap) tma_load_2d(a_dst, &map_a, &ctl->full[i], (kb0 + i) * BLOCK_K, tile_a * BLOCK_M);
+                else tma_load_2d(a_dst + A_TILE_BYTES, &map_b, &ctl->full[i], (kb0 + i) * BLOCK_K, tile_b * g.n_tile);
+            }
+            pdl_wait();
+            for (int i = 0; i < first; i++) {
+                uint8_t* a_dst = smem + (size_t)i * stage_bytes;
+                if (g.swap) tma_load_2d(a_dst + A_TILE_BYTES, &map_b, &ctl->full[i], (kb0 + i) * BLOCK_K, tile_b * g.n_tile);
+                else tma_load_2d(a_dst, &map_a, &ctl->full[i], (kb0 + i) * BLOCK_K, tile_a * BLOCK_M);
+            }
+            for (int i = first; i < n_kb; i++) {
                 const int s = i % g.stages;
                 const uint32_t phase = (uint32_t)(i / g.stages) & 1u;
                 if (!mbar_wait(&ctl->empty[s], phase ^ 1u, ctl, 1)) break;
@@ -304,6 +320,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // every epilogue thread takes the same decision, so that all of them reach the
         // named barriers below
         if (!mbar_wait(&ctl->tmem_full, 0, ctl, 3)) atomicExch(&ctl->epi_ok, 0);
+        pdl_wait();                                   // before the first access to C, workspace, counters
         asm volatile("bar.sync 1, 128;" ::: "memory");
         const bool ok = *(volatile int*)&ctl->epi_ok != 0;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -485,8 +502,8 @@ int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, 
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
-    gemm_tc_kernel<<<grid, THREADS, smem, st>>>(map_a, map_b, g);
-    return (int)cudaGetLastError();
+    const int launch_rc = oe_launch(gemm_tc_kernel, dim3(grid), dim3(THREADS), smem, st, map_a, map_b, g);
+    return launch_rc;
 }
 
 // Reads and clears the device-side error flag (0 = no wait ran out).

@@ -57,12 +57,28 @@ def gemm_supported(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.stride(1) == 1)
 
 
+SKINNY_MAX_TOKENS = 8       # up to here the weight-streaming kernel (gemm_skinny.cu) is used
+
+
+def _skinny():
+    lib = _state.get("skinny")
+    if lib is None:
+        lib = _build.load("gemm_skinny")
+        lib.oe_gemm_skinny_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong,
+                                            c_int, c_void_p]
+        lib.oe_gemm_skinny_bf16.restype = c_int
+        _state["skinny"] = lib
+    return lib
+
+
 def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool = False, split_k: bool = True,
-         swiglu: bool = False) -> None:
+         swiglu: bool = False, kernel: str = "auto") -> None:
     """out (+)= a @ w.T, a [M, K] and w [N, K] bfloat16; out bfloat16 or float32 [M, N].
 
     swiglu: w's rows alternate gate and up rows (g0, u0, g1, u1, ...) and out [M, N/2]
-    bfloat16 receives silu(gate) * up, computed in float32 in the epilogue."""
+    bfloat16 receives silu(gate) * up, computed in float32 in the epilogue.
+    kernel: "auto" (weight-streaming kernel up to SKINNY_MAX_TOKENS rows, tcgen05 above),
+    "tcgen05" or "skinny"."""
     M, K = a.shape
     N = w.shape[0]
     if w.shape[1] != K or out.shape != (M, N // 2 if swiglu else N):
@@ -83,6 +99,11 @@ def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool =
         kind = 1
     else:
         raise KernelError("gemm: output must be bfloat16 or float32")
+    if kernel == "skinny" or (kernel == "auto" and M <= SKINNY_MAX_TOKENS):
+        code = _skinny().oe_gemm_skinny_bf16(out.data_ptr(), a.data_ptr(), w.data_ptr(), M, N, K, a.stride(0),
+                                             out.stride(0), kind, torch.cuda.current_stream().cuda_stream)
+        ops._check(code, "gemm_skinny")
+        return
     ws, counters, sms = _scratch(a.device)
     code = _lib().oe_gemm_tc_bf16(out.data_ptr(), a.data_ptr(), w.data_ptr(), M, N, K, a.stride(0), out.stride(0), kind,
                                   ws.data_ptr() if split_k else None, ws.numel() * 4,

@@ -63,6 +63,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_rows_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = block_argmax(logits + (size_t)blockIdx.x * V, V, s_val, s_idx);
     if (threadIdx.x == 0) out[blockIdx.x] = r;
 }
@@ -84,6 +86,8 @@ sample_rows_kernel(float* __restrict__ logits, int* __restrict__ out, const int*
     __shared__ int s_idx[32];
     __shared__ float s_scan[SAMPLE_THREADS];
     __shared__ int s_pick;
+    pdl_launch_dependents();
+    pdl_wait();
     const int slot = row_slot[blockIdx.x];
     if (slot < 0) { if (threadIdx.x == 0) out[blockIdx.x] = -1; return; }
     float* x = logits + (size_t)blockIdx.x * V;
@@ -208,8 +212,8 @@ extern "C" {
 int oe_argmax_rows(const float* logits, int* out, int rows, int V, cudaStream_t st) {
     if (rows <= 0) return 0;
     if (V <= 0) return OE_ERR_UNSUPPORTED;
-    argmax_rows_kernel<<<rows, SAMPLE_THREADS, 0, st>>>(logits, out, V);
-    return (int)cudaGetLastError();
+    const int launch_rc = oe_launch(argmax_rows_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, st, logits, out, V);
+    return launch_rc;
 }
 
 int oe_sample_rows(float* logits, int* out, const int* row_slot, int rows, int V, float temperature,
@@ -219,9 +223,9 @@ int oe_sample_rows(float* logits, int* out, const int* row_slot, int rows, int V
     if (rows <= 0) return 0;
     if (V <= 0 || (hist != nullptr && hist_cap <= 0)) return OE_ERR_UNSUPPORTED;
     SampleState st{rng_seed, rng_counter, hist, hist_count, hist_cap};
-    sample_rows_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, out, row_slot, V, temperature, top_k, top_p,
+    const int launch_rc = oe_launch(sample_rows_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, logits, out, row_slot, V, temperature, top_k, top_p,
                                                             repeat_pen, repeat_last, st, record);
-    return (int)cudaGetLastError();
+    return launch_rc;
 }
 
 }  // extern "C"

@@ -85,10 +85,42 @@ def test_gemm_simple(dtype, M, N, K):
     assert (outv.double() - wide[:, :K].double() @ w.double().T).abs().max() < tol
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 3072, 1024), (5, 136, 72), (16, 50, 8), (9, 333, 4096), (3, 16, 520)])
+def test_gemm_skinny(M, N, K):
+    from oracle_engine_b200.csrc import ops_tc
+    a, w = _rand(M, K, dtype=torch.bfloat16, scale=0.5, seed=1), _rand(N, K, dtype=torch.bfloat16, scale=0.5, seed=2)
+    want = a.double() @ w.double().T
+    tol = 2e-6 * K + 1e-5
+    out32 = torch.full((M, N), 9.0, device=DEV)
+    ops_tc.gemm(out32, a, w, kernel="skinny")
+    assert (out32.double() - want).abs().max() < tol
+    out16 = torch.full((M, N), 9.0, dtype=torch.bfloat16, device=DEV)
+    ops_tc.gemm(out16, a, w, kernel="skinny")
+    assert (out16.double() - want).abs().max() < 0.005 * want.abs().max() + tol
+    base = _rand(M, N, seed=3)
+    acc = base.clone()
+    ops_tc.gemm(acc, a, w, accumulate=True, kernel="skinny")
+    assert (acc.double() - (base.double() + want)).abs().max() < tol
+    if N % 2 == 0:
+        act = torch.full((M, N // 2), 9.0, dtype=torch.bfloat16, device=DEV)
+        ops_tc.gemm(act, a, w, swiglu=True, kernel="skinny")
+        gate, up = want[:, 0::2], want[:, 1::2]
+        ref = gate / (1 + torch.exp(-gate)) * up
+        assert (act.double() - ref).abs().max() < 0.005 * ref.abs().max() + 10 * tol
+    # a token's result does not depend on the other tokens of the step (bit for bit)
+    one = torch.empty(1, N, device=DEV)
+    ops_tc.gemm(one, a[M - 1:M], w, kernel="skinny")
+    assert torch.equal(one[0], out32[M - 1])
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 3072, 1024), (5, 136, 72), (64, 520, 4096), (100, 333, 200),
                                    (128, 48, 64), (129, 48, 200), (300, 1000, 520), (1000, 264, 72)])
 def test_gemm_tcgen05(M, N, K):
     from oracle_engine_b200.csrc import ops_tc
+    import functools
+    ops_tc = type("tc", (), {"gemm": staticmethod(functools.partial(ops_tc.gemm, kernel="tcgen05")),
+                             "device_error": staticmethod(ops_tc.device_error),
+                             "gemm_supported": staticmethod(ops_tc.gemm_supported)})
     a, w = _rand(M, K, dtype=torch.bfloat16, scale=0.5, seed=1), _rand(N, K, dtype=torch.bfloat16, scale=0.5, seed=2)
     want = a.double() @ w.double().T
     tol = 2e-6 * K + 1e-5

@@ -44,6 +44,14 @@ struct AttnArgs {
     int tokens_per_tile;
     int n_splits;
     float* partial;            // [T, H, n_splits, HD + 2] when n_splits > 1
+    // fused decode (every sequence brings one token): q is the raw fused qkv row, the kernel
+    // rotates q (and the new k) itself, writes the new k, v to the cache and the CTA that
+    // finishes last merges the splits
+    int fused;
+    const float* cos_tab;      // [max_pos, HD/2] or null (no rotation)
+    const float* sin_tab;
+    bf16* cache_w;             // the cache entry, writable, when this call stores the new k, v; else null
+    int* counters;             // [B * KVH] zeros (n_splits > 1)
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -143,6 +151,25 @@ attn_mma_kernel(const AttnArgs a) {
         }
     }
 
+    if (a.fused && a.cos_tab != nullptr) {
+        // rotate-half pairs (d, d + HD/2) sit in the same lane, KS/2 k-steps apart
+#pragma unroll
+        for (int ks = 0; ks < KS / 2; ks++) {
+#pragma unroll
+            for (int x = 0; x < 4; x++) {
+                const int i = x & 1;
+                const int d = ks * 16 + tig * 2 + (x >> 1) * 8;
+                const float2 cs = *(const float2*)(a.cos_tab + (size_t)pos[i] * (HD / 2) + d);
+                const float2 sn = *(const float2*)(a.sin_tab + (size_t)pos[i] * (HD / 2) + d);
+                const __nv_bfloat162 lo = *(__nv_bfloat162*)&qf[ks][x];
+                const __nv_bfloat162 hi = *(__nv_bfloat162*)&qf[ks + KS / 2][x];
+                const float x0a = __low2float(lo), x0b = __high2float(lo), x1a = __low2float(hi), x1b = __high2float(hi);
+                qf[ks][x] = pack_bf16(x0a * cs.x - x1a * sn.x, x0b * cs.y - x1b * sn.y);
+                qf[ks + KS / 2][x] = pack_bf16(x0a * sn.x + x1a * cs.x, x0b * sn.y + x1b * cs.y);
+            }
+        }
+    }
+
     float oacc[HD / 8][4];
 #pragma unroll
     for (int n = 0; n < HD / 8; n++) { oacc[n][0] = oacc[n][1] = oacc[n][2] = oacc[n][3] = 0.f; }
@@ -164,6 +191,32 @@ attn_mma_kernel(const AttnArgs a) {
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
+
+        if (a.fused && a.cache_w != nullptr && j == pos_hi / BN) {
+            // this CTA holds the page of the new token: rotate its key, store key and value
+            // in the cache, and put them into the staged tile as well
+            const int r = pos_hi % BN;
+            const bf16* krow = a.q + packed0 * a.q_stride + (size_t)(a.H + kvh) * HD;
+            const bf16* vrow = krow + (size_t)a.KVH * HD;
+            const size_t page = (size_t)trow[j];
+            bf16* kc = a.cache_w + ((page * 2 + 0) * a.KVH + kvh) * (size_t)(BN * HD) + (size_t)r * HD;
+            bf16* vc = a.cache_w + ((page * 2 + 1) * a.KVH + kvh) * (size_t)(BN * HD) + (size_t)r * HD;
+            bf16* ksm = (bf16*)(ks_cur + r * ROW_BYTES);
+            bf16* vsm = (bf16*)(vs_cur + r * ROW_BYTES);
+            for (int d = threadIdx.x; d < HD / 2; d += blockDim.x) {
+                float k0 = __bfloat162float(krow[d]), k1 = __bfloat162float(krow[d + HD / 2]);
+                if (a.cos_tab != nullptr) {
+                    const float c = a.cos_tab[(size_t)pos_hi * (HD / 2) + d], sn = a.sin_tab[(size_t)pos_hi * (HD / 2) + d];
+                    const float r0 = k0 * c - k1 * sn, r1 = k0 * sn + k1 * c;
+                    k0 = r0; k1 = r1;
+                }
+                const bf16 b0 = __float2bfloat16_rn(k0), b1 = __float2bfloat16_rn(k1);
+                const bf16 v0 = vrow[d], v1 = vrow[d + HD / 2];
+                kc[d] = b0; kc[d + HD / 2] = b1; ksm[d] = b0; ksm[d + HD / 2] = b1;
+                vc[d] = v0; vc[d + HD / 2] = v1; vsm[d] = v0; vsm[d + HD / 2] = v1;
+            }
+            __syncthreads();
+        }
 
         // S = Q K^T for this warp's 16 rows and the block's 64 keys
         float sacc[BN / 8][4];
@@ -269,6 +322,57 @@ attn_mma_kernel(const AttnArgs a) {
             }
             if (tig == 0) { p[HD] = m_run[i]; p[HD + 1] = l_run[i]; }
         }
+        if (a.fused) {
+            // the CTA of this (sequence, KV head) that finishes last merges the splits, in split order
+            __shared__ int s_last;
+            __threadfence();
+            __syncthreads();
+            if (threadIdx.x == 0) s_last = (atomicAdd(&a.counters[b * a.KVH + kvh], 1) == a.n_splits - 1) ? 1 : 0;
+            __syncthreads();
+            if (s_last) {
+                __threadfence();
+                // weights of every (head, split) first, then all value loads of a thread at once
+                __shared__ float s_m[64 * 32], s_l[64 * 32];
+                const int ns = a.n_splits;
+                const float* pbase = a.partial + ((packed0 * a.H + (long long)kvh * G) * ns) * (long long)(HD + 2);
+                for (int idx = threadIdx.x; idx < G * ns; idx += blockDim.x) {
+                    s_m[idx] = __ldcg(pbase + (size_t)idx * (HD + 2) + HD);
+                    s_l[idx] = __ldcg(pbase + (size_t)idx * (HD + 2) + HD + 1);
+                }
+                __syncthreads();
+                for (int gh = threadIdx.x; gh < G; gh += blockDim.x) {
+                    float m = -INFINITY, l = 0.f;
+                    for (int sp = 0; sp < ns; sp++) m = fmaxf(m, s_m[gh * ns + sp]);
+                    for (int sp = 0; sp < ns; sp++)
+                        if (s_m[gh * ns + sp] != -INFINITY) l += s_l[gh * ns + sp] * exp2f(s_m[gh * ns + sp] - m);
+                    const float inv = l > 0.f ? 1.f / l : 0.f;
+                    for (int sp = 0; sp < ns; sp++)
+                        s_l[gh * ns + sp] = (s_m[gh * ns + sp] != -INFINITY) ? exp2f(s_m[gh * ns + sp] - m) * inv : 0.f;
+                }
+                __syncthreads();
+                bf16* obase = a.out + packed0 * (long long)(a.H * HD) + (size_t)kvh * G * HD;
+                const int total = G * HD;
+                for (int i0 = threadIdx.x; i0 < total; i0 += 4 * blockDim.x) {
+                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const int idx = i0 + u * blockDim.x;
+                        if (idx < total) {
+                            const int gh = idx / HD, d = idx % HD;
+#pragma unroll 8
+                            for (int sp = 0; sp < ns; sp++)
+                                acc[u] += s_l[gh * ns + sp] * __ldcg(pbase + (size_t)(gh * ns + sp) * (HD + 2) + d);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const int idx = i0 + u * blockDim.x;
+                        if (idx < total) obase[idx] = __float2bfloat16_rn(acc[u]);
+                    }
+                }
+                if (threadIdx.x == 0) a.counters[b * a.KVH + kvh] = 0;
+            }
+        }
     }
 }
 
@@ -342,6 +446,7 @@ int oe_attn_mma_bf16(bf16* out, const bf16* q, long long q_stride, const bf16* c
     a.cu_q = cu_q; a.seq_start = seq_start; a.seq_qlen = seq_qlen; a.H = H; a.KVH = KVH; a.window = window;
     a.scale_log2 = scale * 1.4426950408889634f;
     a.partial = partial;
+    a.fused = 0; a.cos_tab = nullptr; a.sin_tab = nullptr; a.cache_w = nullptr; a.counters = nullptr;
     // rows per sequence tile: 16 per warp; few rows (decode) use fewer warps
     const long long rows_needed = (long long)max_qlen * G;
     int nwarps = rows_needed <= 16 ? 1 : (rows_needed <= 32 ? 2 : 4);
@@ -361,6 +466,34 @@ int oe_attn_mma_bf16(bf16* out, const bf16* q, long long q_stride, const bf16* c
         rc = launch_rc;
     }
     return rc;
+}
+
+// Decode step in one kernel: every sequence brings ONE token.  qkv rows are the fused
+// projection [H*HD | KVH*HD | KVH*HD] before rotation; the kernel rotates q and the new k
+// (cos/sin float32 [max_pos, HD/2], null = no rotation), stores k and v at the token's
+// position when has_kv is set (else the row holds queries only and the cache already has
+// the key), attends, and merges the splits.  counters: n_seqs * KVH zeroed ints.
+int oe_attn_decode_fused_bf16(bf16* out, const bf16* qkv, long long qkv_stride, const float* cos_tab,
+                              const float* sin_tab, bf16* cache, int has_kv, const int* tables, int max_pages,
+                              const int* cu_q, const int* seq_start, const int* seq_qlen, int n_seqs, int H, int KVH,
+                              int window, float scale, int n_splits, float* partial, int* counters, cudaStream_t st) {
+    if (n_seqs <= 0) return 0;
+    if (H % KVH || ((uintptr_t)qkv & 3) || (qkv_stride & 1) || (HD % 32)) return OE_ERR_UNSUPPORTED;
+    const int G = H / KVH;
+    if (G > 64) return OE_ERR_UNSUPPORTED;
+    if (n_splits > 32 || (n_splits > 1 && (partial == nullptr || counters == nullptr))) return OE_ERR_UNSUPPORTED;
+    AttnArgs a;
+    a.out = out; a.q = qkv; a.q_stride = qkv_stride; a.cache = cache; a.tables = tables; a.max_pages = max_pages;
+    a.cu_q = cu_q; a.seq_start = seq_start; a.seq_qlen = seq_qlen; a.H = H; a.KVH = KVH; a.window = window;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    a.partial = partial;
+    a.fused = 1; a.cos_tab = cos_tab; a.sin_tab = sin_tab; a.cache_w = has_kv ? cache : nullptr; a.counters = counters;
+    int nwarps = G <= 16 ? 1 : (G <= 32 ? 2 : 4);
+    a.tokens_per_tile = (nwarps * 16) / G;
+    a.n_splits = n_splits < 1 ? 1 : n_splits;
+    if (nwarps == 1) return launch<1>(a, n_seqs, a.n_splits, st);
+    if (nwarps == 2) return launch<2>(a, n_seqs, a.n_splits, st);
+    return launch<4>(a, n_seqs, a.n_splits, st);
 }
 
 }  // extern "C"

@@ -140,6 +140,10 @@ def _attn_lib(head_dim: int):
                                          c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                                          c_void_p, c_void_p]
         lib.oe_attn_mma_bf16.restype = c_int
+        lib.oe_attn_decode_fused_bf16.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
+                                                  c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                  c_int, c_float, c_int, c_void_p, c_void_p, c_void_p]
+        lib.oe_attn_decode_fused_bf16.restype = c_int
         lib.oe_attn_mma_partial_floats.argtypes = [c_int, c_int, c_int]
         lib.oe_attn_mma_partial_floats.restype = c_longlong
         _state[key] = lib
@@ -152,6 +156,11 @@ def decode_splits(n_seqs: int, n_kv_heads: int, sm_count: int, max_pages: int) -
     size and the cache geometry only, so a captured graph stays valid."""
     ctas = max(1, n_seqs * n_kv_heads)
     return max(1, min(max_pages, 32, (2 * sm_count + ctas - 1) // ctas))
+
+
+def decode_splits_for(n_seqs: int, n_kv_heads: int, tables) -> int:
+    sms = torch.cuda.get_device_properties(tables.device).multi_processor_count
+    return decode_splits(n_seqs, n_kv_heads, sms, tables.shape[1])
 
 
 def attention(out, qkv, cache, tables, ctx, n_heads: int, n_kv_heads: int, head_dim: int, window: int,
@@ -184,3 +193,49 @@ def attention(out, qkv, cache, tables, ctx, n_heads: int, n_kv_heads: int, head_
     ops._check(code, "attention_mma")
     if n_splits > 1:
         ops.LAUNCHES[0] += 1
+
+
+def decode_fused_supported(head_dim: int, n_heads: int, n_kv_heads: int) -> bool:
+    return attention_supported(head_dim, n_heads, n_kv_heads) and head_dim % 32 == 0
+
+
+def _attn_counters(device):
+    key = ("attn_counters", device.index)
+    c = _state.get(key)
+    if c is None:
+        c = torch.zeros(1 << 16, dtype=torch.int32, device=device)
+        _state[key] = c
+    return c
+
+
+def attention_decode_fused(out, qkv, cos, sin, cache, tables, ctx, n_heads: int, n_kv_heads: int, head_dim: int,
+                           window: int, scale: float, has_kv: bool) -> None:
+    """One kernel for a decode step's mixer core: rotates q and the new k, stores k and v
+    in the cache (has_kv), attends over the sequence's pages split across CTAs and merges.
+
+    qkv [B, (H + 2 KVH) hd] (or [B, H hd] when has_kv is false) before rotation; cos/sin
+    float32 [max_pos, hd/2] or None; every sequence of the step brings exactly one token."""
+    B = out.shape[0]
+    if out.dtype != torch.bfloat16 or qkv.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
+        raise KernelError("attention_decode_fused: bfloat16 tensors expected")
+    width = (n_heads + (2 * n_kv_heads if has_kv else 0)) * head_dim
+    if qkv.shape[1] != width or qkv.stride(1) != 1 or not out.is_contiguous() or not cache.is_contiguous():
+        raise KernelError(f"attention_decode_fused: qkv must be [B, {width}], out and cache contiguous")
+    if tuple(cache.shape[1:]) != (2, n_kv_heads, ops.PAGE, head_dim):
+        raise KernelError("attention_decode_fused: cache entry must be [pages, 2, KVH, PAGE, head_dim]")
+    if ctx.n_seqs * n_kv_heads > (1 << 16):
+        raise KernelError("attention_decode_fused: too many sequences for the merge counters")
+    lib = _attn_lib(head_dim)
+    sms = torch.cuda.get_device_properties(out.device).multi_processor_count
+    n_splits = decode_splits(ctx.n_seqs, n_kv_heads, sms, tables.shape[1])
+    partial = None
+    if n_splits > 1:
+        partial = torch.empty(lib.oe_attn_mma_partial_floats(B, n_heads, n_splits), dtype=torch.float32,
+                              device=out.device)
+    code = lib.oe_attn_decode_fused_bf16(
+        out.data_ptr(), qkv.data_ptr(), qkv.stride(0), None if cos is None else cos.data_ptr(),
+        None if sin is None else sin.data_ptr(), cache.data_ptr(), int(has_kv), tables.data_ptr(), tables.shape[1],
+        ctx.cu_q.data_ptr(), ctx.seq_start.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.n_seqs, n_heads, n_kv_heads,
+        int(window), float(scale), n_splits, None if partial is None else partial.data_ptr(),
+        _attn_counters(out.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+    ops._check(code, "attention_decode_fused")

@@ -66,7 +66,7 @@ class GQAAttention(Part):
         matmul_nt(self.rt, qkv, h, self.w_qkv[:width])
         cos, sin = self.position.tables() if self.position is not None else (None, None)
         from . import attention_dispatch as ad
-        ad.rope_and_cache(self.rt, qkv, cos, sin, cache, ctx, self.H, self.KVH, self.hd, owns_cache)
         o = self.rt.empty(T, q_width)
-        ad.attend(self.rt, o, qkv, cache, ctx, self.H, self.KVH, self.hd, self.window, self.scale)
+        ad.mixer_core(self.rt, o, qkv, cos, sin, cache, ctx, self.H, self.KVH, self.hd, self.window, self.scale,
+                      owns_cache)
         matmul_nt(self.rt, residual, o, self.w_o, accumulate=True)

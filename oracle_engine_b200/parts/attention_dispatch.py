@@ -12,6 +12,20 @@ import torch
 from ..csrc import ops
 
 
+def mixer_core(rt, out, qkv, cos, sin, cache, ctx, H, KVH, hd, window, scale, owns_cache) -> None:
+    """Rotation, cache write and attention of one attention mixer for the step's tokens."""
+    if rt.dtype == torch.bfloat16 and rt.tensor_cores and ctx.all_decode and ctx.n_tokens == ctx.n_seqs:
+        from ..csrc import ops_tc
+        # One kernel when the batch alone fills the GPU (no split over the keys); for small
+        # batches the split kernels plus a parallel merge are faster (measured).
+        if ops_tc.decode_fused_supported(hd, H, KVH) and ops_tc.decode_splits_for(ctx.n_seqs, KVH, cache.tables) == 1:
+            ops_tc.attention_decode_fused(out, qkv, cos, sin, cache.storage, cache.tables, ctx, H, KVH, hd, window,
+                                          scale, owns_cache)
+            return
+    rope_and_cache(rt, qkv, cos, sin, cache, ctx, H, KVH, hd, owns_cache)
+    attend(rt, out, qkv, cache, ctx, H, KVH, hd, window, scale)
+
+
 def rope_and_cache(rt, qkv, cos, sin, cache, ctx, H, KVH, hd, owns_cache) -> None:
     ops.rope_kv_write(qkv, cos, sin, cache.storage if owns_cache else None, cache.tables, ctx.tok_seq,
                       ctx.tok_pos, H, KVH, hd, owns_cache)

@@ -314,3 +314,57 @@ def test_argmax_and_sampling():
                 assert got[r] == want, f"{c} draw {draw} row {r}: {got[r]} vs {want}"
                 history[s].append(got[r])
         assert counters[5].item() == (3 if c["temperature"] > 0 else 0) and hist_count[5].item() == 10
+
+
+@pytest.mark.parametrize("H,KVH,hd,window,rotate", [(24, 8, 128, 0, True), (6, 2, 32, 0, True), (8, 8, 64, 100, False),
+                                                     (4, 1, 32, 0, True)])
+def test_attention_decode_fused(H, KVH, hd, window, rotate):
+    """One kernel for rotation, cache write, split attention and merge, against the plain parts."""
+    from types import SimpleNamespace
+    from oracle_engine_b200.csrc import ops_tc
+    lens = [1, 64, 65, 200, 130, 17, 128]                      # length including the new token
+    B = len(lens)
+    g = torch.Generator().manual_seed(hd + H)
+    bf = lambda t: t.to(torch.bfloat16)                       # noqa: E731
+    inv = pl.rope_inv_freq(hd, 10000.0, None)
+    ang = torch.arange(256, dtype=torch.float64)[:, None] * inv[None]
+    cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
+    k_old = [bf(torch.randn(n - 1, KVH, hd, generator=g)) for n in lens]        # already rotated, in the cache
+    v_old = [bf(torch.randn(n - 1, KVH, hd, generator=g)) for n in lens]
+    qkv = bf(torch.randn(B, (H + 2 * KVH) * hd, generator=g) * 1.2)
+    # cache pages hold the old keys; the page of the new token exists but its row is stale
+    pad = lambda t: torch.cat([t, torch.full((1, KVH, hd), 77.0, dtype=t.dtype)])          # noqa: E731
+    cache, tables = _paged([pad(k) for k in k_old], [pad(v) for v in v_old], lens, torch.bfloat16, seed=3)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)                           # noqa: E731
+    # a padding sequence at the end
+    tab = torch.cat([tables, torch.full((1, tables.shape[1]), -1, dtype=torch.int32, device=DEV)])
+    ctx = SimpleNamespace(cu_q=i32(list(range(B + 1)) + [B]), seq_start=i32([n - 1 for n in lens] + [0]),
+                          seq_qlen=i32([1] * B + [0]), n_seqs=B + 1)
+    out = torch.full((B + 1, H * hd), 5.0, dtype=torch.bfloat16, device=DEV)
+    qkv_dev = torch.cat([qkv, torch.zeros(1, qkv.shape[1], dtype=torch.bfloat16)]).to(DEV)
+    ops_tc.attention_decode_fused(out, qkv_dev, cos if rotate else None, sin if rotate else None, cache, tab, ctx, H, KVH,
+                                  hd, window, 1 / math.sqrt(hd), True)
+    for b, n in enumerate(lens):
+        q = qkv[b, :H * hd].double().reshape(1, H, hd)
+        k = qkv[b, H * hd:(H + KVH) * hd].double().reshape(1, KVH, hd)
+        v = qkv[b, (H + KVH) * hd:].double().reshape(1, KVH, hd)
+        if rotate:
+            p = torch.tensor([n - 1])
+            q, k = pl.rope_rotate(q, p, inv), pl.rope_rotate(k, p, inv)
+        k_new = bf(k).double()
+        k_all = torch.cat([k_old[b].double(), k_new])
+        v_all = torch.cat([v_old[b].double(), v])
+        qq = torch.zeros(n, H, hd, dtype=torch.float64)
+        qq[-1] = bf(q).double()[0]
+        want = pl.causal_attention(qq, k_all, v_all, window or None)[-1]
+        err = (out[b].double().cpu() - want).abs().max().item()
+        assert err < 2.5e-2, f"sequence {b} (len {n}): {err}"
+        page = int(tables[b, (n - 1) // 64])
+        assert torch.equal(cache[page, 0, :, (n - 1) % 64].cpu(), bf(k_new)[0])            # the new key and value are stored
+        assert torch.equal(cache[page, 1, :, (n - 1) % 64].cpu(), bf(v)[0])
+    # an entry that reads another entry's cache: queries only, nothing stored
+    out2 = torch.full_like(out, 5.0)
+    q_only = qkv_dev[:, :H * hd].contiguous()
+    ops_tc.attention_decode_fused(out2, q_only, cos if rotate else None, sin if rotate else None, cache, tab, ctx, H, KVH,
+                                  hd, window, 1 / math.sqrt(hd), False)
+    assert torch.equal(out2[:B], out[:B])

@@ -19,10 +19,8 @@
 
 namespace {
 
-constexpr int WARPS = 8;
 constexpr int ROWS = 16;          // weight rows per CTA
 constexpr int CHUNK = 64;         // k per chunk: 4 lanes x 16 consecutive bf16
-constexpr int UNROLL = 4;         // chunks in flight per warp
 
 __device__ __forceinline__ uint4 ld_weight(const bf16* p) {
     uint4 v;
@@ -37,7 +35,9 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int NT>      // 8-token tiles: 1 (M <= 8) or 2 (M <= 16)
+// NT: 8-token tiles, 1 (M <= 8) or 2 (M <= 16); WARPS: warps per CTA (they split K);
+// UNROLL: 64-wide k chunks whose weight loads a warp has in flight at once.
+template <int NT, int WARPS, int UNROLL>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_skinny_kernel(void* __restrict__ C, const bf16* __restrict__ A, const bf16* __restrict__ W,
                    int M, int N, int K, long long lda, long long ldc, int out_kind) {
@@ -142,12 +142,18 @@ int oe_gemm_skinny_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int
     if (!oe_gemm_skinny_supported(A, W, M, N, K, lda)) return OE_ERR_UNSUPPORTED;
     if (out_kind < 0 || out_kind > 3 || (out_kind == 3 && (N & 1))) return OE_ERR_UNSUPPORTED;
     const int blocks = (N + ROWS - 1) / ROWS;
-    // Launched after the kernel before it has finished: started early, its many CTAs would
-    // take bandwidth and SM slots from the kernel they wait for (measured: slower).
-    static int early = -1;
-    if (early < 0) { const char* e = getenv("OE_SKINNY_EARLY"); early = (e != nullptr && e[0] == '1') ? 1 : 0; }
-    if (M <= 8) return oe_launch_ex(early == 1, gemm_skinny_kernel<1>, dim3(blocks), dim3(WARPS * 32), 0, st, C, A, W, M, N, K, lda, ldc, out_kind);
-    return oe_launch_ex(early == 1, gemm_skinny_kernel<2>, dim3(blocks), dim3(WARPS * 32), 0, st, C, A, W, M, N, K, lda, ldc, out_kind);
+    // Launched only after the kernel before it has finished (`false`): started early, its many
+    // CTAs took bandwidth and SM slots from the kernel they waited for (measured: slower).
+    // Warps and loads in flight per shape, from a sweep on B200 at 8 tokens: matrices with
+    // very many rows do best with small CTAs, long rows with more loads in flight.
+#define OE_SKINNY_LAUNCH(NT, WARPS, UNROLL)                                                                        \
+    return oe_launch_ex(false, gemm_skinny_kernel<NT, WARPS, UNROLL>, dim3(blocks), dim3(WARPS * 32), 0, st, C, A, \
+                        W, M, N, K, lda, ldc, out_kind)
+    if (M > 8) OE_SKINNY_LAUNCH(2, 8, 3);
+    if (blocks >= 4 * 148) OE_SKINNY_LAUNCH(1, 4, 3);
+    if (K > 4096) OE_SKINNY_LAUNCH(1, 8, 3);
+    OE_SKINNY_LAUNCH(1, 8, 2);
+#undef OE_SKINNY_LAUNCH
 }
 
 }  // extern "C"

@@ -41,6 +41,9 @@ class CacheGroup:
         self.entries = entries
         self.pool = PagePool(n_pages)
         self.tables = np.full((n_slots, max_pages_per_seq), -1, dtype=np.int32)
+        # per slot: pages [lo, hi) are mapped (lo > 0 only in window groups)
+        self.lo = np.zeros(n_slots, dtype=np.int64)
+        self.hi = np.zeros(n_slots, dtype=np.int64)
         self.storage = None
 
     def allocate(self, dtype, device) -> None:
@@ -72,6 +75,7 @@ class KVCache:
         self.max_pages_per_seq = pages_for(self.max_seq_len)
         self.slots = SlotAllocator(self.n_slots)
         self.lengths = np.zeros(self.n_slots, dtype=np.int64)
+        self.version = 0                       # grows whenever any page table changes
         self.groups: list[CacheGroup] = []
         self.entry_group: dict[int, tuple[int, int]] = {}      # entry -> (group, index in group)
         by_need: dict = {}
@@ -110,6 +114,8 @@ class KVCache:
             for i in np.nonzero(row >= 0)[0]:
                 g.pool.release(int(row[i]))
             row[:] = -1
+            g.lo[slot] = g.hi[slot] = 0
+        self.version += 1
         self.lengths[slot] = 0
         self.slots.free(slot)
 
@@ -127,6 +133,13 @@ class KVCache:
         cur = int(self.lengths[slot])
         if new_len > self.max_seq_len:
             raise CacheFull(f"sequence would reach {new_len} tokens; the cache allows {self.max_seq_len}")
+        need_hi = pages_for(new_len)
+        for g in self.groups:                       # the common case: every page is there already
+            if need_hi > g.hi[slot] or (g.need.kind == "window"
+                                        and max(0, cur - g.need.window + 1) // PAGE > g.lo[slot]):
+                break
+        else:
+            return False
         changed = False
         first_needed_page = {}
         for g in self.groups:
@@ -151,6 +164,10 @@ class KVCache:
                 if row[p] < 0:
                     row[p] = g.pool.alloc()
                     changed = True
+            g.lo[slot] = lo_page
+            g.hi[slot] = max(int(g.hi[slot]), pages_for(new_len))
+        if changed:
+            self.version += 1
         return changed
 
     def commit(self, slot: int, new_len: int) -> None:

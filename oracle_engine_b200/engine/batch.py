@@ -152,6 +152,19 @@ class StepBuffers:
             self._pending = True
         return self.context(plan)
 
+    def update_decode(self, tokens, starts, n: int) -> None:
+        """For a step of the same sequences as the last upload, each one token further: only
+        token ids, positions and starts change.  Rewrites those and copies the buffer."""
+        if self._pending:
+            self._copied.synchronize()
+        self._host_view(0)[:n] = tokens
+        self._host_view(2)[:n] = starts
+        self._host_view(4)[:n] = starts
+        self.dev.copy_(self.host, non_blocking=True)
+        if self._copied is not None:
+            self._copied.record()
+            self._pending = True
+
     def bytes(self) -> int:
         return self.total * 4
 

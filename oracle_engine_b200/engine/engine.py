@@ -120,6 +120,7 @@ class _Backend:
         self.max_seq_len = engine.max_seq_len
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        self._last_slots = None
 
     def alloc(self, request_index, prompt, params):
         slot = self.e.alloc()
@@ -138,9 +139,11 @@ class _Backend:
         e = self.e
         rows = len(slots)
         row_slot = e._row_slot[:rows]
-        host = torch.tensor(slots, dtype=torch.int32)
-        row_slot.copy_(host)
-        self.h2d_bytes += rows * 4
+        if params.temperature > 0.0 or params.repeat_penalty > 1.0:      # greedy needs no per-sequence state
+            if slots != self._last_slots:
+                row_slot.copy_(torch.tensor(slots, dtype=torch.int32))
+                self._last_slots = list(slots)
+                self.h2d_bytes += rows * 4
         out = e.sampler.sample(logits[:rows], row_slot, params)
         self.d2h_bytes += rows * 4
         return out.tolist()

@@ -45,6 +45,9 @@ class _DecodeGraph:
         self.logits = None
         self.runs = 0
         self.n_kernels = 0
+        self.key = None                # slots of the last upload, in order
+        self.version = -1              # page-table version of the last upload
+        self.ctx = None
 
 
 class Stepper:
@@ -85,8 +88,8 @@ class Stepper:
             seen.add(s.slot)
             if len(s.tokens) < 1:
                 raise StepError(f"sequence {i}: a step needs at least one token per sequence")
-            bad = [t for t in s.tokens if not 0 <= int(t) < self.vocab]
-            if bad:
+            if not (0 <= min(s.tokens) and max(s.tokens) < self.vocab):
+                bad = [t for t in s.tokens if not 0 <= int(t) < self.vocab]
                 raise StepError(f"sequence {i}: token id {bad[0]} is outside the vocabulary [0, {self.vocab})")
             if self.cache.length(s.slot) + len(s.tokens) > self.model.spec.max_positions:
                 raise StepError(f"sequence {i}: {self.cache.length(s.slot)} + {len(s.tokens)} tokens exceed the "
@@ -99,11 +102,12 @@ class Stepper:
         by the next step."""
         self._validate(seqs)
         starts = [self.cache.length(s.slot) for s in seqs]
+        tables_changed = False
         for s, st in zip(seqs, starts):
-            self.cache.reserve(s.slot, st + len(s.tokens))
+            tables_changed |= self.cache.reserve(s.slot, st + len(s.tokens))
         decode = all(len(s.tokens) == 1 for s in seqs)
         if decode and self.use_graphs:
-            logits = self._step_graph(seqs, starts)
+            logits = self._step_graph(seqs, starts, tables_changed)
         else:
             logits = self._step_eager(seqs, starts)
         for s, st in zip(seqs, starts):
@@ -125,16 +129,23 @@ class Stepper:
         self.last_h2d_bytes = buf.bytes()
         return self.model.forward(ctx, self._cache_views(ctx), self._state_views)
 
-    def _step_graph(self, seqs, starts):
+    def _step_graph(self, seqs, starts, tables_changed=True):
         B = len(seqs)
         bucket = _bucket(B)
         g = self._graphs.get(bucket)
         if g is None:
             g = _DecodeGraph(bucket, StepBuffers(bucket, bucket, bucket, self._table_shapes(bucket), self.rt.device))
             self._graphs[bucket] = g
-        plan = build_plan(seqs, starts, pad_seqs=bucket, pad_tokens=bucket, want_all_rows=True)
-        tables = [self.cache.tables_for(gr.index, plan.seq_slot) for gr in self.cache.groups]
-        ctx = g.buffers.upload(plan, tables)
+        key = tuple(s.slot for s in seqs)
+        if key == g.key and g.version == self.cache.version:
+            # the same sequences one token further: only tokens and positions change
+            g.buffers.update_decode([s.tokens[0] for s in seqs], starts, B)
+            ctx = g.ctx
+        else:
+            plan = build_plan(seqs, starts, pad_seqs=bucket, pad_tokens=bucket, want_all_rows=True)
+            tables = [self.cache.tables_for(gr.index, plan.seq_slot) for gr in self.cache.groups]
+            ctx = g.buffers.upload(plan, tables)
+            g.key, g.ctx, g.version = key, ctx, self.cache.version
         self.last_h2d_bytes = g.buffers.bytes()
         g.runs += 1
         if g.graph is None and g.runs == 1:

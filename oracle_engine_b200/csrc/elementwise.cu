@@ -47,6 +47,59 @@ __global__ void rmsnorm_kernel(T* __restrict__ y, const float* __restrict__ x,
     for (int d = threadIdx.x; d < D; d += blockDim.x) yr[d] = from_f32<T>((xr[d] * s) * w[d]);
 }
 
+// The same with 16-byte loads, for D a multiple of 4: each thread keeps its first chunks in
+// registers, so the row is read once.  The order of the sum is fixed by D and the block
+// size, not by the batch.
+template <typename T> struct Out4;
+template <> struct Out4<float> {
+    static __device__ __forceinline__ void store(float* p, float a, float b, float c, float d) { *(float4*)p = make_float4(a, b, c, d); }
+};
+template <> struct Out4<bf16> {
+    static __device__ __forceinline__ void store(bf16* p, float a, float b, float c, float d) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+        *(uint2*)p = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+    }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rmsnorm_vec_kernel(T* __restrict__ y, const float* __restrict__ x, const float* __restrict__ w, int D, float eps) {
+    __shared__ float red[32];
+    constexpr int KEEP = 4;
+    pdl_launch_dependents();
+    pdl_wait();
+    const float4* xr = (const float4*)(x + (size_t)blockIdx.x * D);
+    const float4* wr = (const float4*)w;
+    T* yr = y + (size_t)blockIdx.x * D;
+    const int n4 = D / 4;
+    float4 keep[KEEP];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < KEEP; j++) {
+        const int i = threadIdx.x + j * 256;
+        keep[j] = i < n4 ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        ss += keep[j].x * keep[j].x + keep[j].y * keep[j].y + keep[j].z * keep[j].z + keep[j].w * keep[j].w;
+    }
+    for (int i = threadIdx.x + KEEP * 256; i < n4; i += 256) {
+        const float4 v = xr[i];
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = block_sum(ss, red);
+    const float s = 1.f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+    for (int j = 0; j < KEEP; j++) {
+        const int i = threadIdx.x + j * 256;
+        if (i < n4) {
+            const float4 g = wr[i];
+            Out4<T>::store(yr + 4 * i, (keep[j].x * s) * g.x, (keep[j].y * s) * g.y, (keep[j].z * s) * g.z, (keep[j].w * s) * g.w);
+        }
+    }
+    for (int i = threadIdx.x + KEEP * 256; i < n4; i += 256) {
+        const float4 v = xr[i], g = wr[i];
+        Out4<T>::store(yr + 4 * i, (v.x * s) * g.x, (v.y * s) * g.y, (v.z * s) * g.z, (v.w * s) * g.w);
+    }
+}
+
 // ---------------------------------------------------------------------------------------
 // Rotary encoding of q and k (rotate-half pairs (i, i+hd/2)) at each token's absolute
 // position, from a float32 cos/sin table [max_pos, hd/2]; q is rotated in place, rotated
@@ -103,6 +156,85 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride,
     }
 }
 
+// The same with 16-byte accesses: a work item is VEC consecutive pairs (i, i + hd/2) of one
+// head.  Needs hd/2 and the row stride to be multiples of VEC = 16 / sizeof(T).
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4]) { const float4 t = *(const float4*)p; v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w; }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[4]) { *(float4*)p = make_float4(v[0], v[1], v[2], v[3]); }
+};
+template <> struct Vec16<bf16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const bf16* p, float (&v)[8]) {
+        const uint4 t = *(const uint4*)p;
+        const uint32_t r[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) { const __nv_bfloat162 h = *(const __nv_bfloat162*)&r[j]; v[2 * j] = __low2float(h); v[2 * j + 1] = __high2float(h); }
+    }
+    static __device__ __forceinline__ void store(bf16* p, const float (&v)[8]) {
+        uint32_t r[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) { __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]); r[j] = *(uint32_t*)&h; }
+        *(uint4*)p = make_uint4(r[0], r[1], r[2], r[3]);
+    }
+};
+
+template <typename T>
+__global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, int row_stride,
+                                         const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
+                                         T* __restrict__ cache, const int* __restrict__ tables, int max_pages,
+                                         const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                                         int H, int KVH, int hd, int has_kv, int rotate) {
+    constexpr int V = Vec16<T>::N;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int b = tok_seq[t];
+    if (b < 0) return;
+    const int pos = tok_pos[t];
+    const int half = hd / 2, per_head = half / V;
+    T* row = qkv + (size_t)t * row_stride;
+    const float* cs = cos_tab + (size_t)pos * half;
+    const float* sn = sin_tab + (size_t)pos * half;
+    const int n_q = H * per_head, n_k = has_kv ? KVH * per_head : 0;
+    const int* trow = tables + (size_t)b * max_pages;
+    for (int idx = threadIdx.x; idx < n_q + n_k; idx += blockDim.x) {
+        const bool is_k = idx >= n_q;
+        const int h = (is_k ? idx - n_q : idx) / per_head, i = ((is_k ? idx - n_q : idx) % per_head) * V;
+        const T* src = row + (size_t)(is_k ? H + h : h) * hd;
+        float x0[V], x1[V], y0[V], y1[V];
+        Vec16<T>::load(src + i, x0);
+        Vec16<T>::load(src + i + half, x1);
+        if (rotate) {
+#pragma unroll
+            for (int j = 0; j < V; j++) {
+                const float c = cs[i + j], s = sn[i + j];
+                y0[j] = x0[j] * c - x1[j] * s;
+                y1[j] = x0[j] * s + x1[j] * c;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < V; j++) { y0[j] = x0[j]; y1[j] = x1[j]; }
+        }
+        if (!is_k) {
+            if (rotate) {
+                Vec16<T>::store(row + (size_t)h * hd + i, y0);
+                Vec16<T>::store(row + (size_t)h * hd + i + half, y1);
+            }
+        } else {
+            const long long ko = page_row_offset(trow, pos, 0, h, KVH, hd);
+            const long long vo = page_row_offset(trow, pos, 1, h, KVH, hd);
+            if (ko < 0) continue;
+            Vec16<T>::store(cache + ko + i, y0);
+            Vec16<T>::store(cache + ko + i + half, y1);
+            const T* vsrc = row + (size_t)(H + KVH + h) * hd;
+            *(uint4*)(cache + vo + i) = *(const uint4*)(vsrc + i);
+            *(uint4*)(cache + vo + i + half) = *(const uint4*)(vsrc + i + half);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------
 // a = g / (1 + exp(-g)) * u, with gu = [g | u] per row   (reference: core/model.cpp:638-641)
 // ---------------------------------------------------------------------------------------
@@ -150,11 +282,15 @@ int oe_embed_gather_bf16(float* x, const bf16* table, const int* ids, int n_toke
 
 int oe_rmsnorm_f32(float* y, const float* x, const float* w, int rows, int D, float eps, cudaStream_t st) {
     if (rows <= 0) return 0;
+    if (D % 4 == 0 && !(((uintptr_t)y | (uintptr_t)x | (uintptr_t)w) & 15))
+        return oe_launch(rmsnorm_vec_kernel<float>, dim3(rows), dim3(256), 0, st, y, x, w, D, eps);
     const int launch_rc = oe_launch(rmsnorm_kernel<float>, dim3(rows), dim3(256), 0, st, y, x, w, D, eps);
     return launch_rc;
 }
 int oe_rmsnorm_bf16(bf16* y, const float* x, const float* w, int rows, int D, float eps, cudaStream_t st) {
     if (rows <= 0) return 0;
+    if (D % 4 == 0 && !(((uintptr_t)x | (uintptr_t)w) & 15) && !((uintptr_t)y & 7))
+        return oe_launch(rmsnorm_vec_kernel<bf16>, dim3(rows), dim3(256), 0, st, y, x, w, D, eps);
     const int launch_rc = oe_launch(rmsnorm_kernel<bf16>, dim3(rows), dim3(256), 0, st, y, x, w, D, eps);
     return launch_rc;
 }
@@ -165,6 +301,9 @@ int oe_rope_kv_write_f32(float* qkv, int row_stride, const float* cos_tab, const
                          cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (hd % 2) return OE_ERR_UNSUPPORTED;
+    if ((hd / 2) % 4 == 0 && row_stride % 4 == 0 && !(((uintptr_t)qkv | (uintptr_t)cache) & 15))
+        return oe_launch(rope_kv_write_vec_kernel<float>, dim3(n_tokens), dim3(256), 0, st, qkv, row_stride, cos_tab, sin_tab,
+                         cache, tables, max_pages, tok_seq, tok_pos, H, KVH, hd, has_kv, rotate);
     const int launch_rc = oe_launch(rope_kv_write_kernel<float>, dim3(n_tokens), dim3(256), 0, st, qkv, row_stride, cos_tab, sin_tab, cache, tables,
                                                            max_pages, tok_seq, tok_pos, H, KVH, hd, has_kv, rotate);
     return launch_rc;
@@ -175,6 +314,9 @@ int oe_rope_kv_write_bf16(bf16* qkv, int row_stride, const float* cos_tab, const
                           cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (hd % 2) return OE_ERR_UNSUPPORTED;
+    if ((hd / 2) % 8 == 0 && row_stride % 8 == 0 && !(((uintptr_t)qkv | (uintptr_t)cache) & 15))
+        return oe_launch(rope_kv_write_vec_kernel<bf16>, dim3(n_tokens), dim3(256), 0, st, qkv, row_stride, cos_tab, sin_tab,
+                         cache, tables, max_pages, tok_seq, tok_pos, H, KVH, hd, has_kv, rotate);
     const int launch_rc = oe_launch(rope_kv_write_kernel<bf16>, dim3(n_tokens), dim3(256), 0, st, qkv, row_stride, cos_tab, sin_tab, cache, tables,
                                                           max_pages, tok_seq, tok_pos, H, KVH, hd, has_kv, rotate);
     return launch_rc;

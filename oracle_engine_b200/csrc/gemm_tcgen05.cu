@@ -481,7 +481,18 @@ int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, 
         grid = dim3(tiles_a, 1, splits);
     } else {
         g.swap = 0;
-        g.n_tile = N >= 256 ? 256 : ((N + 15) / 16) * 16;
+        if (N < 256) {
+            g.n_tile = ((N + 15) / 16) * 16;
+        } else {
+            // tile width that wastes the least in the last wave of CTAs (one CTA per SM)
+            const int tiles_m = (M + BLOCK_M - 1) / BLOCK_M;
+            long long best = -1;
+            for (int nt = 256; nt >= 128; nt -= 64) {
+                const long long tiles = (long long)tiles_m * ((N + nt - 1) / nt);
+                const long long cost = ((tiles + sm_count - 1) / sm_count) * nt;
+                if (best < 0 || cost < best) { best = cost; g.n_tile = nt; }
+            }
+        }
         g.rows_a = M; g.rows_b = N;
         if ((rc = make_map(&map_a, A, M, K, lda, BLOCK_M))) return rc;
         if ((rc = make_map(&map_b, W, N, K, K, g.n_tile))) return rc;

@@ -52,6 +52,7 @@ struct AttnArgs {
     const float* sin_tab;
     bf16* cache_w;             // the cache entry, writable, when this call stores the new k, v; else null
     int* counters;             // [B * KVH] zeros (n_splits > 1)
+    int stages;                // K/V tiles staged ahead: 2 (double buffer) or 1
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -182,14 +183,15 @@ attn_mma_kernel(const AttnArgs a) {
     cp_async_commit();
     for (int it = 0; it < n_blocks; it++) {
         const int j = j_lo + it;
-        uint8_t* ks_cur = smem + (size_t)(it & 1) * 2 * TILE_BYTES;
+        const bool dbl = a.stages > 1;
+        uint8_t* ks_cur = smem + (size_t)(dbl ? (it & 1) : 0) * 2 * TILE_BYTES;
         uint8_t* vs_cur = ks_cur + TILE_BYTES;
-        if (it + 1 < n_blocks) {
+        if (dbl && it + 1 < n_blocks) {
             uint8_t* nxt = smem + (size_t)((it + 1) & 1) * 2 * TILE_BYTES;
             load_page<NWARPS * 32>(nxt, nxt + TILE_BYTES, a.cache, trow[j + 1], kvh, a.KVH);
         }
         cp_async_commit();
-        cp_async_wait<1>();
+        if (dbl) cp_async_wait<1>(); else cp_async_wait<0>();
         __syncthreads();
 
         if (a.fused && a.cache_w != nullptr && j == pos_hi / BN) {
@@ -292,6 +294,8 @@ attn_mma_kernel(const AttnArgs a) {
             }
         }
         __syncthreads();
+        if (!dbl && it + 1 < n_blocks)
+            load_page<NWARPS * 32>(smem, smem + TILE_BYTES, a.cache, trow[j + 1], kvh, a.KVH);
     }
     cp_async_wait<0>();
 
@@ -332,7 +336,8 @@ attn_mma_kernel(const AttnArgs a) {
             if (s_last) {
                 __threadfence();
                 // weights of every (head, split) first, then all value loads of a thread at once
-                __shared__ float s_m[64 * 32], s_l[64 * 32];
+                float* s_m = (float*)(smem + (size_t)a.stages * 2 * TILE_BYTES);
+                float* s_l = s_m + 64 * 32;
                 const int ns = a.n_splits;
                 const float* pbase = a.partial + ((packed0 * a.H + (long long)kvh * G) * ns) * (long long)(HD + 2);
                 for (int idx = threadIdx.x; idx < G * ns; idx += blockDim.x) {
@@ -408,10 +413,11 @@ __global__ void attn_merge_kernel(bf16* __restrict__ out, const float* __restric
 
 template <int NWARPS>
 int launch(const AttnArgs& a, int n_seqs, int grid_x, cudaStream_t st) {
-    const size_t smem = 4 * (size_t)TILE_BYTES;
+    const size_t smem = (size_t)a.stages * 2 * TILE_BYTES + (a.fused && a.n_splits > 1 ? 2 * 64 * 32 * sizeof(float) : 0);
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(attn_mma_kernel<NWARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_mma_kernel<NWARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)(4 * TILE_BYTES + 2 * 64 * 32 * sizeof(float)));
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
@@ -419,6 +425,12 @@ int launch(const AttnArgs& a, int n_seqs, int grid_x, cudaStream_t st) {
     const int launch_rc = oe_launch(attn_mma_kernel<NWARPS>, dim3(grid), dim3(NWARPS * 32), smem, st, a);
     return launch_rc;
 }
+
+// One-warp CTAs (decoded tokens).  A large batch, where each CTA walks all pages of its
+// sequence: a single staged page per CTA lets twice as many CTAs share an SM, which hides
+// a page's load behind the other CTAs' work (measured 38 vs 44 us at batch 64).  A small
+// batch split over the keys: few pages per CTA, the double buffer wins (11 vs 13 us at 8).
+int decode_stages(int n_splits) { return n_splits > 1 ? 2 : 1; }
 
 }  // namespace
 
@@ -447,6 +459,7 @@ int oe_attn_mma_bf16(bf16* out, const bf16* q, long long q_stride, const bf16* c
     a.scale_log2 = scale * 1.4426950408889634f;
     a.partial = partial;
     a.fused = 0; a.cos_tab = nullptr; a.sin_tab = nullptr; a.cache_w = nullptr; a.counters = nullptr;
+    a.stages = 2;
     // rows per sequence tile: 16 per warp; few rows (decode) use fewer warps
     const long long rows_needed = (long long)max_qlen * G;
     int nwarps = rows_needed <= 16 ? 1 : (rows_needed <= 32 ? 2 : 4);
@@ -455,6 +468,7 @@ int oe_attn_mma_bf16(bf16* out, const bf16* q, long long q_stride, const bf16* c
     const int n_q_tiles = (max_qlen + a.tokens_per_tile - 1) / a.tokens_per_tile;
     if (n_splits > 1 && (n_q_tiles > 1 || partial == nullptr)) n_splits = 1;
     a.n_splits = n_splits < 1 ? 1 : n_splits;
+    if (nwarps == 1 && max_qlen == 1) a.stages = decode_stages(a.n_splits);
     const int grid_x = a.n_splits > 1 ? a.n_splits : n_q_tiles;
     int rc;
     if (nwarps == 1) rc = launch<1>(a, n_seqs, grid_x, st);
@@ -491,6 +505,7 @@ int oe_attn_decode_fused_bf16(bf16* out, const bf16* qkv, long long qkv_stride, 
     int nwarps = G <= 16 ? 1 : (G <= 32 ? 2 : 4);
     a.tokens_per_tile = (nwarps * 16) / G;
     a.n_splits = n_splits < 1 ? 1 : n_splits;
+    a.stages = nwarps == 1 ? decode_stages(a.n_splits) : 2;
     if (nwarps == 1) return launch<1>(a, n_seqs, a.n_splits, st);
     if (nwarps == 2) return launch<2>(a, n_seqs, a.n_splits, st);
     return launch<4>(a, n_seqs, a.n_splits, st);

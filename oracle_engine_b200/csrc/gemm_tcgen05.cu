@@ -38,7 +38,8 @@ __device__ int g_error = 0;        // 0 = ok; else code of the wait that ran out
 struct SharedCtl {
     uint64_t full[12];
     uint64_t empty[12];
-    uint64_t tmem_full;
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
     uint32_t tmem_base;
     int abort_flag;
     int is_last;
@@ -138,6 +139,7 @@ struct GemmArgs {
     int swap;                   // 1: C[b_row, a_row] (A = weights); 0: C[a_row, b_row] (A = activations)
     int out_kind;               // 0 bf16 store, 1 float32 store, 2 float32 accumulate, 3 bf16 silu(gate)*up
     int splits;
+    int tiles_a, tiles_b;       // output tiles along the A and the B operand
     float* workspace;           // [splits][tiles_a][tiles_b][n_tile][128] float32 when splits > 1
     int* counters;              // [tiles_a * tiles_b], zero between launches
 };
@@ -234,18 +236,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     SharedCtl* ctl = (SharedCtl*)(smem + (size_t)g.stages * stage_bytes);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile_a = blockIdx.x, tile_b = blockIdx.y, split = blockIdx.z;
+    // Work items (output tile x K split), taken round robin by the resident CTAs.  A-tiles
+    // vary fastest, so CTAs that run together share the B tile in L2.
+    const int tiles_a = g.tiles_a, tiles_b = g.tiles_b;
+    const int n_work = tiles_a * tiles_b * g.splits;
     const int n_kb_total = (g.K + BLOCK_K - 1) / BLOCK_K;
     const int kb_per = (n_kb_total + g.splits - 1) / g.splits;
-    const int kb0 = split * kb_per;
-    const int kb1 = min(n_kb_total, kb0 + kb_per);
-    const int n_kb = max(0, kb1 - kb0);
     uint32_t tmem_cols = 32;
-    while ((int)tmem_cols < g.n_tile) tmem_cols <<= 1;
+    while ((int)tmem_cols < 2 * g.n_tile) tmem_cols <<= 1;          // two accumulators
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < g.stages; s++) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
-        mbar_init(&ctl->tmem_full, 1);
+        for (int b = 0; b < 2; b++) { mbar_init(&ctl->tmem_full[b], 1); mbar_init(&ctl->tmem_empty[b], 4); }
         ctl->abort_flag = 0;
         ctl->is_last = 0;
         ctl->epi_ok = 1;
@@ -264,82 +266,104 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         // The weight operand (A when swapped, else B) does not depend on earlier kernels:
-        // its first tiles are requested before pdl_wait(), the activation tiles after it.
+        // the first stages' weight tiles are requested before pdl_wait(), the activation
+        // tiles after it.
         if (lane == 0) {
-            const int first = min(n_kb, g.stages);
-            for (int i = 0; i < first; i++) {
-                uint8_t* a_dst = smem + (size_t)i * stage_bytes;
-                mbar_expect_tx(&ctl->full[i], (uint32_t)(A_TILE_BYTES + b_tile_bytes));
-                if (g.swap) tma_load_2d(a_dst, &map_a, &ctl->full[i], (kb0 + i) * BLOCK_K, tile_a * BLOCK_M);
-                else tma_load_2d(a_dst + A_TILE_BYTES, &map_b, &ctl->full[i], (kb0 + i) * BLOCK_K, tile_b * g.n_tile);
-            }
-            pdl_wait();
-            for (int i = 0; i < first; i++) {
-                uint8_t* a_dst = smem + (size_t)i * stage_bytes;
-                if (g.swap) tma_load_2d(a_dst + A_TILE_BYTES, &map_b, &ctl->full[i], (kb0 + i) * BLOCK_K, tile_b * g.n_tile);
-                else tma_load_2d(a_dst, &map_a, &ctl->full[i], (kb0 + i) * BLOCK_K, tile_a * BLOCK_M);
-            }
-            for (int i = first; i < n_kb; i++) {
-                const int s = i % g.stages;
-                const uint32_t phase = (uint32_t)(i / g.stages) & 1u;
-                if (!mbar_wait(&ctl->empty[s], phase ^ 1u, ctl, 1)) break;
-                uint8_t* a_dst = smem + (size_t)s * stage_bytes;
-                uint8_t* b_dst = a_dst + A_TILE_BYTES;
-                mbar_expect_tx(&ctl->full[s], (uint32_t)(A_TILE_BYTES + b_tile_bytes));
-                tma_load_2d(a_dst, &map_a, &ctl->full[s], (kb0 + i) * BLOCK_K, tile_a * BLOCK_M);
-                tma_load_2d(b_dst, &map_b, &ctl->full[s], (kb0 + i) * BLOCK_K, tile_b * g.n_tile);
+            int it = 0;                                         // k-blocks issued so far, over all work items
+            bool waited = false, ok = true;
+            for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+                const int split = w / (tiles_a * tiles_b), rem = w % (tiles_a * tiles_b);
+                const int tile_b = rem / tiles_a, tile_a = rem % tiles_a;
+                const int kb0 = split * kb_per;
+                const int n_kb = min(n_kb_total, kb0 + kb_per) - kb0;
+                int i = 0;
+                if (!waited) {
+                    const int first = min(n_kb, g.stages);
+                    for (; i < first; i++) {
+                        uint8_t* a_dst = smem + (size_t)i * stage_bytes;
+                        mbar_expect_tx(&ctl->full[i], (uint32_t)(A_TILE_BYTES + b_tile_bytes));
+                        if (g.swap) tma_load_2d(a_dst, &map_a, &ctl->full[i], (kb0 + i) * BLOCK_K, tile_a * BLOCK_M);
+                        else tma_load_2d(a_dst + A_TILE_BYTES, &map_b, &ctl->full[i], (kb0 + i) * BLOCK_K, tile_b * g.n_tile);
+                    }
+                    pdl_wait();
+                    waited = true;
+                    for (int j = 0; j < first; j++) {
+                        uint8_t* a_dst = smem + (size_t)j * stage_bytes;
+                        if (g.swap) tma_load_2d(a_dst + A_TILE_BYTES, &map_b, &ctl->full[j], (kb0 + j) * BLOCK_K, tile_b * g.n_tile);
+                        else tma_load_2d(a_dst, &map_a, &ctl->full[j], (kb0 + j) * BLOCK_K, tile_a * BLOCK_M);
+                    }
+                    it = first;
+                }
+                for (; i < n_kb; i++, it++) {
+                    const int s = it % g.stages;
+                    const uint32_t phase = (uint32_t)(it / g.stages) & 1u;
+                    if (!mbar_wait(&ctl->empty[s], phase ^ 1u, ctl, 1)) { ok = false; break; }
+                    uint8_t* a_dst = smem + (size_t)s * stage_bytes;
+                    mbar_expect_tx(&ctl->full[s], (uint32_t)(A_TILE_BYTES + b_tile_bytes));
+                    tma_load_2d(a_dst, &map_a, &ctl->full[s], (kb0 + i) * BLOCK_K, tile_a * BLOCK_M);
+                    tma_load_2d(a_dst + A_TILE_BYTES, &map_b, &ctl->full[s], (kb0 + i) * BLOCK_K, tile_b * g.n_tile);
+                }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issue ----------------
         if (lane == 0) {
             const uint32_t idesc = umma_idesc(BLOCK_M, g.n_tile);
+            int it = 0, lt = 0;
             bool ok = true;
-            for (int i = 0; i < n_kb && ok; i++) {
-                const int s = i % g.stages;
-                const uint32_t phase = (uint32_t)(i / g.stages) & 1u;
-                ok = mbar_wait(&ctl->full[s], phase, ctl, 2);
-                if (!ok) break;
+            for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, lt++) {
+                const int split = w / (tiles_a * tiles_b);
+                const int kb0 = split * kb_per;
+                const int n_kb = min(n_kb_total, kb0 + kb_per) - kb0;
+                const int buf = lt & 1;
+                // the epilogue must have read this accumulator (two work items ago)
+                if (!mbar_wait(&ctl->tmem_empty[buf], ((uint32_t)(lt >> 1) & 1u) ^ 1u, ctl, 4)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_addr = smem_u32(smem + (size_t)s * stage_bytes);
-                const uint32_t b_addr = a_addr + A_TILE_BYTES;
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * g.n_tile);
+                for (int i = 0; i < n_kb; i++, it++) {
+                    const int s = it % g.stages;
+                    const uint32_t phase = (uint32_t)(it / g.stages) & 1u;
+                    if (!mbar_wait(&ctl->full[s], phase, ctl, 2)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = smem_u32(smem + (size_t)s * stage_bytes);
+                    const uint32_t b_addr = a_addr + A_TILE_BYTES;
 #pragma unroll
-                for (int k = 0; k < BLOCK_K / UMMA_K; k++) {
-                    umma_bf16(tmem_base, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc,
-                              (i > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BLOCK_K / UMMA_K; k++) {
+                        umma_bf16(tmem_d, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc,
+                                  (i > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&ctl->empty[s]);          // frees the stage when these MMAs have read it
                 }
-                umma_commit(&ctl->empty[s]);          // frees the stage when these MMAs have read it
+                umma_commit(&ctl->tmem_full[buf]);        // this accumulator is complete
             }
-            umma_commit(&ctl->tmem_full);             // accumulator complete (also arrives if n_kb == 0)
         }
     } else {
         // ---------------- epilogue: warps 2..5 ----------------
         const int quarter = warp & 3;                 // TMEM lanes 32*quarter .. +31 belong to this warp
         const int row = quarter * 32 + lane;          // row of the A tile
-        const int a_row = tile_a * BLOCK_M + row;
-        // every epilogue thread takes the same decision, so that all of them reach the
-        // named barriers below
-        if (!mbar_wait(&ctl->tmem_full, 0, ctl, 3)) atomicExch(&ctl->epi_ok, 0);
-        pdl_wait();                                   // before the first access to C, workspace, counters
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        const bool ok = *(volatile int*)&ctl->epi_ok != 0;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok) {
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-            const int tiles_a = gridDim.x, tiles_b = gridDim.y;
+        int lt = 0;
+        bool first = true;
+        for (int w = blockIdx.x; w < n_work; w += gridDim.x, lt++) {
+            const int split = w / (tiles_a * tiles_b), rem = w % (tiles_a * tiles_b);
+            const int tile_b = rem / tiles_a, tile_a = rem % tiles_a;
+            const int a_row = tile_a * BLOCK_M + row;
+            const int buf = lt & 1;
+            // every epilogue thread takes the same decision, so that all of them reach the
+            // named barriers below
+            if (!mbar_wait(&ctl->tmem_full[buf], (uint32_t)(lt >> 1) & 1u, ctl, 3)) atomicExch(&ctl->epi_ok, 0);
+            if (first) { pdl_wait(); first = false; }     // before the first access to C, workspace, counters
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (*(volatile int*)&ctl->epi_ok == 0) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * g.n_tile);
             const size_t tile_off = (((size_t)tile_a * tiles_b + tile_b) * (size_t)g.n_tile) * BLOCK_M + row;
             const size_t split_stride = (size_t)tiles_a * tiles_b * g.n_tile * BLOCK_M;
             for (int c0 = 0; c0 < g.n_tile; c0 += 16) {
                 float v[16];
-                if (n_kb > 0) {
-                    uint32_t r[16];
-                    tmem_ld16(taddr + (uint32_t)c0, r);
+                uint32_t r[16];
+                tmem_ld16(taddr + (uint32_t)c0, r);
 #pragma unroll
-                    for (int j = 0; j < 16; j++) v[j] = __uint_as_float(r[j]);
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 16; j++) v[j] = 0.f;
-                }
+                for (int j = 0; j < 16; j++) v[j] = __uint_as_float(r[j]);
                 if (g.splits > 1) {
                     float* part = g.workspace + (size_t)split * split_stride + tile_off + (size_t)c0 * BLOCK_M;
 #pragma unroll
@@ -348,6 +372,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     emit<16>(g, a_row, tile_b * g.n_tile + c0, v);
                 }
             }
+            // the accumulator has been read: the MMA warp may reuse it
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&ctl->tmem_empty[buf])) : "memory");
             if (g.splits > 1) {
                 // the CTA that arrives last adds the partial sums in split order
                 __threadfence();
@@ -378,6 +406,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     }
                     if (warp == 2 && lane == 0) g.counters[tile_id] = 0;
                 }
+                asm volatile("bar.sync 1, 128;" ::: "memory");      // is_last is rewritten by the next item
             }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -478,7 +507,7 @@ int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, 
         g.splits = splits;
         if ((rc = make_map(&map_a, W, N, K, K, BLOCK_M))) return rc;
         if ((rc = make_map(&map_b, A, M, K, lda, g.n_tile))) return rc;
-        grid = dim3(tiles_a, 1, splits);
+        g.tiles_a = tiles_a; g.tiles_b = 1;
     } else {
         g.swap = 0;
         if (N < 256) {
@@ -496,9 +525,12 @@ int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, 
         g.rows_a = M; g.rows_b = N;
         if ((rc = make_map(&map_a, A, M, K, lda, BLOCK_M))) return rc;
         if ((rc = make_map(&map_b, W, N, K, K, g.n_tile))) return rc;
-        grid = dim3((M + BLOCK_M - 1) / BLOCK_M, (N + g.n_tile - 1) / g.n_tile, 1);
-        if (grid.y > 65535) return OE_ERR_UNSUPPORTED;
+        g.tiles_a = (M + BLOCK_M - 1) / BLOCK_M;
+        g.tiles_b = (N + g.n_tile - 1) / g.n_tile;
     }
+    const long long n_work = (long long)g.tiles_a * g.tiles_b * g.splits;
+    if (n_work > 2147483647LL) return OE_ERR_UNSUPPORTED;
+    grid = dim3((unsigned)(n_work < sm_count ? n_work : sm_count));
     const int b_tile_bytes = g.n_tile * BLOCK_K * 2;
     const int stage_bytes = A_TILE_BYTES + ((b_tile_bytes + 1023) & ~1023);
     int stages = (200 * 1024) / stage_bytes;

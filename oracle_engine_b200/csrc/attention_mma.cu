@@ -92,8 +92,8 @@ __device__ __forceinline__ void load_page(uint8_t* ks, uint8_t* vs, const bf16* 
     }
 }
 
-template <int NWARPS>
-__global__ void __launch_bounds__(NWARPS * 32)
+template <int NWARPS, int STAGES>
+__global__ void __launch_bounds__(NWARPS * 32, NWARPS == 4 ? 2 : 1)
 attn_mma_kernel(const AttnArgs a) {
     extern __shared__ __align__(16) uint8_t smem[];
     pdl_launch_dependents();
@@ -183,7 +183,7 @@ attn_mma_kernel(const AttnArgs a) {
     cp_async_commit();
     for (int it = 0; it < n_blocks; it++) {
         const int j = j_lo + it;
-        const bool dbl = a.stages > 1;
+        constexpr bool dbl = STAGES > 1;
         uint8_t* ks_cur = smem + (size_t)(dbl ? (it & 1) : 0) * 2 * TILE_BYTES;
         uint8_t* vs_cur = ks_cur + TILE_BYTES;
         if (dbl && it + 1 < n_blocks) {
@@ -224,15 +224,25 @@ attn_mma_kernel(const AttnArgs a) {
         float sacc[BN / 8][4];
 #pragma unroll
         for (int n = 0; n < BN / 8; n++) { sacc[n][0] = sacc[n][1] = sacc[n][2] = sacc[n][3] = 0.f; }
+        {
+            // K fragments of the next k-step are loaded while the current one multiplies
+            const int m = lane >> 3, r = lane & 7;
+            const uint8_t* kbase = ks_cur + ((m >> 1) * 8 + r) * ROW_BYTES + (m & 1) * 16;
+            uint32_t kb[2][BN / 16][4];
 #pragma unroll
-        for (int ks = 0; ks < KS; ks++) {
+            for (int np = 0; np < BN / 16; np++) ldmatrix_x4(kb[0][np], kbase + np * 16 * ROW_BYTES);
 #pragma unroll
-            for (int np = 0; np < BN / 16; np++) {
-                uint32_t kb[4];
-                const int m = lane >> 3, r = lane & 7;
-                ldmatrix_x4(kb, ks_cur + (np * 16 + (m >> 1) * 8 + r) * ROW_BYTES + (ks * 2 + (m & 1)) * 16);
-                mma_bf16(sacc[2 * np], qf[ks], kb[0], kb[1]);
-                mma_bf16(sacc[2 * np + 1], qf[ks], kb[2], kb[3]);
+            for (int ks = 0; ks < KS; ks++) {
+                if (ks + 1 < KS) {
+#pragma unroll
+                    for (int np = 0; np < BN / 16; np++)
+                        ldmatrix_x4(kb[(ks + 1) & 1][np], kbase + np * 16 * ROW_BYTES + (ks + 1) * 32);
+                }
+#pragma unroll
+                for (int np = 0; np < BN / 16; np++) {
+                    mma_bf16(sacc[2 * np], qf[ks], kb[ks & 1][np][0], kb[ks & 1][np][1]);
+                    mma_bf16(sacc[2 * np + 1], qf[ks], kb[ks & 1][np][2], kb[ks & 1][np][3]);
+                }
             }
         }
         // scale, mask, online softmax
@@ -284,13 +294,17 @@ attn_mma_kernel(const AttnArgs a) {
             pa[1] = pack_bf16(sacc[2 * kk][2], sacc[2 * kk][3]);
             pa[2] = pack_bf16(sacc[2 * kk + 1][0], sacc[2 * kk + 1][1]);
             pa[3] = pack_bf16(sacc[2 * kk + 1][2], sacc[2 * kk + 1][3]);
-#pragma unroll
-            for (int dp = 0; dp < KS; dp++) {
-                uint32_t vb[4];
+            {
                 const int m = lane >> 3, r = lane & 7;
-                ldmatrix_x4_trans(vb, vs_cur + (kk * 16 + (m & 1) * 8 + r) * ROW_BYTES + (dp * 2 + (m >> 1)) * 16);
-                mma_bf16(oacc[2 * dp], pa, vb[0], vb[1]);
-                mma_bf16(oacc[2 * dp + 1], pa, vb[2], vb[3]);
+                const uint8_t* vbase = vs_cur + (kk * 16 + (m & 1) * 8 + r) * ROW_BYTES + (m >> 1) * 16;
+                uint32_t vb[2][4];
+                ldmatrix_x4_trans(vb[0], vbase);
+#pragma unroll
+                for (int dp = 0; dp < KS; dp++) {
+                    if (dp + 1 < KS) ldmatrix_x4_trans(vb[(dp + 1) & 1], vbase + (dp + 1) * 32);
+                    mma_bf16(oacc[2 * dp], pa, vb[dp & 1][0], vb[dp & 1][1]);
+                    mma_bf16(oacc[2 * dp + 1], pa, vb[dp & 1][2], vb[dp & 1][3]);
+                }
             }
         }
         __syncthreads();
@@ -336,7 +350,7 @@ attn_mma_kernel(const AttnArgs a) {
             if (s_last) {
                 __threadfence();
                 // weights of every (head, split) first, then all value loads of a thread at once
-                float* s_m = (float*)(smem + (size_t)a.stages * 2 * TILE_BYTES);
+                float* s_m = (float*)(smem + (size_t)STAGES * 2 * TILE_BYTES);
                 float* s_l = s_m + 64 * 32;
                 const int ns = a.n_splits;
                 const float* pbase = a.partial + ((packed0 * a.H + (long long)kvh * G) * ns) * (long long)(HD + 2);
@@ -411,19 +425,25 @@ __global__ void attn_merge_kernel(bf16* __restrict__ out, const float* __restric
     }
 }
 
-template <int NWARPS>
-int launch(const AttnArgs& a, int n_seqs, int grid_x, cudaStream_t st) {
-    const size_t smem = (size_t)a.stages * 2 * TILE_BYTES + (a.fused && a.n_splits > 1 ? 2 * 64 * 32 * sizeof(float) : 0);
+template <int NWARPS, int STAGES>
+int launch_staged(const AttnArgs& a, int n_seqs, int grid_x, cudaStream_t st) {
+    const size_t smem = (size_t)STAGES * 2 * TILE_BYTES + (a.fused && a.n_splits > 1 ? 2 * 64 * 32 * sizeof(float) : 0);
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(attn_mma_kernel<NWARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)(4 * TILE_BYTES + 2 * 64 * 32 * sizeof(float)));
+        cudaError_t e = cudaFuncSetAttribute(attn_mma_kernel<NWARPS, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)(STAGES * 2 * TILE_BYTES + 2 * 64 * 32 * sizeof(float)));
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
     dim3 grid(grid_x, a.KVH, n_seqs);
-    const int launch_rc = oe_launch(attn_mma_kernel<NWARPS>, dim3(grid), dim3(NWARPS * 32), smem, st, a);
+    const int launch_rc = oe_launch(attn_mma_kernel<NWARPS, STAGES>, dim3(grid), dim3(NWARPS * 32), smem, st, a);
     return launch_rc;
+}
+
+template <int NWARPS>
+int launch(const AttnArgs& a, int n_seqs, int grid_x, cudaStream_t st) {
+    if (NWARPS == 1 && a.stages == 1) return launch_staged<NWARPS, 1>(a, n_seqs, grid_x, st);
+    return launch_staged<NWARPS, 2>(a, n_seqs, grid_x, st);
 }
 
 // One-warp CTAs (decoded tokens).  A large batch, where each CTA walks all pages of its

@@ -46,6 +46,7 @@ _SIGNATURES = {
     },
     "sampling": {
         "oe_argmax_rows": [_P, _P, _I, _I, _P],
+        "oe_argmax_rows_wide": [_P, _P, _P, _P, _I, _I, _P],
         "oe_sample_rows": [_P, _P, _P, _I, _I, _F, _I, _F, _F, _I, _P, _P, _P, _P, _I, _I, _P],
     },
 }
@@ -215,11 +216,28 @@ def attn_paged(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, tables: 
         T, n_heads, n_kv_heads, head_dim, int(window), float(scale), _stream()), "attn_paged")
 
 
+_argmax_scratch: dict = {}
+
+
 def argmax_rows(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = index of the first maximum of row r (float32 logits)."""
     _dev(logits, out)
     _i32(out, "out")
     if logits.dtype != torch.float32 or not logits.is_contiguous():
         raise KernelError("argmax_rows: logits must be contiguous float32")
+    rows, V = logits.shape
+    if V >= 8192 and rows <= 4096:
+        # wide vocabulary: slices of a row on different SMs, then one warp per row
+        key = (logits.device.index, rows)
+        sc = _argmax_scratch.get(key)
+        if sc is None:
+            sc = (torch.empty(rows * 32, dtype=torch.float32, device=logits.device),
+                  torch.empty(rows * 32, dtype=torch.int32, device=logits.device))
+            _argmax_scratch[key] = sc
+        _check(_fn("sampling", "oe_argmax_rows_wide")(_ptr(logits), _ptr(out), _ptr(sc[0]), _ptr(sc[1]), rows, V,
+                                                      _stream()), "argmax_rows")
+        LAUNCHES[0] += 1
+        return
     _check(_fn("sampling", "oe_argmax_rows")(_ptr(logits), _ptr(out), logits.shape[0], logits.shape[1], _stream()),
            "argmax_rows")
 

@@ -69,6 +69,63 @@ argmax_rows_kernel(const float* __restrict__ logits, int* __restrict__ out, int 
     if (threadIdx.x == 0) out[blockIdx.x] = r;
 }
 
+// Two-stage first-maximum for wide rows: each block takes one slice of a row, then one warp
+// per row combines the slices (lowest index wins ties, as in block_argmax).
+constexpr int ARGMAX_SLICES = 32;
+
+__global__ void __launch_bounds__(256)
+argmax_partial_kernel(const float* __restrict__ logits, float* __restrict__ part_val, int* __restrict__ part_idx, int V) {
+    __shared__ float s_val[32];
+    __shared__ int s_idx[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.y, slice = blockIdx.x;
+    const int per = (V + ARGMAX_SLICES - 1) / ARGMAX_SLICES;
+    const int lo = slice * per, hi = min(V, lo + per);
+    const float* x = logits + (size_t)row * V;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float v = x[i];
+        if (v > best || bi == 0x7fffffff) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { s_val[warp] = best; s_idx[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        best = lane < (int)(blockDim.x >> 5) ? s_val[lane] : -INFINITY;
+        bi = lane < (int)(blockDim.x >> 5) ? s_idx[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (lane == 0) { part_val[row * ARGMAX_SLICES + slice] = best; part_idx[row * ARGMAX_SLICES + slice] = bi; }
+    }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx, int* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x, lane = threadIdx.x;
+    float best = part_val[row * ARGMAX_SLICES + lane];
+    int bi = part_idx[row * ARGMAX_SLICES + lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (lane == 0) out[row] = bi;
+}
+
 struct SampleState {
     const long long* rng_seed;   // [slots]
     int* rng_counter;            // [slots] draws made so far
@@ -208,6 +265,15 @@ sample_rows_kernel(float* __restrict__ logits, int* __restrict__ out, const int*
 }  // namespace
 
 extern "C" {
+
+// Wide rows in two stages; scratch: rows * 32 floats and rows * 32 ints.
+int oe_argmax_rows_wide(const float* logits, int* out, float* part_val, int* part_idx, int rows, int V, cudaStream_t st) {
+    if (rows <= 0) return 0;
+    if (V <= 0 || rows > 65535) return OE_ERR_UNSUPPORTED;
+    int rc = oe_launch(argmax_partial_kernel, dim3(ARGMAX_SLICES, rows), dim3(256), 0, st, logits, part_val, part_idx, V);
+    if (rc) return rc;
+    return oe_launch(argmax_final_kernel, dim3(rows), dim3(32), 0, st, (const float*)part_val, (const int*)part_idx, out);
+}
 
 int oe_argmax_rows(const float* logits, int* out, int rows, int V, cudaStream_t st) {
     if (rows <= 0) return 0;

@@ -285,6 +285,13 @@ def test_argmax_and_sampling():
     ops.argmax_rows(logits, out)
     assert out.tolist() == [pl.greedy(logits[r].cpu()) for r in range(R)] and out[2].item() == 100
 
+    wide = (torch.randn(5, 20011, generator=g) * 3).to(DEV)       # the two-stage kernel for wide rows
+    wide[1, 7] = wide[1, 20000] = 60.0
+    wide[3, 20010] = 70.0
+    out5 = torch.empty(5, dtype=torch.int32, device=DEV)
+    ops.argmax_rows(wide, out5)
+    assert out5.tolist() == wide.argmax(dim=1).tolist() and out5[1].item() == 7 and out5[3].item() == 20010
+
     n_slots = 8
     seeds = torch.arange(100, 100 + n_slots, dtype=torch.int64, device=DEV)
     row_slot = torch.tensor([5, 0, 7, 2, 3, 1], dtype=torch.int32, device=DEV)

@@ -30,7 +30,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: Llama 3.2 3B shape
+# The benchmark model: the Llama 3.2 3B shape (28 layers, hidden 3072, 24/8 heads of 128, FFN 8192, vocab 128256)
 LLAMA_3B = dict(architectures=["LlamaForCausalLM"], vocab_size=128256, hidden_size=3072, intermediate_size=8192,
                 num_hidden_layers=28, num_attention_heads=24, num_key_value_heads=8, head_dim=128,
                 rms_norm_eps=1e-5, rope_theta=500000.0,

@@ -16,7 +16,7 @@ epsilon 1e-5, which is what its norms use whatever the file says, core/ops.hpp:4
 The weights are a pure function of (config, seed), so the test regenerates them and only
 the token ids and the reference's logits are stored (`<case>.json`, `<case>.npy`).
 
-Usage:  python tests/golden/make_golden.py [/path/to/reference]
+Usage:  python tests/golden/make_golden.py /path/to/oracle-engine
 """
 import json
 import os
@@ -120,7 +120,9 @@ def write_gguf(path, cfg: dict, tensors: dict) -> None:
 
 
 def main():
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit(__doc__)
+    ref = Path(sys.argv[1])
     from oracle_engine_b200 import LlamaConfig, write_model_folder
     from oracle_engine_b200.weights.safetensors_io import ModelFiles
     with tempfile.TemporaryDirectory() as tmp:

@@ -32,7 +32,13 @@ TINY_C = dict(architectures=["LlamaForCausalLM"], vocab_size=331, hidden_size=12
                             "original_max_position_embeddings": 32},
               max_position_embeddings=384, tie_word_embeddings=False, eos_token_id=0)
 
-TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 5)}
+# sizes the tensor-core kernels refuse (width not a multiple of 8, head_dim not a multiple of 16):
+# the bfloat16 path must fall to the CUDA-core kernels and still be right
+TINY_D = dict(architectures=["LlamaForCausalLM"], vocab_size=257, hidden_size=100, intermediate_size=150,
+              num_hidden_layers=2, num_attention_heads=5, num_key_value_heads=5, head_dim=20, rms_norm_eps=1e-5,
+              rope_theta=10000.0, max_position_embeddings=256, tie_word_embeddings=True, eos_token_id=[1, 2, 3])
+
+TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 5), "D": (TINY_D, 8)}
 
 
 @pytest.fixture(scope="session")

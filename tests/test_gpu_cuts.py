@@ -32,7 +32,7 @@ def _check(got, plain, requests, tol, what):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_cuts_agree_with_plain(model_dirs, plain_models, tmp_path, name, dtype):
     from oracle_engine_b200.engine.engine import Engine
     plain = plain_models[name]

@@ -196,3 +196,48 @@ def test_command_line_generates_the_same_tokens(model_dirs, plain_models, tmp_pa
                               "--dtype", "float32", "--ignore-eos", "--no-stream"], capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
     assert [int(t) for t in r.stdout.split()] == got[0]          # seed 0 is the seed the folder was written with
+
+
+def test_real_widths_bfloat16_against_float32():
+    """Two layers with the widths of the benchmark model (hidden 3072, 24/8 heads of 128, FFN
+    8192, vocabulary 128256): the bfloat16 kernels at their real shapes (tcgen05 tiles, swap
+    and split paths, the weight-streaming kernel, the wide argmax) against the 32-bit path."""
+    from oracle_engine_b200 import GenParams, LlamaConfig, SequenceStep
+    from oracle_engine_b200.engine.engine import Engine
+    raw = dict(architectures=["LlamaForCausalLM"], vocab_size=128256, hidden_size=3072, intermediate_size=8192,
+               num_hidden_layers=2, num_attention_heads=24, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-5,
+               rope_theta=500000.0, rope_scaling={"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                                                  "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+               max_position_embeddings=4096, tie_word_embeddings=True)
+    cfg = LlamaConfig.from_dict(raw)
+    lens = [300, 17, 130, 64, 1, 70, 200, 33, 90, 129, 5, 260]            # 12 sequences: a batch above 8 too
+    prompts = [helpers.random_tokens(n, cfg.vocab_size, 200 + i) for i, n in enumerate(lens)]
+    feed = [helpers.random_tokens(4, cfg.vocab_size, 300 + i) for i in range(len(lens))]
+    outs = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.from_config(cfg, seed=3, dtype=dtype, max_tokens=12 * 384, norm_std=0.1)
+        got = []
+        for group in (range(0, 3), range(3, 12)):                         # 3 sequences, then 9
+            idx = list(group)
+            slots = [eng.alloc() for _ in idx]
+            lg = eng.step([SequenceStep(s, prompts[i], [len(prompts[i]) - 1]) for s, i in zip(slots, idx)])
+            step_logits = [lg.float().cpu()]
+            for t in range(4):
+                lg = eng.step([SequenceStep(s, [feed[i][t]], [0]) for s, i in zip(slots, idx)])
+                step_logits.append(lg.float().cpu().clone())
+            got.append(torch.stack(step_logits))
+            for s in slots:
+                eng.free(s)
+        eng.check_device_errors()
+        outs[dtype] = torch.cat(got, dim=1)
+        del eng
+        torch.cuda.empty_cache()
+    ref, got = outs["float32"], outs["bfloat16"]
+    scale = ref.abs().max().item()
+    err = (ref - got).abs().max().item()
+    assert scale > 0.5 and err < 0.03 * scale + 0.02, f"max abs err {err} at logit scale {scale}"
+    # the most likely token agrees wherever the 32-bit margin is clear
+    top2 = ref.topk(2, dim=-1).values
+    clear = (top2[..., 0] - top2[..., 1]) > 4 * err
+    assert clear.any()
+    assert torch.equal(ref.argmax(-1)[clear], got.argmax(-1)[clear])

@@ -1,0 +1,474 @@
+// Causal grouped-query attention of prompts over the paged cache on the 5th-generation
+// tensor cores (sm_100a), compiled for one head size: -DOE_HD=64 or 128.
+//
+// A CTA owns 128 query rows of one (sequence, KV head); a row is a (token, query head of
+// the group) pair, so the G = H/KVH heads that share a KV head share every K/V tile.  Key
+// blocks are cache pages (64 keys).  Per block:
+//   S = Q K^T      tcgen05.mma M=128 N=64 K=head_dim, Q and K tiles K-major in 128B-swizzled
+//                  shared memory (TMA), S float32 in tensor memory (two buffers);
+//   softmax        128 threads, one row each: tcgen05.ld of the row's 64 scores, scale,
+//                  causal / window mask, running maximum and sum in float32 (no shuffles:
+//                  a thread holds its whole row), P = exp2(s - m) rounded to bf16 and
+//                  written to shared memory in the swizzled K-major layout;
+//   O_blk = P V    tcgen05.mma M=128 N=head_dim K=64, P from shared memory, V as the
+//                  MN-major B operand straight from the page ([key][dim] rows of 128 bytes);
+//   O = O * alpha + O_blk   in registers of the row's thread, after tcgen05.ld of O_blk.
+// The MMA thread issues S of block j+1 before it waits for P of block j, and the threads add
+// O_blk of block j-1 while P V of block j runs, so the tensor pipe and the softmax overlap.
+// Roles (192 threads): warp 0 = TMA producer (Q once, then K/V pages through a 3-stage
+// ring), warp 1 = tensor-memory allocation and MMA issue, warps 2-5 = softmax and output.
+// Every wait on an mbarrier is bounded in time; a wait that runs out raises an error flag,
+// every role leaves its loop, copies in flight get a fixed time, tensor memory is freed.
+// Reference: core/model.cpp:605-626 (scores, softmax, weighted values of a prompt).
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include "common.cuh"
+#include <mutex>
+
+#ifndef OE_HD
+#define OE_HD 128
+#endif
+
+namespace {
+
+constexpr int HD = OE_HD;
+static_assert(HD == 64 || HD == 128, "the tcgen05 attention is built for head_dim 64 or 128");
+constexpr int BM = 128;                    // query rows per CTA
+constexpr int BN = OE_PAGE;                // keys per block
+constexpr int SUB = HD / 64;               // 64-wide (128-byte) sub-tiles along head_dim
+constexpr int Q_BYTES = BM * HD * 2;       // SUB sub-tiles of [128][64]
+constexpr int KV_TILE = BN * HD * 2;       // one K or V page panel, SUB sub-tiles of [64][64]
+constexpr int STAGE_BYTES = 2 * KV_TILE;
+constexpr int STAGES = 3;
+constexpr int P_BYTES = BM * BN * 2;       // [128][64] bf16
+constexpr int THREADS = 192;
+constexpr uint32_t TMEM_COLS = 512;        // S: 2 x 64, O_blk: 2 x HD
+constexpr uint32_t S_COL = 0, O_COL = 128;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+__device__ int g_error = 0;
+
+struct Ctl {
+    uint64_t q_full;
+    uint64_t kv_full[STAGES], kv_empty[STAGES];
+    uint64_t s_full[2], p_ready[2], o_full[2], o_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+struct Args {
+    bf16* out;                 // [T, H*HD]
+    const int* tables;         // [B, max_pages]
+    int max_pages;
+    const int* cu_q;
+    const int* seq_start;
+    const int* seq_qlen;
+    int H, KVH, window;
+    float scale_log2;
+    int tokens_per_tile;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Ctl* ctl, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (uint32_t spin = 0;; spin++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 255u) == 255u) {
+            if (*(volatile int*)&ctl->abort_flag) return false;
+            if (global_ns() - t0 > WAIT_LIMIT_NS) {
+                atomicExch(&ctl->abort_flag, 1);
+                atomicCAS(&g_error, 0, code);
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+// Shared-memory operand descriptor, 128-byte swizzle, version 1 (sm_100).
+// K-major (rows of 128 bytes along K): stride offset 1024 between 8-row groups.
+// MN-major (rows of 128 bytes along N, one row per k): stride offset 1024 between 8-k groups,
+// leading offset = distance between 64-wide column groups.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t addr, uint32_t lead_bytes, uint32_t stride_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lead_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((stride_bytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// kind::f16 instruction descriptor: D float32, A and B bf16, A K-major, B K-major or MN-major.
+__device__ __forceinline__ uint32_t umma_idesc(int m, int n, bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int j = 0; j < 16; j++) v[j] = __uint_as_float(r[j]);
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const Args a) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* q_s = smem;
+    uint8_t* kv_s = q_s + Q_BYTES;
+    uint8_t* p_s = kv_s + STAGES * STAGE_BYTES;
+    Ctl* ctl = (Ctl*)(p_s + 2 * P_BYTES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.z, kvh = blockIdx.y;
+    if (threadIdx.x == 0) {
+        mbar_init(&ctl->q_full, 1);
+        for (int s = 0; s < STAGES; s++) { mbar_init(&ctl->kv_full[s], 1); mbar_init(&ctl->kv_empty[s], 1); }
+        for (int i = 0; i < 2; i++) {
+            mbar_init(&ctl->s_full[i], 1); mbar_init(&ctl->p_ready[i], BM);
+            mbar_init(&ctl->o_full[i], 1); mbar_init(&ctl->o_empty[i], BM);
+        }
+        ctl->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *(volatile uint32_t*)&ctl->tmem_base;
+
+    pdl_launch_dependents();
+    pdl_wait();                                            // q, the cache and the step's integers come from earlier kernels
+
+    // heavy tiles (late rows of a causal prompt) first
+    const int qlen = a.seq_qlen[b];
+    const int tpt = a.tokens_per_tile;
+    const int q_tile = (int)gridDim.x - 1 - (int)blockIdx.x;
+    const bool active = qlen > 0 && q_tile * tpt < qlen;
+    int n_blocks = 0, j_lo = 0, t0 = 0, nt = 0, start = 0;
+    long long packed0 = 0;
+    const int G = a.H / a.KVH;
+    if (active) {
+        start = a.seq_start[b];
+        t0 = q_tile * tpt;
+        nt = min(tpt, qlen - t0);
+        const int pos_lo = start + t0, pos_hi = start + t0 + nt - 1;
+        const int key_lo = a.window > 0 ? max(0, pos_lo - a.window + 1) : 0;
+        j_lo = key_lo / BN;
+        n_blocks = pos_hi / BN - j_lo + 1;
+        packed0 = a.cu_q[b] + t0;
+    }
+    const int* trow = a.tables + (size_t)b * a.max_pages;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0 && active) {
+            mbar_expect_tx(&ctl->q_full, (uint32_t)(SUB * tpt * G * 128));
+            for (int sb = 0; sb < SUB; sb++)
+                tma_load_3d(q_s + sb * (BM * 128), &map_q, &ctl->q_full, sb * 64, kvh * G, (int)packed0);
+            for (int i = 0; i < n_blocks; i++) {
+                const int s = i % STAGES;
+                const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
+                if (!mbar_wait(&ctl->kv_empty[s], phase ^ 1u, ctl, 1)) break;
+                const int page = trow[j_lo + i];
+                uint8_t* k_dst = kv_s + (size_t)s * STAGE_BYTES;
+                uint8_t* v_dst = k_dst + KV_TILE;
+                const int k_row = ((page * 2 + 0) * a.KVH + kvh) * BN, v_row = ((page * 2 + 1) * a.KVH + kvh) * BN;
+                mbar_expect_tx(&ctl->kv_full[s], (uint32_t)STAGE_BYTES);
+                for (int sb = 0; sb < SUB; sb++) {
+                    tma_load_2d(k_dst + sb * (BN * 128), &map_kv, &ctl->kv_full[s], sb * 64, k_row);
+                    tma_load_2d(v_dst + sb * (BN * 128), &map_kv, &ctl->kv_full[s], sb * 64, v_row);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issue ----------------
+        if (lane == 0 && active) {
+            const uint32_t idesc_s = umma_idesc(BM, BN, false);
+            const uint32_t idesc_o = umma_idesc(BM, HD, true);
+            bool ok = mbar_wait(&ctl->q_full, 0, ctl, 2);
+            auto issue_s = [&](int i) {                       // S_i = Q K_i^T into S buffer i & 1
+                const int s = i % STAGES;
+                const uint32_t k_addr = smem_u32(kv_s + (size_t)s * STAGE_BYTES);
+                const uint32_t q_addr = smem_u32(q_s);
+#pragma unroll
+                for (int k = 0; k < HD / 16; k++) {
+                    const uint32_t sb = k / 4, kk = k % 4;
+                    umma(tmem_base + S_COL + (uint32_t)((i & 1) * BN), umma_desc(q_addr + sb * (BM * 128) + kk * 32, 16, 1024),
+                         umma_desc(k_addr + sb * (BN * 128) + kk * 32, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
+                }
+                umma_commit(&ctl->s_full[i & 1]);
+            };
+            if (ok && n_blocks > 0) {
+                ok = mbar_wait(&ctl->kv_full[0], 0, ctl, 3);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (ok) issue_s(0);
+            }
+            for (int i = 0; i < n_blocks && ok; i++) {
+                if (i + 1 < n_blocks) {
+                    const int s1 = (i + 1) % STAGES;
+                    ok = mbar_wait(&ctl->kv_full[s1], (uint32_t)((i + 1) / STAGES) & 1u, ctl, 3);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    issue_s(i + 1);
+                }
+                // P_i is in shared memory (and S_i has been read)
+                ok = mbar_wait(&ctl->p_ready[i & 1], (uint32_t)(i >> 1) & 1u, ctl, 4);
+                if (!ok) break;
+                // O_blk buffer i & 1 has been read (block i - 2)
+                ok = mbar_wait(&ctl->o_empty[i & 1], ((uint32_t)(i >> 1) & 1u) ^ 1u, ctl, 5);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const int s = i % STAGES;
+                const uint32_t v_addr = smem_u32(kv_s + (size_t)s * STAGE_BYTES + KV_TILE);
+                const uint32_t p_addr = smem_u32(p_s + (size_t)(i & 1) * P_BYTES);
+#pragma unroll
+                for (int k = 0; k < BN / 16; k++) {
+                    umma(tmem_base + O_COL + (uint32_t)((i & 1) * HD), umma_desc(p_addr + k * 32, 16, 1024),
+                         umma_desc(v_addr + k * (16 * 128), BN * 128, 1024), idesc_o, k > 0 ? 1u : 0u);
+                }
+                umma_commit(&ctl->o_full[i & 1]);
+                umma_commit(&ctl->kv_empty[s]);              // K_i and V_i are no longer needed
+            }
+        }
+    } else {
+        // ---------------- softmax and output: warps 2..5, one row per thread ----------------
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;                 // row of the tile = TMEM lane
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const int tok = r / G, head = kvh * G + r % G;
+        const bool valid = active && tok < nt;
+        const int pos = start + t0 + tok;
+        float o[HD];
+#pragma unroll
+        for (int d = 0; d < HD; d++) o[d] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
+        bool ok = true;
+        for (int i = 0; i <= n_blocks && active; i++) {
+            if (i < n_blocks) {
+                ok = mbar_wait(&ctl->s_full[i & 1], (uint32_t)(i >> 1) & 1u, ctl, 6);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                float s[BN];
+#pragma unroll
+                for (int c0 = 0; c0 < BN; c0 += 16) tmem_ld16(lane_addr + S_COL + (uint32_t)((i & 1) * BN + c0), *(float(*)[16])&s[c0]);
+                const int key0 = (j_lo + i) * BN;
+                float mx = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < BN; c++) {
+                    const int key = key0 + c;
+                    const bool keep = valid && key <= pos && (a.window <= 0 || key > pos - a.window);
+                    s[c] = keep ? s[c] * a.scale_log2 : -INFINITY;
+                    mx = fmaxf(mx, s[c]);
+                }
+                const float m_new = fmaxf(m_run, mx);
+                const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+                const float alpha = exp2f(m_run - m_use);
+                m_run = m_new;
+                float sum = 0.f;
+                // P row: 64 bf16 = 8 chunks of 16 bytes, chunk c stored at c ^ (row & 7)
+                uint8_t* prow = p_s + (size_t)(i & 1) * P_BYTES + r * 128;
+#pragma unroll
+                for (int ch = 0; ch < 8; ch++) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const float p0 = exp2f(s[ch * 8 + 2 * e] - m_use), p1 = exp2f(s[ch * 8 + 2 * e + 1] - m_use);
+                        sum += p0 + p1;
+                        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                        w[e] = *(uint32_t*)&h;
+                    }
+                    *(uint4*)(prow + ((ch ^ (r & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+                l_run = l_run * alpha + sum;
+                // make the row visible to the tensor core (async proxy), then signal
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(&ctl->p_ready[i & 1]);
+                // add the previous block's O_blk while P V of this block runs
+                if (i > 0) {
+                    const int pb = (i - 1) & 1;
+                    ok = mbar_wait(&ctl->o_full[pb], (uint32_t)((i - 1) >> 1) & 1u, ctl, 7);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                    for (int c0 = 0; c0 < HD; c0 += 16) {
+                        float ob[16];
+                        tmem_ld16(lane_addr + O_COL + (uint32_t)(pb * HD + c0), ob);
+#pragma unroll
+                        for (int d = 0; d < 16; d++) o[c0 + d] = o[c0 + d] * alpha_prev + ob[d];
+                    }
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    mbar_arrive(&ctl->o_empty[pb]);
+                }
+                alpha_prev = alpha;
+            } else {
+                // the last block's O_blk
+                const int pb = (n_blocks - 1) & 1;
+                ok = mbar_wait(&ctl->o_full[pb], (uint32_t)((n_blocks - 1) >> 1) & 1u, ctl, 8);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int c0 = 0; c0 < HD; c0 += 16) {
+                    float ob[16];
+                    tmem_ld16(lane_addr + O_COL + (uint32_t)(pb * HD + c0), ob);
+#pragma unroll
+                    for (int d = 0; d < 16; d++) o[c0 + d] = o[c0 + d] * alpha_prev + ob[d];
+                }
+            }
+        }
+        if (ok && valid) {
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            bf16* dst = a.out + (packed0 + tok) * (long long)(a.H * HD) + (size_t)head * HD;
+#pragma unroll
+            for (int c0 = 0; c0 < HD; c0 += 8) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(o[c0 + 2 * e] * inv, o[c0 + 2 * e + 1] * inv);
+                    w[e] = *(uint32_t*)&h;
+                }
+                *(uint4*)(dst + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+
+    __syncthreads();
+    if (*(volatile int*)&ctl->abort_flag) {
+        const unsigned long long t0w = global_ns();
+        while (global_ns() - t0w < 2000000ull) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+std::mutex g_mutex;
+
+int get_encode() {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (g_encode) return 0;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || fn == nullptr) return e != cudaSuccess ? (int)e : 999;
+    g_encode = (PFN_cuTensorMapEncodeTiled_v12000)fn;
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int oe_attn_tc_head_dim() { return HD; }
+
+// Prompt attention.  q: rows of q_stride bf16 with head h at h*HD (the fused qkv buffer after
+// rotation); cache: one entry [pages][2][KVH][64][HD]; out [T, H*HD].  Needs 16-byte aligned
+// rows (q_stride a multiple of 8) and G = H/KVH <= 128.
+int oe_attn_tc_bf16(bf16* out, const bf16* q, long long q_stride, const bf16* cache, long long n_pages, const int* tables,
+                    int max_pages, const int* cu_q, const int* seq_start, const int* seq_qlen, int n_seqs, int n_tokens,
+                    int max_qlen, int H, int KVH, int window, float scale, cudaStream_t st) {
+    if (n_seqs <= 0 || n_tokens <= 0) return 0;
+    if (H % KVH || (q_stride % 8) || ((uintptr_t)q & 15) || ((uintptr_t)cache & 15) || ((uintptr_t)out & 15)) return OE_ERR_UNSUPPORTED;
+    const int G = H / KVH;
+    if (G > BM || n_seqs > 65535) return OE_ERR_UNSUPPORTED;
+    int rc = get_encode();
+    if (rc) return rc;
+    Args a;
+    a.out = out; a.tables = tables; a.max_pages = max_pages; a.cu_q = cu_q; a.seq_start = seq_start; a.seq_qlen = seq_qlen;
+    a.H = H; a.KVH = KVH; a.window = window; a.scale_log2 = scale * 1.4426950408889634f;
+    a.tokens_per_tile = BM / G;
+    CUtensorMap map_q, map_kv;
+    {   // q as [token][head][dim]; a box holds 64 dims of the G heads of tokens_per_tile tokens
+        cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)H, (cuuint64_t)n_tokens};
+        cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)q_stride * 2};
+        cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)a.tokens_per_tile};
+        cuuint32_t es[3] = {1, 1, 1};
+        CUresult r = g_encode(&map_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<bf16*>(q), dims, strides, box, es,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return 1000 + (int)r;
+    }
+    {   // the cache entry as rows of HD: [pages * 2 * KVH * 64][HD]; a box is 64 rows x 64 dims
+        cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)n_pages * 2 * KVH * BN};
+        cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+        cuuint32_t box[2] = {64, (cuuint32_t)BN};
+        cuuint32_t es[2] = {1, 1};
+        CUresult r = g_encode(&map_kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<bf16*>(cache), dims, strides, box, es,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return 2000 + (int)r;
+    }
+    const int tiles = (max_qlen + a.tokens_per_tile - 1) / a.tokens_per_tile;
+    const size_t smem = (size_t)Q_BYTES + STAGES * STAGE_BYTES + 2 * P_BYTES + sizeof(Ctl) + 1024;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    return oe_launch(attn_tc_kernel, dim3(tiles, KVH, n_seqs), dim3(THREADS), smem, st, map_q, map_kv, a);
+}
+
+int oe_attn_tc_error() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(g_error, &zero, sizeof(int));
+    return v;
+}
+
+}  // extern "C"

@@ -36,6 +36,7 @@ LIBRARIES = {
     "gemm_tc": ("gemm_tcgen05.cu", []),
     "gemm_skinny": ("gemm_skinny.cu", []),
     "attention_tc": ("attention_mma.cu", []),
+    "attention_tc5": ("attention_tcgen05.cu", []),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}
@@ -159,6 +160,8 @@ def build_all(names=None, verbose: bool = True) -> list[Path]:
     for n in names:
         if n == "attention_tc":
             jobs.extend((n, {"OE_HD": hd}) for hd in DEFAULT_HEAD_DIMS)
+        elif n == "attention_tc5":
+            jobs.extend((n, {"OE_HD": hd}) for hd in (64, 128))
         else:
             jobs.append((n, None))
     results: dict[object, object] = {}

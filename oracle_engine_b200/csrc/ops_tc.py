@@ -115,9 +115,13 @@ def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool =
 def device_error() -> int:
     """The code of a bounded wait that ran out inside a tensor-core kernel since the last
     call (0 = none).  Synchronises the device."""
-    if "gemm" not in _state:
-        return 0
-    return int(_lib().oe_gemm_tc_error())
+    code = 0
+    if "gemm" in _state:
+        code = int(_lib().oe_gemm_tc_error())
+    for key, lib in list(_state.items()):
+        if isinstance(key, tuple) and key[0] == "attn_tc5":
+            code = code or int(lib.oe_attn_tc_error())
+    return code
 
 
 # ----------------------------------------------------------------------------------------
@@ -150,6 +154,24 @@ def _attn_lib(head_dim: int):
     return lib
 
 
+TCGEN05_ATTENTION_HEAD_DIMS = (64, 128)
+PROMPT_KERNEL = ["tcgen05"]          # "tcgen05" or "mma": which prompt kernel head sizes 64 / 128 use
+
+
+def _attn_tc5_lib(head_dim: int):
+    key = ("attn_tc5", head_dim)
+    lib = _state.get(key)
+    if lib is None:
+        lib = _build.load("attention_tc5", {"OE_HD": head_dim})
+        lib.oe_attn_tc_bf16.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_void_p,
+                                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
+        lib.oe_attn_tc_bf16.restype = c_int
+        lib.oe_attn_tc_error.argtypes = []
+        lib.oe_attn_tc_error.restype = c_int
+        _state[key] = lib
+    return lib
+
+
 def decode_splits(n_seqs: int, n_kv_heads: int, sm_count: int, max_pages: int) -> int:
     """How many CTAs share one (sequence, KV head) of a decode step: enough to occupy the
     GPU about twice, never more than the pages a sequence can have.  Depends on the batch
@@ -175,9 +197,18 @@ def attention(out, qkv, cache, tables, ctx, n_heads: int, n_kv_heads: int, head_
         raise KernelError("attention: out must be contiguous [T, H hd]; cache contiguous")
     if tuple(cache.shape[1:]) != (2, n_kv_heads, ops.PAGE, head_dim):
         raise KernelError("attention: cache entry must be [pages, 2, KVH, PAGE, head_dim]")
+    group = n_heads // n_kv_heads
+    if (PROMPT_KERNEL[0] == "tcgen05" and head_dim in TCGEN05_ATTENTION_HEAD_DIMS and ctx.max_qlen * group > 64
+            and group <= 128 and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0):
+        # prompts: S and O_blk in tensor memory (csrc/attention_tcgen05.cu)
+        code = _attn_tc5_lib(head_dim).oe_attn_tc_bf16(
+            out.data_ptr(), qkv.data_ptr(), qkv.stride(0), cache.data_ptr(), cache.shape[0], tables.data_ptr(),
+            tables.shape[1], ctx.cu_q.data_ptr(), ctx.seq_start.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.n_seqs, T,
+            ctx.max_qlen, n_heads, n_kv_heads, int(window), float(scale), torch.cuda.current_stream().cuda_stream)
+        ops._check(code, "attention_tcgen05")
+        return
     lib = _attn_lib(head_dim)
     n_splits, partial = 1, None
-    group = n_heads // n_kv_heads
     if ctx.all_decode and group <= 16:
         sms = torch.cuda.get_device_properties(out.device).multi_processor_count
         n_splits = decode_splits(ctx.n_seqs, n_kv_heads, sms, tables.shape[1])

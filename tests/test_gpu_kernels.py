@@ -184,13 +184,17 @@ def _attn_case(H, KVH, hd, lens, qlens, dtype, seed):
 
 
 @pytest.mark.parametrize("dtype,kernel", [(torch.float32, "paged"), (torch.bfloat16, "paged"),
-                                          (torch.bfloat16, "mma")])
+                                          (torch.bfloat16, "mma"), (torch.bfloat16, "tcgen05")])
 @pytest.mark.parametrize("H,KVH,hd,window", [(4, 2, 16, 0), (6, 2, 32, 0), (5, 1, 48, 0), (8, 8, 64, 0),
-                                             (24, 8, 128, 0), (6, 3, 32, 70), (4, 4, 16, 5)])
+                                             (24, 8, 128, 0), (6, 3, 32, 70), (4, 4, 16, 5), (10, 2, 64, 70),
+                                             (3, 1, 128, 129)])
 def test_attention_kernels(dtype, kernel, H, KVH, hd, window):
     """Ragged prompts and decoded tokens over a shuffled paged cache with stale pages."""
     from types import SimpleNamespace
     from oracle_engine_b200.csrc import ops, ops_tc
+    if kernel == "tcgen05" and hd not in ops_tc.TCGEN05_ATTENTION_HEAD_DIMS:
+        pytest.skip("the tcgen05 prompt kernel is built for head_dim 64 and 128")
+    ops_tc.PROMPT_KERNEL[0] = "tcgen05" if kernel == "tcgen05" else "mma"
     lens = [1, 64, 65, 200, 130, 17]
     g = torch.Generator().manual_seed(H * 100 + hd)
     k = [torch.randn(n, KVH, hd, generator=g) for n in lens]
@@ -233,6 +237,8 @@ def test_attention_kernels(dtype, kernel, H, KVH, hd, window):
         got = out[:T - 1].double().cpu()
         err = (got - torch.stack(want)).abs().max().item()
         assert err < tol, f"{kernel} {mode}: {err}"
+    ops_tc.PROMPT_KERNEL[0] = "tcgen05"
+    assert ops_tc.device_error() == 0
 
 
 def test_rope_kv_write():

@@ -6,17 +6,26 @@
 // blocks are cache pages (64 keys).  Per block:
 //   S = Q K^T      tcgen05.mma M=128 N=64 K=head_dim, Q and K tiles K-major in 128B-swizzled
 //                  shared memory (TMA), S float32 in tensor memory (two buffers);
-//   softmax        128 threads, one row each: tcgen05.ld of the row's 64 scores, scale,
-//                  causal / window mask, running maximum and sum in float32 (no shuffles:
-//                  a thread holds its whole row), P = exp2(s - m) rounded to bf16 and
-//                  written to shared memory in the swizzled K-major layout;
-//   O_blk = P V    tcgen05.mma M=128 N=head_dim K=64, P from shared memory, V as the
-//                  MN-major B operand straight from the page ([key][dim] rows of 128 bytes);
-//   O = O * alpha + O_blk   in registers of the row's thread, after tcgen05.ld of O_blk.
-// The MMA thread issues S of block j+1 before it waits for P of block j, and the threads add
-// O_blk of block j-1 while P V of block j runs, so the tensor pipe and the softmax overlap.
-// Roles (192 threads): warp 0 = TMA producer (Q once, then K/V pages through a 3-stage
-// ring), warp 1 = tensor-memory allocation and MMA issue, warps 2-5 = softmax and output.
+//   softmax        128 threads, one row each: tcgen05.ld of the row's 64 scores, causal /
+//                  window mask, maximum and sum in float32 (no shuffles: a thread holds its
+//                  whole row), P = exp2(s * scale - m) rounded to bf16 and written to shared
+//                  memory in the swizzled K-major layout;
+//   O += P V       tcgen05.mma M=128 N=head_dim K=64, P from shared memory, V as the
+//                  MN-major B operand straight from the page ([key][dim] rows of 128 bytes),
+//                  O float32 in tensor memory for the whole tile.
+// The reference maximum m of a row moves only when the row's maximum has grown by more than
+// 2^8 since it was set: then the row's O (tcgen05.ld, multiply, tcgen05.st) and its sum are
+// rescaled before the block's P V is issued.  Between two moves P <= 2^8, which bf16 and the
+// float32 sums hold without loss, and the factor cancels in the final O / l, so the result
+// is the one of the plain online softmax.  The decision is taken per warp (tensor-memory
+// loads and stores are warp-wide).
+// The MMA thread issues S of block j+1 before it waits for P of block j, so the tensor pipe
+// and the softmax overlap; two CTAs share an SM (112 KB of shared memory, 256 columns of
+// tensor memory and at most 168 registers a thread each), which hides the latencies of one
+// CTA's softmax chain behind the other's.
+// Roles (192 threads): warp 0 = TMA producer (Q once, then K and V pages through two-stage
+// rings of their own: a K stage is free once its S is done, a V stage once its P V is done),
+// warp 1 = tensor-memory allocation and MMA issue, warps 2-5 = softmax and output.
 // Every wait on an mbarrier is bounded in time; a wait that runs out raises an error flag,
 // every role leaves its loop, copies in flight get a fixed time, tensor memory is freed.
 // Reference: core/model.cpp:605-626 (scores, softmax, weighted values of a prompt).
@@ -38,23 +47,24 @@ constexpr int BN = OE_PAGE;                // keys per block
 constexpr int SUB = HD / 64;               // 64-wide (128-byte) sub-tiles along head_dim
 constexpr int Q_BYTES = BM * HD * 2;       // SUB sub-tiles of [128][64]
 constexpr int KV_TILE = BN * HD * 2;       // one K or V page panel, SUB sub-tiles of [64][64]
-constexpr int STAGE_BYTES = 2 * KV_TILE;
-constexpr int STAGES = 3;
+constexpr int STAGES = 2;                  // of the K ring and of the V ring
 constexpr int P_BYTES = BM * BN * 2;       // [128][64] bf16
 constexpr int THREADS = 192;
-constexpr uint32_t TMEM_COLS = 512;        // S: 2 x 64, O_blk: 2 x HD
+constexpr uint32_t TMEM_COLS = 256;        // S: 2 x 64, O: HD
 constexpr uint32_t S_COL = 0, O_COL = 128;
+constexpr float RESCALE_STEP = 8.f;        // log2 units
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
 __device__ int g_error = 0;
 
 struct Ctl {
     uint64_t q_full;
-    uint64_t kv_full[STAGES], kv_empty[STAGES];
-    uint64_t s_full[2], p_ready[2], o_full[2], o_empty[2];
+    uint64_t k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
+    uint64_t s_full[2], p_ready, pv_done;
     uint32_t tmem_base;
     int abort_flag;
 };
+constexpr int SMEM_NEEDED = Q_BYTES + 2 * STAGES * KV_TILE + P_BYTES + (int)sizeof(Ctl);
 
 struct Args {
     bf16* out;                 // [T, H*HD]
@@ -145,36 +155,60 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t b
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
-    uint32_t r[16];
+// 16 columns of this thread's TMEM lane; the values are valid after tmem_ld_wait().
+__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, float* v) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]),
+          "=f"(v[8]), "=f"(v[9]), "=f"(v[10]), "=f"(v[11]), "=f"(v[12]), "=f"(v[13]), "=f"(v[14]), "=f"(v[15])
         : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int j = 0; j < 16; j++) v[j] = __uint_as_float(r[j]);
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const float* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15]))
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, 2)
 attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const Args a) {
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    {   // the swizzled tiles need a 1024-byte boundary; the launch leaves less than 1024 bytes of slack
+        uint32_t dyn;
+        asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
+        if ((uint32_t)(smem - smem_raw) + (uint32_t)SMEM_NEEDED > dyn) {
+            if (threadIdx.x == 0) atomicCAS(&g_error, 0, 9);
+            return;
+        }
+    }
     uint8_t* q_s = smem;
-    uint8_t* kv_s = q_s + Q_BYTES;
-    uint8_t* p_s = kv_s + STAGES * STAGE_BYTES;
-    Ctl* ctl = (Ctl*)(p_s + 2 * P_BYTES);
+    uint8_t* k_s = q_s + Q_BYTES;
+    uint8_t* v_s = k_s + STAGES * KV_TILE;
+    uint8_t* p_s = v_s + STAGES * KV_TILE;
+    Ctl* ctl = (Ctl*)(p_s + P_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.z, kvh = blockIdx.y;
     if (threadIdx.x == 0) {
         mbar_init(&ctl->q_full, 1);
-        for (int s = 0; s < STAGES; s++) { mbar_init(&ctl->kv_full[s], 1); mbar_init(&ctl->kv_empty[s], 1); }
-        for (int i = 0; i < 2; i++) {
-            mbar_init(&ctl->s_full[i], 1); mbar_init(&ctl->p_ready[i], BM);
-            mbar_init(&ctl->o_full[i], 1); mbar_init(&ctl->o_empty[i], BM);
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&ctl->k_full[s], 1); mbar_init(&ctl->k_empty[s], 1);
+            mbar_init(&ctl->v_full[s], 1); mbar_init(&ctl->v_empty[s], 1);
         }
+        mbar_init(&ctl->s_full[0], 1); mbar_init(&ctl->s_full[1], 1);
+        mbar_init(&ctl->p_ready, 4);                       // one arrival per softmax warp
+        mbar_init(&ctl->pv_done, 1);
         ctl->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -211,24 +245,25 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const int* trow = a.tables + (size_t)b * a.max_pages;
 
     if (warp == 0) {
-        // ---------------- TMA producer ----------------
+        // ---------------- TMA producer: Q, K_0, then K_{i+1} and V_i in turn ----------------
         if (lane == 0 && active) {
             mbar_expect_tx(&ctl->q_full, (uint32_t)(SUB * tpt * G * 128));
             for (int sb = 0; sb < SUB; sb++)
                 tma_load_3d(q_s + sb * (BM * 128), &map_q, &ctl->q_full, sb * 64, kvh * G, (int)packed0);
-            for (int i = 0; i < n_blocks; i++) {
+            auto load = [&](int i, int which, uint64_t* full, uint64_t* empty, uint8_t* ring, int code) -> bool {
                 const int s = i % STAGES;
-                const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
-                if (!mbar_wait(&ctl->kv_empty[s], phase ^ 1u, ctl, 1)) break;
+                if (!mbar_wait(&empty[s], ((uint32_t)(i / STAGES) & 1u) ^ 1u, ctl, code)) return false;
                 const int page = trow[j_lo + i];
-                uint8_t* k_dst = kv_s + (size_t)s * STAGE_BYTES;
-                uint8_t* v_dst = k_dst + KV_TILE;
-                const int k_row = ((page * 2 + 0) * a.KVH + kvh) * BN, v_row = ((page * 2 + 1) * a.KVH + kvh) * BN;
-                mbar_expect_tx(&ctl->kv_full[s], (uint32_t)STAGE_BYTES);
-                for (int sb = 0; sb < SUB; sb++) {
-                    tma_load_2d(k_dst + sb * (BN * 128), &map_kv, &ctl->kv_full[s], sb * 64, k_row);
-                    tma_load_2d(v_dst + sb * (BN * 128), &map_kv, &ctl->kv_full[s], sb * 64, v_row);
-                }
+                const int row = ((page * 2 + which) * a.KVH + kvh) * BN;
+                uint8_t* dst = ring + (size_t)s * KV_TILE;
+                mbar_expect_tx(&full[s], (uint32_t)KV_TILE);
+                for (int sb = 0; sb < SUB; sb++) tma_load_2d(dst + sb * (BN * 128), &map_kv, &full[s], sb * 64, row);
+                return true;
+            };
+            bool ok = n_blocks > 0 && load(0, 0, ctl->k_full, ctl->k_empty, k_s, 1);
+            for (int i = 0; i < n_blocks && ok; i++) {
+                if (i + 1 < n_blocks) ok = load(i + 1, 0, ctl->k_full, ctl->k_empty, k_s, 1);
+                if (ok) ok = load(i, 1, ctl->v_full, ctl->v_empty, v_s, 10);
             }
         }
     } else if (warp == 1) {
@@ -239,7 +274,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             bool ok = mbar_wait(&ctl->q_full, 0, ctl, 2);
             auto issue_s = [&](int i) {                       // S_i = Q K_i^T into S buffer i & 1
                 const int s = i % STAGES;
-                const uint32_t k_addr = smem_u32(kv_s + (size_t)s * STAGE_BYTES);
+                const uint32_t k_addr = smem_u32(k_s + (size_t)s * KV_TILE);
                 const uint32_t q_addr = smem_u32(q_s);
 #pragma unroll
                 for (int k = 0; k < HD / 16; k++) {
@@ -248,37 +283,38 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                          umma_desc(k_addr + sb * (BN * 128) + kk * 32, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
                 }
                 umma_commit(&ctl->s_full[i & 1]);
+                umma_commit(&ctl->k_empty[s]);               // K_i is no longer needed
             };
             if (ok && n_blocks > 0) {
-                ok = mbar_wait(&ctl->kv_full[0], 0, ctl, 3);
+                ok = mbar_wait(&ctl->k_full[0], 0, ctl, 3);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 if (ok) issue_s(0);
             }
             for (int i = 0; i < n_blocks && ok; i++) {
                 if (i + 1 < n_blocks) {
+                    // S buffer (i + 1) & 1 held block i - 1, read before P_{i-1} was signalled
                     const int s1 = (i + 1) % STAGES;
-                    ok = mbar_wait(&ctl->kv_full[s1], (uint32_t)((i + 1) / STAGES) & 1u, ctl, 3);
+                    ok = mbar_wait(&ctl->k_full[s1], (uint32_t)((i + 1) / STAGES) & 1u, ctl, 3);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     issue_s(i + 1);
                 }
-                // P_i is in shared memory (and S_i has been read)
-                ok = mbar_wait(&ctl->p_ready[i & 1], (uint32_t)(i >> 1) & 1u, ctl, 4);
+                // P_i is in shared memory, S_i has been read, O has been rescaled if it had to be
+                ok = mbar_wait(&ctl->p_ready, (uint32_t)i & 1u, ctl, 4);
                 if (!ok) break;
-                // O_blk buffer i & 1 has been read (block i - 2)
-                ok = mbar_wait(&ctl->o_empty[i & 1], ((uint32_t)(i >> 1) & 1u) ^ 1u, ctl, 5);
+                const int s = i % STAGES;
+                ok = mbar_wait(&ctl->v_full[s], (uint32_t)(i / STAGES) & 1u, ctl, 5);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const int s = i % STAGES;
-                const uint32_t v_addr = smem_u32(kv_s + (size_t)s * STAGE_BYTES + KV_TILE);
-                const uint32_t p_addr = smem_u32(p_s + (size_t)(i & 1) * P_BYTES);
+                const uint32_t v_addr = smem_u32(v_s + (size_t)s * KV_TILE);
+                const uint32_t p_addr = smem_u32(p_s);
 #pragma unroll
                 for (int k = 0; k < BN / 16; k++) {
-                    umma(tmem_base + O_COL + (uint32_t)((i & 1) * HD), umma_desc(p_addr + k * 32, 16, 1024),
-                         umma_desc(v_addr + k * (16 * 128), BN * 128, 1024), idesc_o, k > 0 ? 1u : 0u);
+                    umma(tmem_base + O_COL, umma_desc(p_addr + k * 32, 16, 1024),
+                         umma_desc(v_addr + k * (16 * 128), BN * 128, 1024), idesc_o, (i > 0 || k > 0) ? 1u : 0u);
                 }
-                umma_commit(&ctl->o_full[i & 1]);
-                umma_commit(&ctl->kv_empty[s]);              // K_i and V_i are no longer needed
+                umma_commit(&ctl->pv_done);
+                umma_commit(&ctl->v_empty[s]);               // V_i is no longer needed
             }
         }
     } else {
@@ -289,96 +325,105 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const int tok = r / G, head = kvh * G + r % G;
         const bool valid = active && tok < nt;
         const int pos = start + t0 + tok;
-        float o[HD];
-#pragma unroll
-        for (int d = 0; d < HD; d++) o[d] = 0.f;
-        float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
+        float m_run = -INFINITY, l_run = 0.f;              // m_run in units of the scaled scores (log2)
         bool ok = true;
-        for (int i = 0; i <= n_blocks && active; i++) {
-            if (i < n_blocks) {
-                ok = mbar_wait(&ctl->s_full[i & 1], (uint32_t)(i >> 1) & 1u, ctl, 6);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                float s[BN];
+        for (int i = 0; i < n_blocks && active; i++) {
+            ok = mbar_wait(&ctl->s_full[i & 1], (uint32_t)(i >> 1) & 1u, ctl, 6);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float s[BN];
 #pragma unroll
-                for (int c0 = 0; c0 < BN; c0 += 16) tmem_ld16(lane_addr + S_COL + (uint32_t)((i & 1) * BN + c0), *(float(*)[16])&s[c0]);
-                const int key0 = (j_lo + i) * BN;
-                float mx = -INFINITY;
+            for (int c0 = 0; c0 < BN; c0 += 16) tmem_ld16_nowait(lane_addr + S_COL + (uint32_t)((i & 1) * BN + c0), &s[c0]);
+            tmem_ld_wait();
+            const int key0 = (j_lo + i) * BN;
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            // a block that lies wholly before this row's position and inside its window needs no mask
+            const bool whole = valid && key0 + BN - 1 <= pos && (a.window <= 0 || key0 > pos - a.window);
+            if (whole) {
+#pragma unroll
+                for (int c = 0; c < BN; c++) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
+            } else {
 #pragma unroll
                 for (int c = 0; c < BN; c++) {
                     const int key = key0 + c;
                     const bool keep = valid && key <= pos && (a.window <= 0 || key > pos - a.window);
-                    s[c] = keep ? s[c] * a.scale_log2 : -INFINITY;
-                    mx = fmaxf(mx, s[c]);
+                    s[c] = keep ? s[c] : -INFINITY;
+                    mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
                 }
-                const float m_new = fmaxf(m_run, mx);
-                const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-                const float alpha = exp2f(m_run - m_use);
-                m_run = m_new;
-                float sum = 0.f;
-                // P row: 64 bf16 = 8 chunks of 16 bytes, chunk c stored at c ^ (row & 7)
-                uint8_t* prow = p_s + (size_t)(i & 1) * P_BYTES + r * 128;
-#pragma unroll
-                for (int ch = 0; ch < 8; ch++) {
-                    uint32_t w[4];
-#pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        const float p0 = exp2f(s[ch * 8 + 2 * e] - m_use), p1 = exp2f(s[ch * 8 + 2 * e + 1] - m_use);
-                        sum += p0 + p1;
-                        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                        w[e] = *(uint32_t*)&h;
-                    }
-                    *(uint4*)(prow + ((ch ^ (r & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
-                }
-                l_run = l_run * alpha + sum;
-                // make the row visible to the tensor core (async proxy), then signal
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                mbar_arrive(&ctl->p_ready[i & 1]);
-                // add the previous block's O_blk while P V of this block runs
-                if (i > 0) {
-                    const int pb = (i - 1) & 1;
-                    ok = mbar_wait(&ctl->o_full[pb], (uint32_t)((i - 1) >> 1) & 1u, ctl, 7);
-                    if (!ok) break;
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-                    for (int c0 = 0; c0 < HD; c0 += 16) {
-                        float ob[16];
-                        tmem_ld16(lane_addr + O_COL + (uint32_t)(pb * HD + c0), ob);
-#pragma unroll
-                        for (int d = 0; d < 16; d++) o[c0 + d] = o[c0 + d] * alpha_prev + ob[d];
-                    }
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    mbar_arrive(&ctl->o_empty[pb]);
-                }
-                alpha_prev = alpha;
-            } else {
-                // the last block's O_blk
-                const int pb = (n_blocks - 1) & 1;
-                ok = mbar_wait(&ctl->o_full[pb], (uint32_t)((n_blocks - 1) >> 1) & 1u, ctl, 8);
+            }
+            const float m_new = fmaxf(m_run, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2);
+            // P_{i-1} V_{i-1} has read the P buffer and has been added to O
+            if (i > 0) {
+                ok = mbar_wait(&ctl->pv_done, (uint32_t)(i - 1) & 1u, ctl, 7);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+            if (i == 0) {
+                m_run = m_new;
+            } else if (__any_sync(0xffffffffu, m_new > m_run + RESCALE_STEP)) {
+                const float alpha = fast_exp2(m_run - (m_new == -INFINITY ? 0.f : m_new));
 #pragma unroll
                 for (int c0 = 0; c0 < HD; c0 += 16) {
                     float ob[16];
-                    tmem_ld16(lane_addr + O_COL + (uint32_t)(pb * HD + c0), ob);
+                    tmem_ld16_nowait(lane_addr + O_COL + (uint32_t)c0, ob);
+                    tmem_ld_wait();
 #pragma unroll
-                    for (int d = 0; d < 16; d++) o[c0 + d] = o[c0 + d] * alpha_prev + ob[d];
+                    for (int d = 0; d < 16; d++) ob[d] *= alpha;
+                    tmem_st16(lane_addr + O_COL + (uint32_t)c0, ob);
                 }
+                tmem_st_wait();
+                l_run *= alpha;
+                m_run = m_new;
             }
-        }
-        if (ok && valid) {
-            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            bf16* dst = a.out + (packed0 + tok) * (long long)(a.H * HD) + (size_t)head * HD;
+            const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            // P row: 64 bf16 = 8 chunks of 16 bytes, chunk c stored at c ^ (row & 7)
+            uint8_t* prow = p_s + r * 128;
 #pragma unroll
-            for (int c0 = 0; c0 < HD; c0 += 8) {
+            for (int ch = 0; ch < 8; ch++) {
                 uint32_t w[4];
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
-                    __nv_bfloat162 h = __floats2bfloat162_rn(o[c0 + 2 * e] * inv, o[c0 + 2 * e + 1] * inv);
+                    const float p0 = fast_exp2(fmaf(s[ch * 8 + 2 * e], a.scale_log2, neg_m));
+                    const float p1 = fast_exp2(fmaf(s[ch * 8 + 2 * e + 1], a.scale_log2, neg_m));
+                    sum4[e] += p0 + p1;
+                    __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                     w[e] = *(uint32_t*)&h;
                 }
-                *(uint4*)(dst + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+                *(uint4*)(prow + ((ch ^ (r & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            // make the row visible to the tensor core (async proxy), then signal
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ctl->p_ready);
+        }
+        if (ok && active && n_blocks > 0) {
+            ok = mbar_wait(&ctl->pv_done, (uint32_t)(n_blocks - 1) & 1u, ctl, 8);
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+                bf16* dst = a.out + (packed0 + tok) * (long long)(a.H * HD) + (size_t)head * HD;
+#pragma unroll
+                for (int c0 = 0; c0 < HD; c0 += 32) {
+                    float ob[32];
+                    tmem_ld16_nowait(lane_addr + O_COL + (uint32_t)c0, ob);
+                    tmem_ld16_nowait(lane_addr + O_COL + (uint32_t)(c0 + 16), ob + 16);
+                    tmem_ld_wait();
+                    if (valid) {
+#pragma unroll
+                        for (int c = 0; c < 32; c += 8) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                __nv_bfloat162 h = __floats2bfloat162_rn(ob[c + 2 * e] * inv, ob[c + 2 * e + 1] * inv);
+                                w[e] = *(uint32_t*)&h;
+                            }
+                            *(uint4*)(dst + c0 + c) = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    }
+                }
             }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -454,10 +499,14 @@ int oe_attn_tc_bf16(bf16* out, const bf16* q, long long q_stride, const bf16* ca
         if (r != CUDA_SUCCESS) return 2000 + (int)r;
     }
     const int tiles = (max_qlen + a.tokens_per_tile - 1) / a.tokens_per_tile;
-    const size_t smem = (size_t)Q_BYTES + STAGES * STAGE_BYTES + 2 * P_BYTES + sizeof(Ctl) + 1024;
+    // two CTAs an SM: (228 KB - 2 x 1 KB reserved) / 2 each; the kernel checks that its tiles fit behind
+    // the 1024-byte boundary it needs and raises error 9 if they do not
+    const size_t smem = HD == 128 ? (size_t)115712 : (size_t)SMEM_NEEDED + 1024;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }

@@ -241,6 +241,42 @@ def test_attention_kernels(dtype, kernel, H, KVH, hd, window):
     assert ops_tc.device_error() == 0
 
 
+@pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
+@pytest.mark.parametrize("hd,step", [(64, 12.0), (128, 4.0), (128, -6.0)])
+def test_attention_moving_maximum(kernel, hd, step):
+    """Scores that climb (or fall) by `step` from one block of 64 keys to the next: the running maximum
+    moves at every block (12), at every second or third block (4: in between, probabilities above 1
+    are summed against an older maximum), or never (falling: the first block outweighs all later ones)."""
+    from types import SimpleNamespace
+    from oracle_engine_b200.csrc import ops_tc
+    ops_tc.PROMPT_KERNEL[0] = kernel
+    H, KVH, n = 4, 2, 700
+    g = torch.Generator().manual_seed(int(hd + step))
+    u = torch.randn(hd, generator=g)
+    u = u / u.norm()
+    k = torch.randn(n, KVH, hd, generator=g) * 0.5
+    q = torch.randn(n, H, hd, generator=g) * 0.5
+    v = torch.randn(n, KVH, hd, generator=g)
+    # q . k / sqrt(hd) gains `step` per block along u
+    q = q + u * math.sqrt(math.sqrt(hd) * 8.0)
+    k = k + u * (torch.arange(n) // 64).reshape(n, 1, 1) * (step / 8.0) * math.sqrt(math.sqrt(hd) * 8.0)
+    rd = lambda t: t.to(torch.bfloat16).double()                          # noqa: E731
+    want = pl.causal_attention(rd(q), rd(k), rd(v), None)
+    cache, tables = _paged([k], [v], [n], torch.bfloat16)
+    qbuf = torch.zeros(n, (H + 2 * KVH) * hd)
+    qbuf[:, :H * hd] = q.reshape(n, -1)
+    qbuf = qbuf.to(torch.bfloat16).to(DEV)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)        # noqa: E731
+    out = torch.full((n, H * hd), 7.0, dtype=torch.bfloat16, device=DEV)
+    ctx = SimpleNamespace(cu_q=i32([0, n]), seq_start=i32([0]), seq_qlen=i32([n]), tok_seq=i32([0] * n), n_seqs=1,
+                          max_qlen=n, all_decode=False)
+    ops_tc.attention(out, qbuf, cache, tables, ctx, H, KVH, hd, 0, 1 / math.sqrt(hd))
+    err = (out.double().cpu() - want.reshape(n, -1)).abs().max().item()
+    ops_tc.PROMPT_KERNEL[0] = "tcgen05"
+    assert err < 2.5e-2, err
+    assert ops_tc.device_error() == 0
+
+
 def test_rope_kv_write():
     from oracle_engine_b200.csrc import ops
     from oracle_engine_b200.parts.positions import rotary_inv_freq

@@ -127,8 +127,8 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
           "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
         : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 struct GemmArgs {
     void* C;
@@ -144,10 +144,19 @@ struct GemmArgs {
     int* counters;              // [tiles_a * tiles_b], zero between launches
 };
 
+// Accumulation into C goes out as reductions that the L2 performs (no load on the SM's side, so
+// the epilogue does not wait for memory).  Every element of C gets exactly one addition per
+// product, so the result does not depend on the order in which the reductions arrive.
+__device__ __forceinline__ void red_add(float* p, float v) {
+    asm volatile("red.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
+}
+__device__ __forceinline__ void red_add4(float* p, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
 __device__ __forceinline__ void store_out(const GemmArgs& g, long long idx, float v) {
     if (g.out_kind == 0) ((bf16*)g.C)[idx] = __float2bfloat16_rn(v);
     else if (g.out_kind == 1) ((float*)g.C)[idx] = v;
-    else ((float*)g.C)[idx] += v;
+    else red_add((float*)g.C + idx, v);
 }
 
 __device__ __forceinline__ float silu_mul(float gate, float up) { return (gate / (1.f + expf(-gate))) * up; }
@@ -212,12 +221,8 @@ __device__ __forceinline__ void emit(const GemmArgs& g, int a_row, int b_row0, c
         float4* dst = (float4*)((float*)g.C + base);
 #pragma unroll
         for (int j = 0; j < NC / 4; j++) {
-            float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-            if (g.out_kind == 2) {
-                const float4 old = dst[j];
-                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-            }
-            dst[j] = o;
+            if (g.out_kind == 2) red_add4((float*)(dst + j), v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            else dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
         }
     } else {
 #pragma unroll
@@ -358,18 +363,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * g.n_tile);
             const size_t tile_off = (((size_t)tile_a * tiles_b + tile_b) * (size_t)g.n_tile) * BLOCK_M + row;
             const size_t split_stride = (size_t)tiles_a * tiles_b * g.n_tile * BLOCK_M;
-            for (int c0 = 0; c0 < g.n_tile; c0 += 16) {
-                float v[16];
-                uint32_t r[16];
-                tmem_ld16(taddr + (uint32_t)c0, r);
+            // 32 columns per wait (n_tile is a multiple of 16: the last group may be half)
+            for (int c0 = 0; c0 < g.n_tile; c0 += 32) {
+                uint32_t r[2][16];
+                const bool two = c0 + 16 < g.n_tile;
+                tmem_ld16(taddr + (uint32_t)c0, r[0]);
+                if (two) tmem_ld16(taddr + (uint32_t)(c0 + 16), r[1]);
+                tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 16; j++) v[j] = __uint_as_float(r[j]);
-                if (g.splits > 1) {
-                    float* part = g.workspace + (size_t)split * split_stride + tile_off + (size_t)c0 * BLOCK_M;
+                for (int h = 0; h < 2; h++) {
+                    if (h == 1 && !two) break;
+                    float v[16];
 #pragma unroll
-                    for (int j = 0; j < 16; j++) part[(size_t)j * BLOCK_M] = v[j];
-                } else {
-                    emit<16>(g, a_row, tile_b * g.n_tile + c0, v);
+                    for (int j = 0; j < 16; j++) v[j] = __uint_as_float(r[h][j]);
+                    const int c = c0 + 16 * h;
+                    if (g.splits > 1) {
+                        float* part = g.workspace + (size_t)split * split_stride + tile_off + (size_t)c * BLOCK_M;
+#pragma unroll
+                        for (int j = 0; j < 16; j++) part[(size_t)j * BLOCK_M] = v[j];
+                    } else {
+                        emit<16>(g, a_row, tile_b * g.n_tile + c, v);
+                    }
                 }
             }
             // the accumulator has been read: the MMA warp may reuse it

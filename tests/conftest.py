@@ -38,7 +38,16 @@ TINY_D = dict(architectures=["LlamaForCausalLM"], vocab_size=257, hidden_size=10
               num_hidden_layers=2, num_attention_heads=5, num_key_value_heads=5, head_dim=20, rms_norm_eps=1e-5,
               rope_theta=10000.0, max_position_embeddings=256, tie_word_embeddings=True, eos_token_id=[1, 2, 3])
 
-TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 5), "D": (TINY_D, 8)}
+# head_dim 64 (the smaller head size of the tensor-memory prompt attention), 3 query heads per KV head,
+# widths that are multiples of 16 but no powers of two, a width that differs from heads x head_dim
+TINY_E = dict(architectures=["LlamaForCausalLM"], vocab_size=389, hidden_size=208, intermediate_size=464,
+              num_hidden_layers=3, num_attention_heads=6, num_key_value_heads=2, head_dim=64, rms_norm_eps=2e-6,
+              rope_theta=100000.0,
+              rope_scaling={"rope_type": "llama3", "factor": 16.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                            "original_max_position_embeddings": 128},
+              max_position_embeddings=640, tie_word_embeddings=False, eos_token_id=3)
+
+TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 5), "D": (TINY_D, 8), "E": (TINY_E, 11)}
 
 
 @pytest.fixture(scope="session")

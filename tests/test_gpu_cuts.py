@@ -18,7 +18,7 @@ def _requests(cfg, seed0=10):
 
 @pytest.fixture(scope="module")
 def sharp_dirs(model_dirs, tmp_path_factory):
-    return {k: helpers.sharpen(model_dirs[k], tmp_path_factory.mktemp(f"sharp_{k}"), 6.0) for k in ("A", "B")}
+    return {k: helpers.sharpen(model_dirs[k], tmp_path_factory.mktemp(f"sharp_{k}"), 6.0) for k in ("A", "B", "E")}
 
 
 def _check(got, plain, requests, tol, what):
@@ -32,7 +32,7 @@ def _check(got, plain, requests, tol, what):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_cuts_agree_with_plain(model_dirs, plain_models, tmp_path, name, dtype):
     from oracle_engine_b200.engine.engine import Engine
     plain = plain_models[name]
@@ -64,7 +64,7 @@ def test_sharp_attention_far_keys(sharp_dirs, tmp_path, dtype):
     """Peaked softmax over several pages: a far key, a page edge or a stale slot shows."""
     import plain_llama
     from oracle_engine_b200.engine.engine import Engine
-    for name in ("A", "B"):
+    for name in ("A", "B", "E"):
         plain = plain_llama.PlainLlama(sharp_dirs[name])
         limit = plain.cfg["max_position_embeddings"]
         lens = [min(limit, n) for n in (127, 128, 129, 300, 63, 65)]

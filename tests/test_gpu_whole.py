@@ -17,7 +17,7 @@ def _tokens(n, vocab, seed):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "E"])
 def test_whole_prompt_logits(model_dirs, plain_models, name, dtype):
     from oracle_engine_b200 import SequenceStep
     from oracle_engine_b200.engine.engine import Engine

@@ -34,6 +34,7 @@ LIBRARIES = {
     "attention": ("attention.cu", []),
     "sampling": ("sampling.cu", []),
     "gemm_tc": ("gemm_tcgen05.cu", []),
+    "gemm_pair": ("gemm_tcgen05_pair.cu", []),
     "gemm_skinny": ("gemm_skinny.cu", []),
     "attention_tc": ("attention_mma.cu", []),
     "attention_tc5": ("attention_tcgen05.cu", []),

@@ -142,7 +142,7 @@ def main(argv=None):
     g.add_argument("--n", type=int, default=16384)
     g.add_argument("--k", type=int, default=3072)
     g.add_argument("--out", default="bfloat16", choices=["bfloat16", "float32", "accumulate", "swiglu"])
-    g.add_argument("--kernel", default="auto", choices=["auto", "tcgen05", "skinny"])
+    g.add_argument("--kernel", default="auto", choices=["auto", "tcgen05", "pair", "skinny"])
     at = sub.add_parser("attention")
     at.add_argument("--batch", type=int, default=8)
     at.add_argument("--context", type=int, default=640)

@@ -58,6 +58,21 @@ def gemm_supported(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
 
 
 SKINNY_MAX_TOKENS = 8       # up to here the weight-streaming kernel (gemm_skinny.cu) is used
+PAIR_MIN_TOKENS = 256       # from here on the two-SM kernel (gemm_tcgen05_pair.cu) for stores; measured the
+                            # same speed as the one-SM kernel or a little faster, except with the accumulate epilogue
+PAIR_MAX_TILE = [0]         # tests: an upper limit for the pair kernel's tile width (0 = none)
+
+
+def _pair():
+    lib = _state.get("pair")
+    if lib is None:
+        lib = _build.load("gemm_pair")
+        lib.oe_gemm_pair_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong,
+                                          c_int, c_int, c_void_p]
+        lib.oe_gemm_pair_bf16.restype = c_int
+        lib.oe_gemm_pair_error.restype = c_int
+        _state["pair"] = lib
+    return lib
 
 
 def _skinny():
@@ -77,8 +92,9 @@ def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool =
 
     swiglu: w's rows alternate gate and up rows (g0, u0, g1, u1, ...) and out [M, N/2]
     bfloat16 receives silu(gate) * up, computed in float32 in the epilogue.
-    kernel: "auto" (weight-streaming kernel up to SKINNY_MAX_TOKENS rows, tcgen05 above),
-    "tcgen05" or "skinny"."""
+    kernel: "auto" (weight-streaming kernel up to SKINNY_MAX_TOKENS rows, the two-SM tcgen05
+    kernel from PAIR_MIN_TOKENS rows unless it accumulates, the one-SM tcgen05 kernel otherwise),
+    "tcgen05", "pair" or "skinny"."""
     M, K = a.shape
     N = w.shape[0]
     if w.shape[1] != K or out.shape != (M, N // 2 if swiglu else N):
@@ -104,6 +120,11 @@ def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool =
                                              out.stride(0), kind, torch.cuda.current_stream().cuda_stream)
         ops._check(code, "gemm_skinny")
         return
+    if kernel == "pair" or (kernel == "auto" and M >= PAIR_MIN_TOKENS and N >= 32 and not accumulate):
+        code = _pair().oe_gemm_pair_bf16(out.data_ptr(), a.data_ptr(), w.data_ptr(), M, N, K, a.stride(0), out.stride(0),
+                                         kind, PAIR_MAX_TILE[0], torch.cuda.current_stream().cuda_stream)
+        ops._check(code, "gemm_pair")
+        return
     ws, counters, sms = _scratch(a.device)
     code = _lib().oe_gemm_tc_bf16(out.data_ptr(), a.data_ptr(), w.data_ptr(), M, N, K, a.stride(0), out.stride(0), kind,
                                   ws.data_ptr() if split_k else None, ws.numel() * 4,
@@ -118,6 +139,8 @@ def device_error() -> int:
     code = 0
     if "gemm" in _state:
         code = int(_lib().oe_gemm_tc_error())
+    if "pair" in _state:
+        code = code or int(_state["pair"].oe_gemm_pair_error())
     for key, lib in list(_state.items()):
         if isinstance(key, tuple) and key[0] == "attn_tc5":
             code = code or int(lib.oe_attn_tc_error())

@@ -151,6 +151,44 @@ def test_gemm_tcgen05(M, N, K):
     assert not ops_tc.gemm_supported(a[:, :K - 1], w[:, :K - 1].contiguous(), out32)      # rows not 16-byte aligned
 
 
+@pytest.mark.parametrize("M,N,K,max_tile", [(300, 1000, 520, 128), (256, 256, 64, 128), (1000, 264, 72, 0), (513, 3072, 1024, 0),
+                                            (2048, 640, 200, 0), (129, 40, 8, 0)])
+def test_gemm_pair(M, N, K, max_tile):
+    """The two-SM kernel: row and column edges, both halves of the weight tile, all epilogues."""
+    from oracle_engine_b200.csrc import ops_tc
+    ops_tc.PAIR_MAX_TILE[0] = max_tile
+    try:
+        a, w = _rand(M, K, dtype=torch.bfloat16, scale=0.5, seed=1), _rand(N, K, dtype=torch.bfloat16, scale=0.5, seed=2)
+        want = a.double() @ w.double().T
+        tol = 2e-6 * K + 1e-5
+        out32 = torch.full((M, N), 9.0, device=DEV)
+        ops_tc.gemm(out32, a, w, kernel="pair")
+        assert (out32.double() - want).abs().max() < tol
+        out16 = torch.full((M, N), 9.0, dtype=torch.bfloat16, device=DEV)
+        ops_tc.gemm(out16, a, w, kernel="pair")
+        assert (out16.double() - want).abs().max() < 0.005 * want.abs().max() + tol
+        base = _rand(M, N, seed=3)
+        acc = base.clone()
+        ops_tc.gemm(acc, a, w, accumulate=True, kernel="pair")
+        assert (acc.double() - (base.double() + want)).abs().max() < tol
+        again = torch.empty(M, N, device=DEV)
+        ops_tc.gemm(again, a, w, kernel="pair")
+        assert torch.equal(again, out32)
+        if N % 2 == 0:
+            act = torch.full((M, N // 2), 9.0, dtype=torch.bfloat16, device=DEV)
+            ops_tc.gemm(act, a, w, swiglu=True, kernel="pair")
+            gate, up = want[:, 0::2], want[:, 1::2]
+            ref = gate / (1 + torch.exp(-gate)) * up
+            assert (act.double() - ref).abs().max() < 0.005 * ref.abs().max() + 10 * tol
+        # the one-SM kernel computes the same sums in the same order
+        one = torch.empty(M, N, device=DEV)
+        ops_tc.gemm(one, a, w, kernel="tcgen05", split_k=False)
+        assert torch.equal(one, out32)
+        assert ops_tc.device_error() == 0
+    finally:
+        ops_tc.PAIR_MAX_TILE[0] = 0
+
+
 def _paged(k, v, lens, dtype, extra_pages=3, seed=0):
     """Dense per-sequence K/V [len, KVH, hd] -> one cache entry [pages, 2, KVH, 64, hd] with
     shuffled pages, and the page tables."""

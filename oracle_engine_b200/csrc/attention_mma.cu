@@ -395,6 +395,271 @@ attn_mma_kernel(const AttnArgs a) {
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// Decoded tokens, one CTA per (sequence, KV head), the WARPS of the CTA split the keys.
+// Every warp holds the same 16 query rows (the G heads of the group for the one new token),
+// walks half pages (32 keys) warp, warp + NW, ... of the sequence through a double buffer of
+// its own (cp.async, no CTA-wide barrier in the loop) and keeps its own running softmax; at
+// the end the warps' partial results are added in warp order through shared memory.  The
+// kernel also rotates q and the new token's k and writes k and v to the cache (as the fused
+// path of attn_mma_kernel does), so a decode step needs one attention launch and no scratch
+// in global memory.  For batches whose (sequence, KV head) pairs alone give enough CTAs.
+// ---------------------------------------------------------------------------------------
+constexpr int TB = 32;                          // keys per tile of a warp
+constexpr int TB_BYTES = TB * ROW_BYTES;
+constexpr int WARP_STAGE_BYTES = 2 * TB_BYTES;  // K and V
+constexpr int WARP_BYTES = 2 * WARP_STAGE_BYTES;
+
+__device__ __forceinline__ void load_half_page(uint8_t* ks, uint8_t* vs, const bf16* cache, int page, int half, int kvh, int KVH, int lane) {
+    const bf16* kg = cache + (((size_t)page * 2 + 0) * KVH + kvh) * (size_t)(BN * HD) + (size_t)half * TB * HD;
+    const bf16* vg = cache + (((size_t)page * 2 + 1) * KVH + kvh) * (size_t)(BN * HD) + (size_t)half * TB * HD;
+    constexpr int CHUNKS = TB * HD / 8;
+#pragma unroll
+    for (int c0 = 0; c0 < CHUNKS; c0 += 32) {
+        const int c = c0 + lane;
+        const int row = c / (HD / 8), col = c % (HD / 8);
+        cp_async16(ks + row * ROW_BYTES + col * 16, kg + (size_t)c * 8);
+        cp_async16(vs + row * ROW_BYTES + col * 16, vg + (size_t)c * 8);
+    }
+}
+
+template <int NW>
+__global__ void __launch_bounds__(NW * 32, 1)
+attn_decode_warps_kernel(const AttnArgs a) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.z, kvh = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int G = a.H / a.KVH;
+    const int qlen = a.seq_qlen[b];
+    const long long packed0 = a.cu_q[b];
+    if (qlen <= 0) return;                                   // a padding sequence: its row is never read
+    const int pos = a.seq_start[b];                          // the new token's position
+    const int key_lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    const int hp_lo = key_lo / TB, hp_hi = pos / TB;
+    const int* trow = a.tables + (size_t)b * a.max_pages;
+    uint8_t* mine = smem + (size_t)warp * WARP_BYTES;
+
+    // this warp's first tiles are requested before anything else
+    const int n_my = hp_lo + warp <= hp_hi ? (hp_hi - hp_lo - warp) / NW + 1 : 0;
+    if (n_my > 0) {
+        const int hp = hp_lo + warp;
+        load_half_page(mine, mine + TB_BYTES, a.cache, trow[hp >> 1], hp & 1, kvh, a.KVH, lane);
+    }
+    cp_async_commit();
+
+    bool valid[2];
+    int head[2];
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        const int r = gid + i * 8;
+        valid[i] = r < G;
+        head[i] = kvh * G + (valid[i] ? r : 0);
+    }
+    // Q fragments (A operand): rows gid and gid + 8 are heads of the group
+    uint32_t qf[KS][4];
+#pragma unroll
+    for (int ks = 0; ks < KS; ks++) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            if (valid[i]) {
+                const bf16* qr = a.q + packed0 * a.q_stride + (size_t)head[i] * HD + ks * 16 + tig * 2;
+                qf[ks][i] = *(const uint32_t*)qr;
+                qf[ks][i + 2] = *(const uint32_t*)(qr + 8);
+            } else {
+                qf[ks][i] = 0u;
+                qf[ks][i + 2] = 0u;
+            }
+        }
+    }
+    if (a.cos_tab != nullptr) {
+        // rotate-half pairs (d, d + HD/2) sit in the same lane, KS/2 k-steps apart
+#pragma unroll
+        for (int ks = 0; ks < KS / 2; ks++) {
+#pragma unroll
+            for (int x = 0; x < 4; x++) {
+                const int d = ks * 16 + tig * 2 + (x >> 1) * 8;
+                const float2 cs = *(const float2*)(a.cos_tab + (size_t)pos * (HD / 2) + d);
+                const float2 sn = *(const float2*)(a.sin_tab + (size_t)pos * (HD / 2) + d);
+                const __nv_bfloat162 lo = *(__nv_bfloat162*)&qf[ks][x];
+                const __nv_bfloat162 hi = *(__nv_bfloat162*)&qf[ks + KS / 2][x];
+                const float x0a = __low2float(lo), x0b = __high2float(lo), x1a = __low2float(hi), x1b = __high2float(hi);
+                qf[ks][x] = pack_bf16(x0a * cs.x - x1a * sn.x, x0b * cs.y - x1b * sn.y);
+                qf[ks + KS / 2][x] = pack_bf16(x0a * sn.x + x1a * cs.x, x0b * sn.y + x1b * cs.y);
+            }
+        }
+    }
+
+    float oacc[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; n++) { oacc[n][0] = oacc[n][1] = oacc[n][2] = oacc[n][3] = 0.f; }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+    for (int it = 0; it < n_my; it++) {
+        const int hp = hp_lo + warp + it * NW;
+        uint8_t* ks_cur = mine + (size_t)(it & 1) * WARP_STAGE_BYTES;
+        uint8_t* vs_cur = ks_cur + TB_BYTES;
+        if (it + 1 < n_my) {
+            uint8_t* nxt = mine + (size_t)((it + 1) & 1) * WARP_STAGE_BYTES;
+            const int hn = hp + NW;
+            load_half_page(nxt, nxt + TB_BYTES, a.cache, trow[hn >> 1], hn & 1, kvh, a.KVH, lane);
+        }
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncwarp();
+        if (hp == hp_hi && a.cache_w != nullptr) {
+            // this warp holds the tile of the new token: rotate its key, store key and value in the
+            // cache, and put them into the staged tile as well
+            const int r = pos % TB;
+            const bf16* krow = a.q + packed0 * a.q_stride + (size_t)(a.H + kvh) * HD;
+            const bf16* vrow = krow + (size_t)a.KVH * HD;
+            const size_t page = (size_t)trow[pos / BN];
+            bf16* kc = a.cache_w + ((page * 2 + 0) * a.KVH + kvh) * (size_t)(BN * HD) + (size_t)(pos % BN) * HD;
+            bf16* vc = a.cache_w + ((page * 2 + 1) * a.KVH + kvh) * (size_t)(BN * HD) + (size_t)(pos % BN) * HD;
+            bf16* ksm = (bf16*)(ks_cur + r * ROW_BYTES);
+            bf16* vsm = (bf16*)(vs_cur + r * ROW_BYTES);
+            for (int d = lane; d < HD / 2; d += 32) {
+                float k0 = __bfloat162float(krow[d]), k1 = __bfloat162float(krow[d + HD / 2]);
+                if (a.cos_tab != nullptr) {
+                    const float c = a.cos_tab[(size_t)pos * (HD / 2) + d], sn = a.sin_tab[(size_t)pos * (HD / 2) + d];
+                    const float r0 = k0 * c - k1 * sn, r1 = k0 * sn + k1 * c;
+                    k0 = r0; k1 = r1;
+                }
+                const bf16 b0 = __float2bfloat16_rn(k0), b1 = __float2bfloat16_rn(k1);
+                const bf16 v0 = vrow[d], v1 = vrow[d + HD / 2];
+                kc[d] = b0; kc[d + HD / 2] = b1; ksm[d] = b0; ksm[d + HD / 2] = b1;
+                vc[d] = v0; vc[d + HD / 2] = v1; vsm[d] = v0; vsm[d + HD / 2] = v1;
+            }
+            __syncwarp();
+        }
+
+        // S = Q K^T for the 16 rows and the tile's 32 keys
+        float sacc[TB / 8][4];
+#pragma unroll
+        for (int n = 0; n < TB / 8; n++) { sacc[n][0] = sacc[n][1] = sacc[n][2] = sacc[n][3] = 0.f; }
+        {
+            const int m = lane >> 3, r = lane & 7;
+            const uint8_t* kbase = ks_cur + ((m >> 1) * 8 + r) * ROW_BYTES + (m & 1) * 16;
+            uint32_t kb[2][TB / 16][4];
+#pragma unroll
+            for (int np = 0; np < TB / 16; np++) ldmatrix_x4(kb[0][np], kbase + np * 16 * ROW_BYTES);
+#pragma unroll
+            for (int ks = 0; ks < KS; ks++) {
+                if (ks + 1 < KS) {
+#pragma unroll
+                    for (int np = 0; np < TB / 16; np++)
+                        ldmatrix_x4(kb[(ks + 1) & 1][np], kbase + np * 16 * ROW_BYTES + (ks + 1) * 32);
+                }
+#pragma unroll
+                for (int np = 0; np < TB / 16; np++) {
+                    mma_bf16(sacc[2 * np], qf[ks], kb[ks & 1][np][0], kb[ks & 1][np][1]);
+                    mma_bf16(sacc[2 * np + 1], qf[ks], kb[ks & 1][np][2], kb[ks & 1][np][3]);
+                }
+            }
+        }
+        float rmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < TB / 8; n++) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int i = e >> 1;
+                const int key = hp * TB + n * 8 + tig * 2 + (e & 1);
+                const bool ok = valid[i] && key <= pos && key >= key_lo;
+                const float sv = ok ? sacc[n][e] * a.scale_log2 : -INFINITY;
+                sacc[n][e] = sv;
+                rmax[i] = fmaxf(rmax[i], sv);
+            }
+        }
+        float alpha[2], m_use[2];
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            rmax[i] = fmaxf(rmax[i], __shfl_xor_sync(0xffffffffu, rmax[i], 1));
+            rmax[i] = fmaxf(rmax[i], __shfl_xor_sync(0xffffffffu, rmax[i], 2));
+            const float m_new = fmaxf(m_run[i], rmax[i]);
+            m_use[i] = (m_new == -INFINITY) ? 0.f : m_new;
+            alpha[i] = exp2f(m_run[i] - m_use[i]);
+            m_run[i] = m_new;
+        }
+        float rsum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int n = 0; n < TB / 8; n++) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float p = exp2f(sacc[n][e] - m_use[e >> 1]);
+                sacc[n][e] = p;
+                rsum[e >> 1] += p;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 2; i++) l_run[i] = l_run[i] * alpha[i] + rsum[i];
+#pragma unroll
+        for (int n = 0; n < HD / 8; n++) {
+            oacc[n][0] *= alpha[0]; oacc[n][1] *= alpha[0];
+            oacc[n][2] *= alpha[1]; oacc[n][3] *= alpha[1];
+        }
+#pragma unroll
+        for (int kk = 0; kk < TB / 16; kk++) {
+            uint32_t pa[4];
+            pa[0] = pack_bf16(sacc[2 * kk][0], sacc[2 * kk][1]);
+            pa[1] = pack_bf16(sacc[2 * kk][2], sacc[2 * kk][3]);
+            pa[2] = pack_bf16(sacc[2 * kk + 1][0], sacc[2 * kk + 1][1]);
+            pa[3] = pack_bf16(sacc[2 * kk + 1][2], sacc[2 * kk + 1][3]);
+            const int m = lane >> 3, r = lane & 7;
+            const uint8_t* vbase = vs_cur + (kk * 16 + (m & 1) * 8 + r) * ROW_BYTES + (m >> 1) * 16;
+            uint32_t vb[2][4];
+            ldmatrix_x4_trans(vb[0], vbase);
+#pragma unroll
+            for (int dp = 0; dp < KS; dp++) {
+                if (dp + 1 < KS) ldmatrix_x4_trans(vb[(dp + 1) & 1], vbase + (dp + 1) * 32);
+                mma_bf16(oacc[2 * dp], pa, vb[dp & 1][0], vb[dp & 1][1]);
+                mma_bf16(oacc[2 * dp + 1], pa, vb[dp & 1][2], vb[dp & 1][3]);
+            }
+        }
+        __syncwarp();                                       // the stage is refilled two tiles from now
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+    }
+    // the warps' partial results, added in warp order
+    __syncthreads();                                        // every warp has left its staging buffers
+    float* part = (float*)smem;                             // [NW][G][HD + 2]
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        if (!valid[i]) continue;
+        float* p = part + ((size_t)warp * G + gid + i * 8) * (HD + 2);
+#pragma unroll
+        for (int n = 0; n < HD / 8; n++) {
+            p[n * 8 + tig * 2] = oacc[n][2 * i];
+            p[n * 8 + tig * 2 + 1] = oacc[n][2 * i + 1];
+        }
+        if (tig == 0) { p[HD] = m_run[i]; p[HD + 1] = l_run[i]; }
+    }
+    __syncthreads();
+    bf16* obase = a.out + packed0 * (long long)(a.H * HD) + (size_t)kvh * G * HD;
+    for (int idx = threadIdx.x; idx < G * HD; idx += NW * 32) {
+        const int gh = idx / HD, d = idx % HD;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NW; w++) m = fmaxf(m, part[((size_t)w * G + gh) * (HD + 2) + HD]);
+        float l = 0.f, o = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; w++) {
+            const float* p = part + ((size_t)w * G + gh) * (HD + 2);
+            if (p[HD] != -INFINITY) {
+                const float wgt = exp2f(p[HD] - m);
+                l += p[HD + 1] * wgt;
+                o += p[d] * wgt;
+            }
+        }
+        obase[idx] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+    }
+}
+
 // out[row, head] = sum_s o_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), splits taken in order.
 __global__ void attn_merge_kernel(bf16* __restrict__ out, const float* __restrict__ partial,
                                   const int* __restrict__ tok_seq, int H, int n_splits) {
@@ -529,6 +794,34 @@ int oe_attn_decode_fused_bf16(bf16* out, const bf16* qkv, long long qkv_stride, 
     if (nwarps == 1) return launch<1>(a, n_seqs, a.n_splits, st);
     if (nwarps == 2) return launch<2>(a, n_seqs, a.n_splits, st);
     return launch<4>(a, n_seqs, a.n_splits, st);
+}
+
+// The same decode step with the warps of a CTA splitting the keys (attn_decode_warps_kernel):
+// one launch, no scratch.  Needs G = H/KVH <= 16.
+int oe_attn_decode_warps_bf16(bf16* out, const bf16* qkv, long long qkv_stride, const float* cos_tab,
+                              const float* sin_tab, bf16* cache, int has_kv, const int* tables, int max_pages,
+                              const int* cu_q, const int* seq_start, const int* seq_qlen, int n_seqs, int H, int KVH,
+                              int window, float scale, cudaStream_t st) {
+    if (n_seqs <= 0) return 0;
+    if (H % KVH || ((uintptr_t)qkv & 3) || (qkv_stride & 1) || (HD % 32)) return OE_ERR_UNSUPPORTED;
+    const int G = H / KVH;
+    if (G > 16 || n_seqs > 65535) return OE_ERR_UNSUPPORTED;
+    AttnArgs a;
+    a.out = out; a.q = qkv; a.q_stride = qkv_stride; a.cache = cache; a.tables = tables; a.max_pages = max_pages;
+    a.cu_q = cu_q; a.seq_start = seq_start; a.seq_qlen = seq_qlen; a.H = H; a.KVH = KVH; a.window = window;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    a.partial = nullptr; a.fused = 1; a.cos_tab = cos_tab; a.sin_tab = sin_tab; a.cache_w = has_kv ? cache : nullptr;
+    a.counters = nullptr; a.tokens_per_tile = 1; a.n_splits = 1; a.stages = 2;
+    constexpr int NW = (6 * WARP_BYTES <= 220 * 1024) ? 6 : 3;
+    static_assert(NW * 16 * (HD + 2) * 4 <= NW * WARP_BYTES, "the merge scratch shares the staging buffers");
+    const size_t smem = (size_t)NW * WARP_BYTES;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_warps_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    return oe_launch(attn_decode_warps_kernel<NW>, dim3(1, KVH, n_seqs), dim3(NW * 32), smem, st, a);
 }
 
 }  // extern "C"

@@ -171,6 +171,10 @@ def _attn_lib(head_dim: int):
                                                   c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                                   c_int, c_float, c_int, c_void_p, c_void_p, c_void_p]
         lib.oe_attn_decode_fused_bf16.restype = c_int
+        lib.oe_attn_decode_warps_bf16.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
+                                                  c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                  c_int, c_float, c_void_p]
+        lib.oe_attn_decode_warps_bf16.restype = c_int
         lib.oe_attn_mma_partial_floats.argtypes = [c_int, c_int, c_int]
         lib.oe_attn_mma_partial_floats.restype = c_longlong
         _state[key] = lib
@@ -251,6 +255,46 @@ def attention(out, qkv, cache, tables, ctx, n_heads: int, n_kv_heads: int, head_
 
 def decode_fused_supported(head_dim: int, n_heads: int, n_kv_heads: int) -> bool:
     return attention_supported(head_dim, n_heads, n_kv_heads) and head_dim % 32 == 0
+
+
+DECODE_KERNEL = ["auto"]     # "auto", "warps", "split" (tests pin a kernel)
+DECODE_WARPS_FULL_CTAS = 48  # (sequence, KV head) pairs from which long contexts stay on the warps kernel too
+
+
+def decode_warps_supported(head_dim: int, n_heads: int, n_kv_heads: int) -> bool:
+    return decode_fused_supported(head_dim, n_heads, n_kv_heads) and n_heads // n_kv_heads <= 16
+
+
+def decode_uses_warps(n_seqs: int, long_context: bool, head_dim: int, n_heads: int, n_kv_heads: int) -> bool:
+    """Whether a decode step goes to the kernel whose warps split the keys (one launch, no
+    scratch) rather than to CTAs that split the keys plus a merge.  Short contexts: always (a
+    warp walks a few half pages).  Long contexts: when the (sequence, KV head) pairs alone give
+    enough CTAs; with few sequences more CTAs per sequence win.  Depends on the batch size and
+    the step's context class only; a captured graph is kept per class."""
+    if DECODE_KERNEL[0] == "split" or not decode_warps_supported(head_dim, n_heads, n_kv_heads):
+        return False
+    return DECODE_KERNEL[0] == "warps" or not long_context or n_seqs * n_kv_heads >= DECODE_WARPS_FULL_CTAS
+
+
+def attention_decode_warps(out, qkv, cos, sin, cache, tables, ctx, n_heads: int, n_kv_heads: int, head_dim: int,
+                           window: int, scale: float, has_kv: bool) -> None:
+    """The decode step's mixer core (rotation, cache write, attention) in one launch: one CTA per
+    (sequence, KV head), whose warps split the keys (csrc/attention_mma.cu).  Same arguments as
+    attention_decode_fused."""
+    if out.dtype != torch.bfloat16 or qkv.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
+        raise KernelError("attention_decode_warps: bfloat16 tensors expected")
+    width = (n_heads + (2 * n_kv_heads if has_kv else 0)) * head_dim
+    if qkv.shape[1] != width or qkv.stride(1) != 1 or not out.is_contiguous() or not cache.is_contiguous():
+        raise KernelError(f"attention_decode_warps: qkv must be [B, {width}], out and cache contiguous")
+    if tuple(cache.shape[1:]) != (2, n_kv_heads, ops.PAGE, head_dim):
+        raise KernelError("attention_decode_warps: cache entry must be [pages, 2, KVH, PAGE, head_dim]")
+    lib = _attn_lib(head_dim)
+    code = lib.oe_attn_decode_warps_bf16(
+        out.data_ptr(), qkv.data_ptr(), qkv.stride(0), None if cos is None else cos.data_ptr(),
+        None if sin is None else sin.data_ptr(), cache.data_ptr(), int(has_kv), tables.data_ptr(), tables.shape[1],
+        ctx.cu_q.data_ptr(), ctx.seq_start.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.n_seqs, n_heads, n_kv_heads,
+        int(window), float(scale), torch.cuda.current_stream().cuda_stream)
+    ops._check(code, "attention_decode_warps")
 
 
 def _attn_counters(device):

@@ -85,6 +85,11 @@ def build_plan(seqs: list, starts: list, pad_seqs: int = 0, pad_tokens: int = 0,
         all_decode=all(n == 1 for n in qlens) and B > 0)
 
 
+# Steps are classed by the longest sequence they touch: kernels may be chosen by the class, and a
+# captured decode graph is kept per class, so the choice stays valid as sequences grow.
+LONG_CONTEXT_TOKENS = 1536
+
+
 @dataclass
 class StepContext:
     """Device-side view of a step, handed to every part."""
@@ -103,6 +108,7 @@ class StepContext:
     max_qlen: int
     max_kvlen: int
     all_decode: bool
+    long_context: bool = False      # some sequence is longer than LONG_CONTEXT_TOKENS (kernels may choose by it)
 
 
 class StepBuffers:
@@ -174,4 +180,5 @@ class StepBuffers:
         return StepContext(
             n_tokens=self.n_tokens, n_seqs=self.n_seqs, n_want=self.n_want, token_ids=v[0], tok_seq=v[1],
             tok_pos=v[2], seq_slot=v[3], seq_start=v[4], seq_qlen=v[5], cu_q=v[6], want_rows=v[7], tables=tabs,
-            max_qlen=plan.max_qlen, max_kvlen=plan.max_kvlen, all_decode=plan.all_decode)
+            max_qlen=plan.max_qlen, max_kvlen=plan.max_kvlen, all_decode=plan.all_decode,
+            long_context=plan.max_kvlen > LONG_CONTEXT_TOKENS)

@@ -21,7 +21,7 @@ import torch
 
 from ..cache.kv_cache import CacheView
 from ..csrc import ops
-from .batch import SequenceStep, StepBuffers, build_plan
+from .batch import LONG_CONTEXT_TOKENS, SequenceStep, StepBuffers, build_plan
 
 _BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 
@@ -64,7 +64,7 @@ class Stepper:
         self._state_views = [state.views(e) for e in range(self.n_entries)]
         parts_ok = all(getattr(p, "graph_safe", False) for layer in model.layers for p in layer.parts())
         self.use_graphs = bool(use_graphs and parts_ok)
-        self._graphs: dict[int, _DecodeGraph] = {}
+        self._graphs: dict[tuple, _DecodeGraph] = {}      # (padded batch size, long context) -> graph
         self._eager_buffers: dict[tuple, StepBuffers] = {}
         self.launch_counter = None         # set by the bench to count kernel launches
 
@@ -132,10 +132,12 @@ class Stepper:
     def _step_graph(self, seqs, starts, tables_changed=True):
         B = len(seqs)
         bucket = _bucket(B)
-        g = self._graphs.get(bucket)
+        # one graph per padded batch size and context class: kernels chosen by the class stay right
+        gkey = (bucket, max(starts) + 1 > LONG_CONTEXT_TOKENS)
+        g = self._graphs.get(gkey)
         if g is None:
             g = _DecodeGraph(bucket, StepBuffers(bucket, bucket, bucket, self._table_shapes(bucket), self.rt.device))
-            self._graphs[bucket] = g
+            self._graphs[gkey] = g
         key = tuple(s.slot for s in seqs)
         if key == g.key and g.version == self.cache.version:
             # the same sequences one token further: only tokens and positions change

@@ -403,18 +403,21 @@ def test_argmax_and_sampling():
         assert counters[5].item() == (3 if c["temperature"] > 0 else 0) and hist_count[5].item() == 10
 
 
+@pytest.mark.parametrize("kernel", ["fused", "warps"])
 @pytest.mark.parametrize("H,KVH,hd,window,rotate", [(24, 8, 128, 0, True), (6, 2, 32, 0, True), (8, 8, 64, 100, False),
-                                                     (4, 1, 32, 0, True)])
-def test_attention_decode_fused(H, KVH, hd, window, rotate):
-    """One kernel for rotation, cache write, split attention and merge, against the plain parts."""
+                                                     (4, 1, 32, 0, True), (16, 1, 64, 300, True)])
+def test_attention_decode_fused(H, KVH, hd, window, rotate, kernel):
+    """One kernel for rotation, cache write, attention and merge (the keys split over CTAs, or over
+    the warps of one CTA), against the plain parts."""
     from types import SimpleNamespace
     from oracle_engine_b200.csrc import ops_tc
-    lens = [1, 64, 65, 200, 130, 17, 128]                      # length including the new token
+    decode = ops_tc.attention_decode_fused if kernel == "fused" else ops_tc.attention_decode_warps
+    lens = [1, 64, 65, 200, 130, 17, 128, 33, 600]             # length including the new token
     B = len(lens)
     g = torch.Generator().manual_seed(hd + H)
     bf = lambda t: t.to(torch.bfloat16)                       # noqa: E731
     inv = pl.rope_inv_freq(hd, 10000.0, None)
-    ang = torch.arange(256, dtype=torch.float64)[:, None] * inv[None]
+    ang = torch.arange(1024, dtype=torch.float64)[:, None] * inv[None]
     cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
     k_old = [bf(torch.randn(n - 1, KVH, hd, generator=g)) for n in lens]        # already rotated, in the cache
     v_old = [bf(torch.randn(n - 1, KVH, hd, generator=g)) for n in lens]
@@ -429,8 +432,8 @@ def test_attention_decode_fused(H, KVH, hd, window, rotate):
                           seq_qlen=i32([1] * B + [0]), n_seqs=B + 1)
     out = torch.full((B + 1, H * hd), 5.0, dtype=torch.bfloat16, device=DEV)
     qkv_dev = torch.cat([qkv, torch.zeros(1, qkv.shape[1], dtype=torch.bfloat16)]).to(DEV)
-    ops_tc.attention_decode_fused(out, qkv_dev, cos if rotate else None, sin if rotate else None, cache, tab, ctx, H, KVH,
-                                  hd, window, 1 / math.sqrt(hd), True)
+    decode(out, qkv_dev, cos if rotate else None, sin if rotate else None, cache, tab, ctx, H, KVH,
+           hd, window, 1 / math.sqrt(hd), True)
     for b, n in enumerate(lens):
         q = qkv[b, :H * hd].double().reshape(1, H, hd)
         k = qkv[b, H * hd:(H + KVH) * hd].double().reshape(1, KVH, hd)
@@ -452,6 +455,6 @@ def test_attention_decode_fused(H, KVH, hd, window, rotate):
     # an entry that reads another entry's cache: queries only, nothing stored
     out2 = torch.full_like(out, 5.0)
     q_only = qkv_dev[:, :H * hd].contiguous()
-    ops_tc.attention_decode_fused(out2, q_only, cos if rotate else None, sin if rotate else None, cache, tab, ctx, H, KVH,
-                                  hd, window, 1 / math.sqrt(hd), False)
+    decode(out2, q_only, cos if rotate else None, sin if rotate else None, cache, tab, ctx, H, KVH,
+           hd, window, 1 / math.sqrt(hd), False)
     assert torch.equal(out2[:B], out[:B])

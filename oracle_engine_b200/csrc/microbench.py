@@ -3,6 +3,7 @@
     python -m oracle_engine_b200.csrc.microbench gemm --m 8 --n 16384 --k 3072 [--out swiglu] [--kernel auto]
     python -m oracle_engine_b200.csrc.microbench attention --batch 8 --context 640 [--prompt 0]
     python -m oracle_engine_b200.csrc.microbench attention --batch 1 --prompt 2048
+    python -m oracle_engine_b200.csrc.microbench attention --batch 8 --context 640 --decode warps
     python -m oracle_engine_b200.csrc.microbench norm --rows 2048 --width 3072
 
 In the manner of the reference's benchmark/micro_gemm.cpp (:97-128 correctness against a
@@ -108,6 +109,18 @@ def run_attention(a):
                           seq_qlen=i32([qlen] * B), tok_seq=i32([b for b in range(B) for _ in range(qlen)]),
                           n_seqs=B, n_tokens=T, max_qlen=qlen, all_decode=(qlen == 1))
     scale = 1 / math.sqrt(hd)
+    if a.decode != "split" and not a.prompt:
+        # the one-launch decode kernels: rotation, cache write, attention and merge together
+        half = hd // 2
+        ang = torch.arange(ctx_len, dtype=torch.float64)[:, None] * (10000.0 ** (-torch.arange(half, dtype=torch.float64) / half))[None]
+        cos, sin = torch.cos(ang).float().to(dev), torch.sin(ang).float().to(dev)
+        fn = ops_tc.attention_decode_warps if a.decode == "warps" else ops_tc.attention_decode_fused
+        fn(out, qkv, cos, sin, caches[0], tables, ctx, H, KVH, hd, 0, scale, True)
+        torch.cuda.synchronize()
+        us = timed(lambda i: fn(out, qkv, cos, sin, caches[i % copies], tables, ctx, H, KVH, hd, 0, scale, True), a.iters, a.once)
+        report(f"decode attention ({a.decode}) B={B} context={ctx_len} H={H} KVH={KVH} hd={hd}", us,
+               B * ctx_len * 2 * KVH * hd * 2 + 2 * T * H * hd * 2, 4.0 * B * H * hd * ctx_len, float("nan"))
+        return
     ops_tc.attention(out, qkv, caches[0], tables, ctx, H, KVH, hd, 0, scale)
     # correctness on the first sequence's last row, head 0
     kk = caches[0][:pages, 0, 0].reshape(-1, hd)[:ctx_len].double()
@@ -150,6 +163,9 @@ def main(argv=None):
     at.add_argument("--heads", type=int, default=24)
     at.add_argument("--kv-heads", type=int, default=8)
     at.add_argument("--head-dim", type=int, default=128)
+    at.add_argument("--decode", default="split", choices=["split", "warps", "fused"],
+                    help="decode kernel: keys split over CTAs plus a merge (after a separate rotation kernel, not timed "
+                         "here), over the warps of one CTA, or the one-warp fused kernel")
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=2048)
     n.add_argument("--width", type=int, default=3072)

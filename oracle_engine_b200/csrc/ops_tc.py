@@ -259,6 +259,7 @@ def decode_fused_supported(head_dim: int, n_heads: int, n_kv_heads: int) -> bool
 
 DECODE_KERNEL = ["auto"]     # "auto", "warps", "split" (tests pin a kernel)
 DECODE_WARPS_FULL_CTAS = 48  # (sequence, KV head) pairs from which long contexts stay on the warps kernel too
+DECODE_WARPS_MAX_CTAS = 300  # more pairs than this: the one-warp kernel, several CTAs an SM
 
 
 def decode_warps_supported(head_dim: int, n_heads: int, n_kv_heads: int) -> bool:
@@ -273,7 +274,12 @@ def decode_uses_warps(n_seqs: int, long_context: bool, head_dim: int, n_heads: i
     the step's context class only; a captured graph is kept per class."""
     if DECODE_KERNEL[0] == "split" or not decode_warps_supported(head_dim, n_heads, n_kv_heads):
         return False
-    return DECODE_KERNEL[0] == "warps" or not long_context or n_seqs * n_kv_heads >= DECODE_WARPS_FULL_CTAS
+    if DECODE_KERNEL[0] == "warps":
+        return True
+    pairs = n_seqs * n_kv_heads
+    if pairs > DECODE_WARPS_MAX_CTAS:
+        return False                      # every SM has several one-warp CTAs of the fused kernel: measured faster
+    return not long_context or pairs >= DECODE_WARPS_FULL_CTAS
 
 
 def attention_decode_warps(out, qkv, cos, sin, cache, tables, ctx, n_heads: int, n_kv_heads: int, head_dim: int,

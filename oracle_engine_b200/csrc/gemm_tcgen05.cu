@@ -502,11 +502,11 @@ int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, 
     CUtensorMap map_a, map_b;
     dim3 grid;
     const int n_kb = (K + BLOCK_K - 1) / BLOCK_K;
-    // 48..128 tokens with a short K (or more than 96 tokens): no split over K.  The
-    // activations stay the 128-row operand (rows beyond M are not fetched) and a narrow
-    // weight tile per CTA gives about one CTA per SM; measured faster than swap + split-K
-    // there (e.g. 64 tokens, 3072x3072: 23 vs 32 us), slower for long K or fewer tokens.
-    const bool narrow = M <= 128 && M >= 48 && (K <= 4096 || M > 96);
+    // 48..128 tokens with a short K: no split over K.  The activations stay the 128-row
+    // operand (rows beyond M are not fetched) and a narrow weight tile per CTA gives about one
+    // CTA per SM; measured faster than swap + split-K there (e.g. 96 tokens, 3072x3072: 21 vs
+    // 28 us), slower for long K (128 tokens, 3072x8192: 50 vs 39 us) or fewer tokens.
+    const bool narrow = M <= 128 && M >= 48 && K <= 4096;
     if (narrow) {
         g.swap = 0;
         int nt = ((N + sm_count - 1) / sm_count + 15) / 16 * 16;

@@ -57,7 +57,8 @@ def gemm_supported(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.stride(1) == 1)
 
 
-SKINNY_MAX_TOKENS = 8       # up to here the weight-streaming kernel (gemm_skinny.cu) is used
+SKINNY_MAX_TOKENS = 16      # up to here the weight-streaming kernel (gemm_skinny.cu) is used (measured: 58 vs 65 us
+                            # for a layer's four products at 16 tokens; from 24 tokens on tcgen05 wins)
 PAIR_MIN_TOKENS = 256       # from here on the two-SM kernel (gemm_tcgen05_pair.cu) for stores; measured the
                             # same speed as the one-SM kernel or a little faster, except with the accumulate epilogue
 PAIR_MAX_TILE = [0]         # tests: an upper limit for the pair kernel's tile width (0 = none)

@@ -8,11 +8,11 @@
 //                  shared memory (TMA), S float32 in tensor memory (two buffers);
 //   softmax        128 threads, one row each: tcgen05.ld of the row's 64 scores, causal /
 //                  window mask, maximum and sum in float32 (no shuffles: a thread holds its
-//                  whole row), P = exp2(s * scale - m) rounded to bf16 and written to shared
-//                  memory in the swizzled K-major layout;
-//   O += P V       tcgen05.mma M=128 N=head_dim K=64, P from shared memory, V as the
-//                  MN-major B operand straight from the page ([key][dim] rows of 128 bytes),
-//                  O float32 in tensor memory for the whole tile.
+//                  whole row), P = exp2(s * scale - m) rounded to bf16 and stored back into
+//                  the first half of the same tensor-memory columns (tcgen05.st);
+//   O += P V       tcgen05.mma M=128 N=head_dim K=64, P as the A operand from tensor memory,
+//                  V as the MN-major B operand straight from the page ([key][dim] rows of 128
+//                  bytes), O float32 in tensor memory for the whole tile.
 // The reference maximum m of a row moves only when the row's maximum has grown by more than
 // 2^8 since it was set: then the row's O (tcgen05.ld, multiply, tcgen05.st) and its sum are
 // rescaled before the block's P V is issued.  Between two moves P <= 2^8, which bf16 and the
@@ -20,7 +20,7 @@
 // is the one of the plain online softmax.  The decision is taken per warp (tensor-memory
 // loads and stores are warp-wide).
 // The MMA thread issues S of block j+1 before it waits for P of block j, so the tensor pipe
-// and the softmax overlap; two CTAs share an SM (112 KB of shared memory, 256 columns of
+// and the softmax overlap; two CTAs share an SM (96 KB of shared memory, 256 columns of
 // tensor memory and at most 168 registers a thread each), which hides the latencies of one
 // CTA's softmax chain behind the other's.
 // Roles (192 threads): warp 0 = TMA producer (Q once, then K and V pages through two-stage
@@ -48,7 +48,6 @@ constexpr int SUB = HD / 64;               // 64-wide (128-byte) sub-tiles along
 constexpr int Q_BYTES = BM * HD * 2;       // SUB sub-tiles of [128][64]
 constexpr int KV_TILE = BN * HD * 2;       // one K or V page panel, SUB sub-tiles of [64][64]
 constexpr int STAGES = 2;                  // of the K ring and of the V ring
-constexpr int P_BYTES = BM * BN * 2;       // [128][64] bf16
 constexpr int THREADS = 192;
 constexpr uint32_t TMEM_COLS = 256;        // S: 2 x 64, O: HD
 constexpr uint32_t S_COL = 0, O_COL = 128;
@@ -60,11 +59,11 @@ __device__ int g_error = 0;
 struct Ctl {
     uint64_t q_full;
     uint64_t k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
-    uint64_t s_full[2], p_ready, pv_done;
+    uint64_t s_full[2], p_ready[2], pv_done, o_done;
     uint32_t tmem_base;
     int abort_flag;
 };
-constexpr int SMEM_NEEDED = Q_BYTES + 2 * STAGES * KV_TILE + P_BYTES + (int)sizeof(Ctl);
+constexpr int SMEM_NEEDED = Q_BYTES + 2 * STAGES * KV_TILE + (int)sizeof(Ctl);
 
 struct Args {
     bf16* out;                 // [T, H*HD]
@@ -152,6 +151,14 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t b
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same with the A operand in tensor memory (rows = lanes, two bf16 of consecutive k per column).
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -171,6 +178,13 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const float* v) {
           "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
           "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
           "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15]))
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16_u32(uint32_t taddr, const uint32_t* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+          "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
         : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -195,8 +209,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     uint8_t* q_s = smem;
     uint8_t* k_s = q_s + Q_BYTES;
     uint8_t* v_s = k_s + STAGES * KV_TILE;
-    uint8_t* p_s = v_s + STAGES * KV_TILE;
-    Ctl* ctl = (Ctl*)(p_s + P_BYTES);
+    Ctl* ctl = (Ctl*)(v_s + STAGES * KV_TILE);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.z, kvh = blockIdx.y;
@@ -207,8 +220,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             mbar_init(&ctl->v_full[s], 1); mbar_init(&ctl->v_empty[s], 1);
         }
         mbar_init(&ctl->s_full[0], 1); mbar_init(&ctl->s_full[1], 1);
-        mbar_init(&ctl->p_ready, 4);                       // one arrival per softmax warp
+        mbar_init(&ctl->p_ready[0], 4); mbar_init(&ctl->p_ready[1], 4);   // one arrival per softmax warp; one barrier per
+                                                           // S buffer: a warp may be a block ahead of the others
         mbar_init(&ctl->pv_done, 1);
+        mbar_init(&ctl->o_done, 1);
         ctl->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -300,21 +315,23 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     issue_s(i + 1);
                 }
                 // P_i is in shared memory, S_i has been read, O has been rescaled if it had to be
-                ok = mbar_wait(&ctl->p_ready, (uint32_t)i & 1u, ctl, 4);
+                ok = mbar_wait(&ctl->p_ready[i & 1], (uint32_t)(i >> 1) & 1u, ctl, 4);
                 if (!ok) break;
                 const int s = i % STAGES;
                 ok = mbar_wait(&ctl->v_full[s], (uint32_t)(i / STAGES) & 1u, ctl, 5);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t v_addr = smem_u32(v_s + (size_t)s * KV_TILE);
-                const uint32_t p_addr = smem_u32(p_s);
+                // P_i sits in the first 32 columns of S buffer i & 1: 16 keys = 8 columns per instruction
+                const uint32_t p_tmem = tmem_base + S_COL + (uint32_t)((i & 1) * BN);
 #pragma unroll
                 for (int k = 0; k < BN / 16; k++) {
-                    umma(tmem_base + O_COL, umma_desc(p_addr + k * 32, 16, 1024),
-                         umma_desc(v_addr + k * (16 * 128), BN * 128, 1024), idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+                    umma_ts(tmem_base + O_COL, p_tmem + (uint32_t)(k * 8),
+                            umma_desc(v_addr + k * (16 * 128), BN * 128, 1024), idesc_o, (i > 0 || k > 0) ? 1u : 0u);
                 }
                 umma_commit(&ctl->pv_done);
                 umma_commit(&ctl->v_empty[s]);               // V_i is no longer needed
+                if (i == n_blocks - 1) umma_commit(&ctl->o_done);   // O is complete
             }
         }
     } else {
@@ -352,15 +369,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 }
             }
             const float m_new = fmaxf(m_run, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2);
-            // P_{i-1} V_{i-1} has read the P buffer and has been added to O
-            if (i > 0) {
-                ok = mbar_wait(&ctl->pv_done, (uint32_t)(i - 1) & 1u, ctl, 7);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            }
             if (i == 0) {
                 m_run = m_new;
             } else if (__any_sync(0xffffffffu, m_new > m_run + RESCALE_STEP)) {
+                // P_{i-1} V_{i-1} must have been added to O before O is rescaled.  S_i is complete, so
+                // P_{i-2} V_{i-2} (issued before it) is too: the parity cannot be that of an earlier block
+                ok = mbar_wait(&ctl->pv_done, (uint32_t)(i - 1) & 1u, ctl, 7);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const float alpha = fast_exp2(m_run - (m_new == -INFINITY ? 0.f : m_new));
 #pragma unroll
                 for (int c0 = 0; c0 < HD; c0 += 16) {
@@ -377,30 +393,29 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             }
             const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-            // P row: 64 bf16 = 8 chunks of 16 bytes, chunk c stored at c ^ (row & 7)
-            uint8_t* prow = p_s + r * 128;
+            // P row: 64 bf16, two per column, into the first 32 columns of this S buffer (the scores
+            // are in registers by now); the tensor core reads it from there as the A operand of P V
+            uint32_t w[BN / 2];
 #pragma unroll
-            for (int ch = 0; ch < 8; ch++) {
-                uint32_t w[4];
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const float p0 = fast_exp2(fmaf(s[ch * 8 + 2 * e], a.scale_log2, neg_m));
-                    const float p1 = fast_exp2(fmaf(s[ch * 8 + 2 * e + 1], a.scale_log2, neg_m));
-                    sum4[e] += p0 + p1;
-                    __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                    w[e] = *(uint32_t*)&h;
-                }
-                *(uint4*)(prow + ((ch ^ (r & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+            for (int c = 0; c < BN / 2; c++) {
+                const float p0 = fast_exp2(fmaf(s[2 * c], a.scale_log2, neg_m));
+                const float p1 = fast_exp2(fmaf(s[2 * c + 1], a.scale_log2, neg_m));
+                sum4[c & 3] += p0 + p1;
+                __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                w[c] = *(uint32_t*)&h;
             }
+            tmem_st16_u32(lane_addr + S_COL + (uint32_t)((i & 1) * BN), w);
+            tmem_st16_u32(lane_addr + S_COL + (uint32_t)((i & 1) * BN + 16), w + 16);
+            tmem_st_wait();
             l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-            // make the row visible to the tensor core (async proxy), then signal
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(&ctl->p_ready);
+            if (lane == 0) mbar_arrive(&ctl->p_ready[i & 1]);
         }
         if (ok && active && n_blocks > 0) {
-            ok = mbar_wait(&ctl->pv_done, (uint32_t)(n_blocks - 1) & 1u, ctl, 8);
+            // a barrier of its own: the threads do not follow every phase of pv_done, so its parity
+            // could be that of an earlier block
+            ok = mbar_wait(&ctl->o_done, 0, ctl, 8);
             if (ok) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
@@ -499,9 +514,8 @@ int oe_attn_tc_bf16(bf16* out, const bf16* q, long long q_stride, const bf16* ca
         if (r != CUDA_SUCCESS) return 2000 + (int)r;
     }
     const int tiles = (max_qlen + a.tokens_per_tile - 1) / a.tokens_per_tile;
-    // two CTAs an SM: (228 KB - 2 x 1 KB reserved) / 2 each; the kernel checks that its tiles fit behind
-    // the 1024-byte boundary it needs and raises error 9 if they do not
-    const size_t smem = HD == 128 ? (size_t)115712 : (size_t)SMEM_NEEDED + 1024;
+    // two CTAs an SM; the kernel checks that its tiles fit behind the 1024-byte boundary it needs
+    const size_t smem = (size_t)SMEM_NEEDED + 1024;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

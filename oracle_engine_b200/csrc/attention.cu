@@ -19,8 +19,8 @@ constexpr int MAX_HD = 256;
 
 template <typename T>
 __global__ void __launch_bounds__(WARPS * 32)
-attn_paged_kernel(T* __restrict__ out, const T* __restrict__ q, int q_stride,
-                  const T* __restrict__ cache, const int* __restrict__ tables, int max_pages,
+attn_paged_kernel(T* out, const T* q, int q_stride,
+                  const T* cache, const int* __restrict__ tables, int max_pages,
                   const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                   int n_tokens, int H, int KVH, int hd, int window, float scale) {
     extern __shared__ float qs_all[];

@@ -661,7 +661,7 @@ attn_decode_warps_kernel(const AttnArgs a) {
 }
 
 // out[row, head] = sum_s o_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), splits taken in order.
-__global__ void attn_merge_kernel(bf16* __restrict__ out, const float* __restrict__ partial,
+__global__ void attn_merge_kernel(bf16* out, const float* partial,
                                   const int* __restrict__ tok_seq, int H, int n_splits) {
     pdl_launch_dependents();
     pdl_wait();

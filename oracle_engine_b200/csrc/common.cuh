@@ -24,6 +24,10 @@ typedef __nv_bfloat16 bf16;
 // overwrites).  pdl_wait() returns when every earlier kernel has completed and its
 // writes are visible.  Every kernel calls it, so completion is transitive along the
 // stream.  pdl_launch_dependents() lets the next kernel be scheduled early.
+// A kernel that starts early must read what earlier kernels wrote through the coherent path:
+// pointers to such data are NOT `const __restrict__` (which lets the compiler use the read-only
+// cache, valid only for data that does not change while the kernel is resident); weights and
+// the step's integer tables, written before the step's first kernel, may be.
 // Set OE_PDL=0 in the environment to launch without the attribute.
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

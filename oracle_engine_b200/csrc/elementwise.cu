@@ -33,7 +33,7 @@ __global__ void embed_gather_kernel(float* __restrict__ x, const T* __restrict__
 // y = (x * 1/sqrt(mean(x^2) + eps)) * w      (reference: core/ops.cpp:149-195)
 // ---------------------------------------------------------------------------------------
 template <typename T>
-__global__ void rmsnorm_kernel(T* __restrict__ y, const float* __restrict__ x,
+__global__ void rmsnorm_kernel(T* y, const float* x,
                                const float* __restrict__ w, int D, float eps) {
     __shared__ float red[32];
     pdl_launch_dependents();
@@ -63,7 +63,7 @@ template <> struct Out4<bf16> {
 
 template <typename T>
 __global__ void __launch_bounds__(256)
-rmsnorm_vec_kernel(T* __restrict__ y, const float* __restrict__ x, const float* __restrict__ w, int D, float eps) {
+rmsnorm_vec_kernel(T* y, const float* x, const float* __restrict__ w, int D, float eps) {
     __shared__ float red[32];
     constexpr int KEEP = 4;
     pdl_launch_dependents();
@@ -239,7 +239,7 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, int row_stride,
 // a = g / (1 + exp(-g)) * u, with gu = [g | u] per row   (reference: core/model.cpp:638-641)
 // ---------------------------------------------------------------------------------------
 template <typename T>
-__global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int FF, size_t total) {
+__global__ void swiglu_kernel(T* out, const T* gu, int FF, size_t total) {
     pdl_launch_dependents();
     pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -251,7 +251,7 @@ __global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int
     }
 }
 
-__global__ void gather_rows_f32_kernel(float* __restrict__ out, const float* __restrict__ x,
+__global__ void gather_rows_f32_kernel(float* out, const float* x,
                                        const int* __restrict__ rows, int D) {
     pdl_launch_dependents();
     pdl_wait();

@@ -16,7 +16,7 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 // MODE 0: C = acc (type TC);  MODE 1: C += acc (TC must be float: the residual stream)
 template <typename TA, typename TC, int MODE>
 __global__ void __launch_bounds__(256)
-gemm_nt_kernel(TC* __restrict__ C, const TA* __restrict__ A, const TA* __restrict__ W,
+gemm_nt_kernel(TC* C, const TA* A, const TA* __restrict__ W,
                int M, int N, int K, long long lda, long long ldc) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];

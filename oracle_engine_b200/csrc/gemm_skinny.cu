@@ -39,7 +39,7 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
 // UNROLL: 64-wide k chunks whose weight loads a warp has in flight at once.
 template <int NT, int WARPS, int UNROLL>
 __global__ void __launch_bounds__(WARPS * 32)
-gemm_skinny_kernel(void* __restrict__ C, const bf16* __restrict__ A, const bf16* __restrict__ W,
+gemm_skinny_kernel(void* C, const bf16* A, const bf16* __restrict__ W,
                    int M, int N, int K, long long lda, long long ldc, int out_kind) {
     __shared__ float red[WARPS][ROWS][8 * NT + 1];
     __shared__ float total[ROWS][8 * NT + 1];
@@ -137,17 +137,21 @@ int oe_gemm_skinny_supported(const void* A, const void* W, int M, int N, int K, 
 }
 
 // out_kind: 0 bf16, 1 float32, 2 float32 accumulate, 3 bf16 silu(gate)*up on interleaved rows (C is [M, N/2]).
+// early: launch with programmatic stream serialization (see below).
 int oe_gemm_skinny_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, long long lda, long long ldc,
-                        int out_kind, cudaStream_t st) {
+                        int out_kind, int early, cudaStream_t st) {
     if (!oe_gemm_skinny_supported(A, W, M, N, K, lda)) return OE_ERR_UNSUPPORTED;
     if (out_kind < 0 || out_kind > 3 || (out_kind == 3 && (N & 1))) return OE_ERR_UNSUPPORTED;
     const int blocks = (N + ROWS - 1) / ROWS;
-    // Launched only after the kernel before it has finished (`false`): started early, its many
-    // CTAs took bandwidth and SM slots from the kernel they waited for (measured: slower).
+    // early: the kernel may start (and request its first weights) while the kernel before it
+    // drains.  Measured on B200 in a decode step of the 3B shape (1.838 ms with no product early):
+    // each product alone gains about 1 %, qkv and o together 2.3 %, but o, gate/up and down
+    // together cost 30 % and all four 90 % (runs of early kernels with very many CTAs pile up on
+    // the SMs), so the caller decides.
     // Warps and loads in flight per shape, from a sweep on B200 at 8 tokens: matrices with
     // very many rows do best with small CTAs, long rows with more loads in flight.
 #define OE_SKINNY_LAUNCH(NT, WARPS, UNROLL)                                                                        \
-    return oe_launch_ex(false, gemm_skinny_kernel<NT, WARPS, UNROLL>, dim3(blocks), dim3(WARPS * 32), 0, st, C, A, \
+    return oe_launch_ex(early != 0, gemm_skinny_kernel<NT, WARPS, UNROLL>, dim3(blocks), dim3(WARPS * 32), 0, st, C, A, \
                         W, M, N, K, lda, ldc, out_kind)
     if (M > 8) OE_SKINNY_LAUNCH(2, 8, 3);
     if (blocks >= 4 * 148) OE_SKINNY_LAUNCH(1, 4, 3);

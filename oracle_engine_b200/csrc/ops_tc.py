@@ -81,21 +81,22 @@ def _skinny():
     if lib is None:
         lib = _build.load("gemm_skinny")
         lib.oe_gemm_skinny_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong,
-                                            c_int, c_void_p]
+                                            c_int, c_int, c_void_p]
         lib.oe_gemm_skinny_bf16.restype = c_int
         _state["skinny"] = lib
     return lib
 
 
 def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool = False, split_k: bool = True,
-         swiglu: bool = False, kernel: str = "auto") -> None:
+         swiglu: bool = False, kernel: str = "auto", early: bool = False) -> None:
     """out (+)= a @ w.T, a [M, K] and w [N, K] bfloat16; out bfloat16 or float32 [M, N].
 
     swiglu: w's rows alternate gate and up rows (g0, u0, g1, u1, ...) and out [M, N/2]
     bfloat16 receives silu(gate) * up, computed in float32 in the epilogue.
     kernel: "auto" (weight-streaming kernel up to SKINNY_MAX_TOKENS rows, the two-SM tcgen05
     kernel from PAIR_MIN_TOKENS rows unless it accumulates, the one-SM tcgen05 kernel otherwise),
-    "tcgen05", "pair" or "skinny"."""
+    "tcgen05", "pair" or "skinny".
+    early: the weight-streaming kernel may start while the kernel before it drains."""
     M, K = a.shape
     N = w.shape[0]
     if w.shape[1] != K or out.shape != (M, N // 2 if swiglu else N):
@@ -118,7 +119,7 @@ def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool =
         raise KernelError("gemm: output must be bfloat16 or float32")
     if kernel == "skinny" or (kernel == "auto" and M <= SKINNY_MAX_TOKENS):
         code = _skinny().oe_gemm_skinny_bf16(out.data_ptr(), a.data_ptr(), w.data_ptr(), M, N, K, a.stride(0),
-                                             out.stride(0), kind, torch.cuda.current_stream().cuda_stream)
+                                             out.stride(0), kind, int(early), torch.cuda.current_stream().cuda_stream)
         ops._check(code, "gemm_skinny")
         return
     if kernel == "pair" or (kernel == "auto" and M >= PAIR_MIN_TOKENS and N >= 32 and not accumulate):

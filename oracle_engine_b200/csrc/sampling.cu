@@ -25,7 +25,7 @@ __device__ __forceinline__ float uniform_from_counter(unsigned long long seed, u
 }
 
 // First maximum of a row (strict >, lowest index wins ties; core/ops.cpp:490-497).
-__device__ int block_argmax(const float* __restrict__ x, int V, float* s_val, int* s_idx) {
+__device__ int block_argmax(const float* x, int V, float* s_val, int* s_idx) {
     float best = -INFINITY;
     int bi = 0x7fffffff;
     for (int i = threadIdx.x; i < V; i += blockDim.x) {
@@ -60,7 +60,7 @@ __device__ int block_argmax(const float* __restrict__ x, int V, float* s_val, in
 }
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
-argmax_rows_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
+argmax_rows_kernel(const float* logits, int* out, int V) {
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
     pdl_launch_dependents();
@@ -74,7 +74,7 @@ argmax_rows_kernel(const float* __restrict__ logits, int* __restrict__ out, int 
 constexpr int ARGMAX_SLICES = 32;
 
 __global__ void __launch_bounds__(256)
-argmax_partial_kernel(const float* __restrict__ logits, float* __restrict__ part_val, int* __restrict__ part_idx, int V) {
+argmax_partial_kernel(const float* logits, float* part_val, int* part_idx, int V) {
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
     pdl_launch_dependents();
@@ -111,7 +111,7 @@ argmax_partial_kernel(const float* __restrict__ logits, float* __restrict__ part
     }
 }
 
-__global__ void argmax_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx, int* __restrict__ out) {
+__global__ void argmax_final_kernel(const float* part_val, const int* part_idx, int* out) {
     pdl_launch_dependents();
     pdl_wait();
     const int row = blockIdx.x, lane = threadIdx.x;

@@ -63,10 +63,12 @@ class GQAAttention(Part):
         q_width = self.H * self.hd
         width = q_width + (2 * self.KVH * self.hd if owns_cache else 0)
         qkv = self.rt.empty(T, width)
-        matmul_nt(self.rt, qkv, h, self.w_qkv[:width])
+        # both products of the mixer may start while the kernel before them drains (measured: 2 % of a
+        # decode step; the feed-forward's products must not, see csrc/gemm_skinny.cu)
+        matmul_nt(self.rt, qkv, h, self.w_qkv[:width], early=True)
         cos, sin = self.position.tables() if self.position is not None else (None, None)
         from . import attention_dispatch as ad
         o = self.rt.empty(T, q_width)
         ad.mixer_core(self.rt, o, qkv, cos, sin, cache, ctx, self.H, self.KVH, self.hd, self.window, self.scale,
                       owns_cache)
-        matmul_nt(self.rt, residual, o, self.w_o, accumulate=True)
+        matmul_nt(self.rt, residual, o, self.w_o, accumulate=True, early=True)

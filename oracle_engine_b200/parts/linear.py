@@ -13,10 +13,12 @@ import torch
 from ..csrc import ops
 
 
-def matmul_nt(rt, out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool = False) -> None:
+def matmul_nt(rt, out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool = False,
+              early: bool = False) -> None:
+    """early: the product may start while the kernel before it drains (see csrc/gemm_skinny.cu)."""
     if rt.dtype == torch.bfloat16 and rt.tensor_cores:
         from ..csrc import ops_tc
         if ops_tc.gemm_supported(a, w, out):
-            ops_tc.gemm(out, a, w, accumulate=accumulate)
+            ops_tc.gemm(out, a, w, accumulate=accumulate, early=early)
             return
     ops.gemm_simple(out, a, w, accumulate=accumulate)

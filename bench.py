@@ -38,6 +38,15 @@ LLAMA_3B = dict(architectures=["LlamaForCausalLM"], vocab_size=128256, hidden_si
                               "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
                 max_position_embeddings=131072, tie_word_embeddings=True, bos_token_id=128000,
                 eos_token_id=128001)
+# Further shapes of the same architecture (not the headline): --shape 1b | 8b
+LLAMA_1B = dict(LLAMA_3B, hidden_size=2048, num_hidden_layers=16, num_attention_heads=32, num_key_value_heads=8,
+                head_dim=64, intermediate_size=8192)
+LLAMA_8B = dict(LLAMA_3B, hidden_size=4096, num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8,
+                head_dim=128, intermediate_size=14336, tie_word_embeddings=False,
+                rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                              "high_freq_factor": 4.0, "original_max_position_embeddings": 8192})
+SHAPES = {"3b": ("llama-3.2-3b-shape", LLAMA_3B, 8192), "1b": ("llama-3.2-1b-shape", LLAMA_1B, 4096),
+          "8b": ("llama-3.1-8b-shape", LLAMA_8B, 8192)}
 CONTEXT = 8192
 PROMPT_LEN = 512
 PREFILL_TOKENS = 2048
@@ -58,7 +67,7 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons, sampled every 200 ms while it is open."""
+    """nvidia-smi clocks and throttle reasons, sampled every 50 ms while it is open."""
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
@@ -67,7 +76,7 @@ class ClockSampler:
         self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=self.file, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -225,6 +234,7 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--shape", default="3b", choices=sorted(SHAPES), help="3b is the headline configuration")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -241,7 +251,9 @@ def main():
     from oracle_engine_b200 import LlamaConfig
     from oracle_engine_b200.engine.engine import Engine
 
-    raw = dict(LLAMA_3B)
+    global CONTEXT
+    model_name, shape_cfg, CONTEXT = SHAPES[args.shape]
+    raw = dict(shape_cfg)
     layers_full = raw["num_hidden_layers"]
     if args.layers:
         raw["num_hidden_layers"] = args.layers
@@ -273,18 +285,20 @@ def main():
         * itemsize / 2
     achieved = step_bytes / (dec["ms_per_step"] / 1e3) / 1e9
     line = {
-        "metric": "decode tok/s at batch 8 (Llama 3.2 3B shape, bf16); prefill tok/s at 2,048 tokens; "
-                  "points at batch 1 and 64",
+        "metric": "decode tok/s at batch %d (%s, %s); prefill tok/s at 2,048 tokens; points at batch 1 and 64"
+                  % (args.batch, {"3b": "Llama 3.2 3B shape", "1b": "Llama 3.2 1B shape", "8b": "Llama 3.1 8B shape"}[args.shape],
+                     "bf16" if args.dtype == "bfloat16" else "fp32"),
         "value": round(dec["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(dec["ms_per_step"], 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
         "data": "synthetic token ids, random-init weights N(0, 0.02) from seed 2",
-        "config": {"model": "llama-3.2-3b-shape", "global_batch": args.batch, "seq_len": CONTEXT,
+        "config": {"model": model_name, "global_batch": args.batch, "seq_len": CONTEXT,
                    "parallelism": "single-gpu", "layers": cfg.num_hidden_layers, "layers_full": layers_full,
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "ffn": cfg.intermediate_size, "vocab": cfg.vocab_size,
                    "prompt_len": PROMPT_LEN, "prefill_tokens": PREFILL_TOKENS, "tied_head": cfg.tie_word_embeddings,
-                   "rope": "llama3 factor 32", "l2": "inputs larger than L2 (weights 6.4 GB per step)",
+                   "rope": "llama3 factor %g" % cfg.rope_scaling.factor,
+                   "l2": "inputs larger than L2 (weights %.1f GB per step)" % (nums["weight_bytes"] / 1e9),
                    "peaks": pk["source"]},
         "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tokens/s", "ms_per_step": round(e2e["ms_per_step"], 4),
                 "h2d_bytes_per_step": e2e["h2d_bytes_per_step"], "d2h_bytes_per_step": e2e["d2h_bytes_per_step"]},

@@ -315,6 +315,35 @@ def test_attention_moving_maximum(kernel, hd, step):
     assert ops_tc.device_error() == 0
 
 
+@pytest.mark.parametrize("hd,window", [(128, 0), (64, 1000)])
+def test_attention_long_prompt(hd, window):
+    """A prompt of 36 key blocks through the tensor-memory kernel (every row checked), with and
+    without a window that spans many blocks, and the same sequence continued from a cached prefix."""
+    from types import SimpleNamespace
+    from oracle_engine_b200.csrc import ops_tc
+    H, KVH, n = 2, 1, 2300
+    g = torch.Generator().manual_seed(hd + window)
+    k = torch.randn(n, KVH, hd, generator=g)
+    v = torch.randn(n, KVH, hd, generator=g)
+    q = torch.randn(n, H, hd, generator=g) * 1.5
+    rd = lambda t: t.to(torch.bfloat16).double()                          # noqa: E731
+    want = pl.causal_attention(rd(q), rd(k), rd(v), window or None)
+    cache, tables = _paged([k], [v], [n], torch.bfloat16)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)        # noqa: E731
+    for start in (0, 1111):                                               # whole, and the last tokens over a cached prefix
+        m = n - start
+        qbuf = torch.zeros(m, (H + 2 * KVH) * hd)
+        qbuf[:, :H * hd] = q[start:].reshape(m, -1)
+        qbuf = qbuf.to(torch.bfloat16).to(DEV)
+        out = torch.full((m, H * hd), 7.0, dtype=torch.bfloat16, device=DEV)
+        ctx = SimpleNamespace(cu_q=i32([0, m]), seq_start=i32([start]), seq_qlen=i32([m]), tok_seq=i32([0] * m), n_seqs=1,
+                              max_qlen=m, all_decode=False)
+        ops_tc.attention(out, qbuf, cache, tables, ctx, H, KVH, hd, window, 1 / math.sqrt(hd))
+        err = (out.double().cpu() - want[start:]).abs().max().item()
+        assert err < 2.5e-2, (start, err)
+    assert ops_tc.device_error() == 0
+
+
 def test_rope_kv_write():
     from oracle_engine_b200.csrc import ops
     from oracle_engine_b200.parts.positions import rotary_inv_freq
@@ -412,12 +441,12 @@ def test_attention_decode_fused(H, KVH, hd, window, rotate, kernel):
     from types import SimpleNamespace
     from oracle_engine_b200.csrc import ops_tc
     decode = ops_tc.attention_decode_fused if kernel == "fused" else ops_tc.attention_decode_warps
-    lens = [1, 64, 65, 200, 130, 17, 128, 33, 600]             # length including the new token
+    lens = [1, 64, 65, 200, 130, 17, 128, 33, 600, 2100]       # length including the new token
     B = len(lens)
     g = torch.Generator().manual_seed(hd + H)
     bf = lambda t: t.to(torch.bfloat16)                       # noqa: E731
     inv = pl.rope_inv_freq(hd, 10000.0, None)
-    ang = torch.arange(1024, dtype=torch.float64)[:, None] * inv[None]
+    ang = torch.arange(4096, dtype=torch.float64)[:, None] * inv[None]
     cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
     k_old = [bf(torch.randn(n - 1, KVH, hd, generator=g)) for n in lens]        # already rotated, in the cache
     v_old = [bf(torch.randn(n - 1, KVH, hd, generator=g)) for n in lens]

@@ -65,7 +65,14 @@ def _fn(lib: str, name: str, dtype=None):
     return f
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current CUDA stream's handle.  torch.cuda.current_stream() builds a Python object on
+    every call (about 17 us); the raw query is what a kernel launch per few microseconds needs."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 

@@ -119,19 +119,19 @@ def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool =
         raise KernelError("gemm: output must be bfloat16 or float32")
     if kernel == "skinny" or (kernel == "auto" and M <= SKINNY_MAX_TOKENS):
         code = _skinny().oe_gemm_skinny_bf16(out.data_ptr(), a.data_ptr(), w.data_ptr(), M, N, K, a.stride(0),
-                                             out.stride(0), kind, int(early), torch.cuda.current_stream().cuda_stream)
+                                             out.stride(0), kind, int(early), ops._stream())
         ops._check(code, "gemm_skinny")
         return
     if kernel == "pair" or (kernel == "auto" and M >= PAIR_MIN_TOKENS and N >= 32 and not accumulate):
         code = _pair().oe_gemm_pair_bf16(out.data_ptr(), a.data_ptr(), w.data_ptr(), M, N, K, a.stride(0), out.stride(0),
-                                         kind, PAIR_MAX_TILE[0], torch.cuda.current_stream().cuda_stream)
+                                         kind, PAIR_MAX_TILE[0], ops._stream())
         ops._check(code, "gemm_pair")
         return
     ws, counters, sms = _scratch(a.device)
     code = _lib().oe_gemm_tc_bf16(out.data_ptr(), a.data_ptr(), w.data_ptr(), M, N, K, a.stride(0), out.stride(0), kind,
                                   ws.data_ptr() if split_k else None, ws.numel() * 4,
                                   counters.data_ptr() if split_k else None, counters.numel(), sms,
-                                  torch.cuda.current_stream().cuda_stream)
+                                  ops._stream())
     ops._check(code, "gemm_tc")
 
 
@@ -233,7 +233,7 @@ def attention(out, qkv, cache, tables, ctx, n_heads: int, n_kv_heads: int, head_
         code = _attn_tc5_lib(head_dim).oe_attn_tc_bf16(
             out.data_ptr(), qkv.data_ptr(), qkv.stride(0), cache.data_ptr(), cache.shape[0], tables.data_ptr(),
             tables.shape[1], ctx.cu_q.data_ptr(), ctx.seq_start.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.n_seqs, T,
-            ctx.max_qlen, n_heads, n_kv_heads, int(window), float(scale), torch.cuda.current_stream().cuda_stream)
+            ctx.max_qlen, n_heads, n_kv_heads, int(window), float(scale), ops._stream())
         ops._check(code, "attention_tcgen05")
         return
     lib = _attn_lib(head_dim)
@@ -249,7 +249,7 @@ def attention(out, qkv, cache, tables, ctx, n_heads: int, n_kv_heads: int, head_
                                 ctx.seq_qlen.data_ptr(), ctx.tok_seq.data_ptr(), ctx.n_seqs, T, max(1, ctx.max_qlen),
                                 n_heads, n_kv_heads, int(window), float(scale), n_splits,
                                 None if partial is None else partial.data_ptr(),
-                                torch.cuda.current_stream().cuda_stream)
+                                ops._stream())
     ops._check(code, "attention_mma")
     if n_splits > 1:
         ops.LAUNCHES[0] += 1
@@ -301,7 +301,7 @@ def attention_decode_warps(out, qkv, cos, sin, cache, tables, ctx, n_heads: int,
         out.data_ptr(), qkv.data_ptr(), qkv.stride(0), None if cos is None else cos.data_ptr(),
         None if sin is None else sin.data_ptr(), cache.data_ptr(), int(has_kv), tables.data_ptr(), tables.shape[1],
         ctx.cu_q.data_ptr(), ctx.seq_start.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.n_seqs, n_heads, n_kv_heads,
-        int(window), float(scale), torch.cuda.current_stream().cuda_stream)
+        int(window), float(scale), ops._stream())
     ops._check(code, "attention_decode_warps")
 
 
@@ -343,5 +343,5 @@ def attention_decode_fused(out, qkv, cos, sin, cache, tables, ctx, n_heads: int,
         None if sin is None else sin.data_ptr(), cache.data_ptr(), int(has_kv), tables.data_ptr(), tables.shape[1],
         ctx.cu_q.data_ptr(), ctx.seq_start.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.n_seqs, n_heads, n_kv_heads,
         int(window), float(scale), n_splits, None if partial is None else partial.data_ptr(),
-        _attn_counters(out.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+        _attn_counters(out.device).data_ptr(), ops._stream())
     ops._check(code, "attention_decode_fused")

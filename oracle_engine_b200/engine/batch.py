@@ -154,7 +154,7 @@ class StepBuffers:
             self._host_view(8 + j)[:] = tb.reshape(-1)
         self.dev.copy_(self.host, non_blocking=True)
         if self._copied is not None:
-            self._copied.record()
+            self._copied.record(torch.cuda.current_stream())
             self._pending = True
         return self.context(plan)
 
@@ -168,7 +168,7 @@ class StepBuffers:
         self._host_view(4)[:n] = starts
         self.dev.copy_(self.host, non_blocking=True)
         if self._copied is not None:
-            self._copied.record()
+            self._copied.record(torch.cuda.current_stream())
             self._pending = True
 
     def bytes(self) -> int:

@@ -140,6 +140,8 @@ struct GemmArgs {
     int out_kind;               // 0 bf16 store, 1 float32 store, 2 float32 accumulate, 3 bf16 silu(gate)*up
     int splits;
     int tiles_a, tiles_b;       // output tiles along the A and the B operand
+    int streamk;                // 1: the CTAs share the k-blocks of the first sk_tiles tiles equally (see ItemIter)
+    int sk_tiles;
     float* workspace;           // [splits][tiles_a][tiles_b][n_tile][128] float32 when splits > 1
     int* counters;              // [tiles_a * tiles_b], zero between launches
 };
@@ -231,6 +233,98 @@ __device__ __forceinline__ void emit(const GemmArgs& g, int a_row, int b_row0, c
     }
 }
 
+// The work items of a CTA.
+// Tile mode: output tiles (times K splits), taken round robin by the resident CTAs; A-tiles vary
+// fastest, so CTAs that run together share the B tile in L2.
+// Stream-K mode (many tokens, a tile count that does not fill the last round of CTAs): an
+// instruction of any width up to 256 costs about the same, so a k-block of a 128 x 256 tile is
+// the unit of work.  The k-blocks of the first sk_tiles tiles, in tile order, are cut into
+// gridDim.x equal runs: a CTA's run is the tail of one tile, whole tiles, and the head of
+// another.  The other tiles (a multiple of gridDim.x) follow round robin, whole, so every SM
+// multiplies the same number of k-blocks whatever the shape, and the sums of the shared
+// tiles are added up by the epilogue warps while the whole tiles are multiplied.  The pieces
+// of a shared tile go through the workspace (slot 2 c for CTA c's first item, 2 c + 1 for
+// its last), and the CTA that arrives last on the tile's counter adds them in k order and
+// stores: no CTA waits for another.
+struct Item {
+    int tile_a, tile_b, kb0, n_kb;
+    int n_parts, my_part;       // pieces of this tile and which one this is (1, 0: the whole tile)
+    int split;                  // tile mode: the K split
+    int c_first;                // stream-K: the CTA that has the tile's first k-block
+};
+struct ItemIter {
+    int streamk, tiles_a, tiles_b, splits, n_kb_total, kb_per;
+    int w, step, n_work;                        // tile mode
+    long long u, u0, u1, T;                     // stream-K: this CTA's run of k-block units and the total
+    long long dp, n_tiles;                      // stream-K: the next whole tile of this CTA
+    int G;
+    __device__ long long start_of(int c) const { return T * c / G; }
+    __device__ int cta_of(long long unit) const {
+        int c = (int)(unit * G / T);
+        while (c + 1 < G && start_of(c + 1) <= unit) c++;
+        while (c > 0 && start_of(c) > unit) c--;
+        return c;
+    }
+    __device__ bool next(Item& it) {
+        if (streamk) {
+            if (u >= u1) {
+                if (dp >= n_tiles) return false;
+                it.tile_b = (int)(dp / tiles_a); it.tile_a = (int)(dp % tiles_a);
+                it.kb0 = 0; it.n_kb = n_kb_total; it.split = 0;
+                it.n_parts = 1; it.my_part = 0; it.c_first = (int)blockIdx.x;
+                dp += G;
+                return true;
+            }
+            const long long tile = u / n_kb_total;
+            it.kb0 = (int)(u % n_kb_total);
+            long long n = u1 - u;
+            if (n > n_kb_total - it.kb0) n = n_kb_total - it.kb0;
+            it.n_kb = (int)n;
+            it.tile_b = (int)(tile / tiles_a); it.tile_a = (int)(tile % tiles_a);
+            it.split = 0;
+            if (it.n_kb == n_kb_total) { it.n_parts = 1; it.my_part = 0; it.c_first = (int)blockIdx.x; }
+            else {
+                it.c_first = cta_of(tile * n_kb_total);
+                it.n_parts = cta_of((tile + 1) * n_kb_total - 1) - it.c_first + 1;
+                it.my_part = (int)blockIdx.x - it.c_first;
+            }
+            u += n;
+            return true;
+        }
+        if (w >= n_work) return false;
+        const int rem = w % (tiles_a * tiles_b);
+        it.split = w / (tiles_a * tiles_b); it.tile_b = rem / tiles_a; it.tile_a = rem % tiles_a;
+        it.kb0 = it.split * kb_per;
+        it.n_kb = min(n_kb_total, it.kb0 + kb_per) - it.kb0;
+        it.n_parts = splits; it.my_part = it.split; it.c_first = 0;
+        w += step;
+        return true;
+    }
+};
+__device__ __forceinline__ ItemIter make_iter(const GemmArgs& g) {
+    ItemIter t;
+    t.streamk = g.streamk; t.tiles_a = g.tiles_a; t.tiles_b = g.tiles_b; t.splits = g.splits;
+    t.n_kb_total = (g.K + BLOCK_K - 1) / BLOCK_K;
+    t.kb_per = (t.n_kb_total + g.splits - 1) / g.splits;
+    t.w = blockIdx.x; t.step = gridDim.x; t.n_work = g.tiles_a * g.tiles_b * g.splits;
+    t.G = gridDim.x;
+    t.T = (long long)g.sk_tiles * t.n_kb_total;
+    t.n_tiles = (long long)g.tiles_a * g.tiles_b; t.dp = (long long)g.sk_tiles + blockIdx.x;
+    t.u0 = t.start_of(blockIdx.x); t.u1 = t.start_of(blockIdx.x + 1); t.u = t.u0;
+    return t;
+}
+// Where piece p of the item's tile lies in the workspace (floats), for row 0 and column 0.
+__device__ __forceinline__ size_t part_base(const GemmArgs& g, const ItemIter& t, const Item& it, int p) {
+    const size_t tile_floats = (size_t)g.n_tile * BLOCK_M;
+    if (g.streamk) {
+        const int c = it.c_first + p;
+        const long long tile = (long long)it.tile_b * g.tiles_a + it.tile_a;
+        const int slot = 2 * c + ((t.start_of(c) / t.n_kb_total == tile) ? 0 : 1);
+        return (size_t)slot * tile_floats;
+    }
+    return ((size_t)p * g.tiles_a * g.tiles_b + (size_t)it.tile_a * g.tiles_b + it.tile_b) * tile_floats;
+}
+
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -241,12 +335,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     SharedCtl* ctl = (SharedCtl*)(smem + (size_t)g.stages * stage_bytes);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // Work items (output tile x K split), taken round robin by the resident CTAs.  A-tiles
-    // vary fastest, so CTAs that run together share the B tile in L2.
-    const int tiles_a = g.tiles_a, tiles_b = g.tiles_b;
-    const int n_work = tiles_a * tiles_b * g.splits;
-    const int n_kb_total = (g.K + BLOCK_K - 1) / BLOCK_K;
-    const int kb_per = (n_kb_total + g.splits - 1) / g.splits;
+    const int tiles_b = g.tiles_b;
     uint32_t tmem_cols = 32;
     while ((int)tmem_cols < 2 * g.n_tile) tmem_cols <<= 1;          // two accumulators
 
@@ -276,11 +365,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (lane == 0) {
             int it = 0;                                         // k-blocks issued so far, over all work items
             bool waited = false, ok = true;
-            for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
-                const int split = w / (tiles_a * tiles_b), rem = w % (tiles_a * tiles_b);
-                const int tile_b = rem / tiles_a, tile_a = rem % tiles_a;
-                const int kb0 = split * kb_per;
-                const int n_kb = min(n_kb_total, kb0 + kb_per) - kb0;
+            ItemIter iter = make_iter(g);
+            Item item;
+            while (ok && iter.next(item)) {
+                const int tile_b = item.tile_b, tile_a = item.tile_a, kb0 = item.kb0, n_kb = item.n_kb;
                 int i = 0;
                 if (!waited) {
                     const int first = min(n_kb, g.stages);
@@ -316,10 +404,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t idesc = umma_idesc(BLOCK_M, g.n_tile);
             int it = 0, lt = 0;
             bool ok = true;
-            for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, lt++) {
-                const int split = w / (tiles_a * tiles_b);
-                const int kb0 = split * kb_per;
-                const int n_kb = min(n_kb_total, kb0 + kb_per) - kb0;
+            ItemIter iter = make_iter(g);
+            Item item;
+            for (; ok && iter.next(item); lt++) {
+                const int n_kb = item.n_kb;
                 const int buf = lt & 1;
                 // the epilogue must have read this accumulator (two work items ago)
                 if (!mbar_wait(&ctl->tmem_empty[buf], ((uint32_t)(lt >> 1) & 1u) ^ 1u, ctl, 4)) break;
@@ -348,9 +436,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int row = quarter * 32 + lane;          // row of the A tile
         int lt = 0;
         bool first = true;
-        for (int w = blockIdx.x; w < n_work; w += gridDim.x, lt++) {
-            const int split = w / (tiles_a * tiles_b), rem = w % (tiles_a * tiles_b);
-            const int tile_b = rem / tiles_a, tile_a = rem % tiles_a;
+        ItemIter iter = make_iter(g);
+        Item item;
+        for (; iter.next(item); lt++) {
+            const int tile_b = item.tile_b, tile_a = item.tile_a;
             const int a_row = tile_a * BLOCK_M + row;
             const int buf = lt & 1;
             // every epilogue thread takes the same decision, so that all of them reach the
@@ -361,8 +450,67 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (*(volatile int*)&ctl->epi_ok == 0) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * g.n_tile);
-            const size_t tile_off = (((size_t)tile_a * tiles_b + tile_b) * (size_t)g.n_tile) * BLOCK_M + row;
-            const size_t split_stride = (size_t)tiles_a * tiles_b * g.n_tile * BLOCK_M;
+            const bool shared_tile = item.n_parts > 1;      // several work items add up to this tile
+            const int tile_id = tile_a * tiles_b + tile_b;
+            // A piece lies in the workspace as [column / 4][row][4] floats: a thread's four columns
+            // are one 16-byte access and a warp's accesses are contiguous.
+            bool fast = false;
+            if (shared_tile && g.streamk) {
+                // All the other pieces are there already (the usual case for the piece a CTA ends
+                // its run with): add them to the accumulator without writing it out first.
+                if (warp == 2 && lane == 0) {
+                    int seen;
+                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(g.counters + tile_id) : "memory");
+                    ctl->is_last = (seen == item.n_parts - 1) ? 1 : 0;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                fast = *(volatile int*)&ctl->is_last != 0;
+            }
+            if (fast) {
+                __threadfence();
+                for (int c0 = 0; c0 < g.n_tile; c0 += 32) {
+                    const bool two = c0 + 16 < g.n_tile;
+                    float acc[32];
+                    for (int sp = 0; sp < item.n_parts; sp++) {
+                        float t[32];
+                        if (sp == item.my_part) {
+                            uint32_t r[2][16];
+                            tmem_ld16(taddr + (uint32_t)c0, r[0]);
+                            if (two) tmem_ld16(taddr + (uint32_t)(c0 + 16), r[1]);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int q = 0; q < 2; q++)
+#pragma unroll
+                                for (int j = 0; j < 16; j++) t[16 * q + j] = __uint_as_float(r[q][j]);
+                        } else {
+                            const float4* src = reinterpret_cast<const float4*>(g.workspace + part_base(g, iter, item, sp)) +
+                                                (size_t)(c0 / 4) * BLOCK_M + row;
+#pragma unroll
+                            for (int i = 0; i < 8; i++) {
+                                float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+                                if (i < 4 || two) x = __ldcg(src + (size_t)i * BLOCK_M);
+                                t[4 * i] = x.x; t[4 * i + 1] = x.y; t[4 * i + 2] = x.z; t[4 * i + 3] = x.w;
+                            }
+                        }
+                        if (sp == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j++) acc[j] = t[j];
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++) acc[j] += t[j];
+                        }
+                    }
+#pragma unroll
+                    for (int q = 0; q < 2; q++)
+                        if ((q == 0 || two) && tile_b * g.n_tile + c0 + 16 * q < g.rows_b)
+                            emit<16>(g, a_row, tile_b * g.n_tile + c0 + 16 * q, reinterpret_cast<const float(&)[16]>(acc[16 * q]));
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&ctl->tmem_empty[buf])) : "memory");
+                if (warp == 2 && lane == 0) g.counters[tile_id] = 0;
+                continue;
+            }
             // 32 columns per wait (n_tile is a multiple of 16: the last group may be half)
             for (int c0 = 0; c0 < g.n_tile; c0 += 32) {
                 uint32_t r[2][16];
@@ -377,10 +525,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                     for (int j = 0; j < 16; j++) v[j] = __uint_as_float(r[h][j]);
                     const int c = c0 + 16 * h;
-                    if (g.splits > 1) {
-                        float* part = g.workspace + (size_t)split * split_stride + tile_off + (size_t)c * BLOCK_M;
+                    if (shared_tile) {
+                        float4* part = reinterpret_cast<float4*>(g.workspace + part_base(g, iter, item, item.my_part)) +
+                                       (size_t)(c / 4) * BLOCK_M + row;
 #pragma unroll
-                        for (int j = 0; j < 16; j++) part[(size_t)j * BLOCK_M] = v[j];
+                        for (int j = 0; j < 4; j++)
+                            part[(size_t)j * BLOCK_M] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                     } else {
                         emit<16>(g, a_row, tile_b * g.n_tile + c, v);
                     }
@@ -390,33 +540,54 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&ctl->tmem_empty[buf])) : "memory");
-            if (g.splits > 1) {
-                // the CTA that arrives last adds the partial sums in split order
+            if (shared_tile) {
+                // the CTA that arrives last adds the partial sums in k order
                 __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                const int tile_id = tile_a * tiles_b + tile_b;
                 if (warp == 2 && lane == 0) {
                     const int old = atomicAdd(&g.counters[tile_id], 1);
-                    ctl->is_last = (old == g.splits - 1) ? 1 : 0;
+                    ctl->is_last = (old == item.n_parts - 1) ? 1 : 0;
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (*(volatile int*)&ctl->is_last) {
                     __threadfence();
-                    for (int c0 = 0; c0 < g.n_tile; c0 += 8) {
+                    // the loads of four pieces are in flight together; the sums stay in k order
+                    const float4* src4[4];
+#pragma unroll
+                    for (int q = 0; q < 4; q++)
+                        src4[q] = reinterpret_cast<const float4*>(
+                                      g.workspace + part_base(g, iter, item, q < item.n_parts ? q : 0)) + row;
+                    for (int c0 = 0; c0 < g.n_tile; c0 += 16) {
                         if (tile_b * g.n_tile + c0 >= g.rows_b) break;
-                        float acc[8];
+                        float acc[16];
+                        for (int sp0 = 0; sp0 < item.n_parts; sp0 += 4) {
+                            float4 t[4][4];
 #pragma unroll
-                        for (int u = 0; u < 8; u++) acc[u] = 0.f;
-                        const float* src = g.workspace + tile_off + (size_t)c0 * BLOCK_M;
-#pragma unroll 4
-                        for (int sp = 0; sp < g.splits; sp++) {
-                            float t[8];
+                            for (int q = 0; q < 4; q++) {
+                                if (sp0 + q >= item.n_parts) break;
+                                const float4* src = (sp0 == 0 ? src4[q]
+                                                              : reinterpret_cast<const float4*>(
+                                                                    g.workspace + part_base(g, iter, item, sp0 + q)) + row) +
+                                                    (size_t)(c0 / 4) * BLOCK_M;
 #pragma unroll
-                            for (int u = 0; u < 8; u++) t[u] = __ldcg(src + (size_t)sp * split_stride + (size_t)u * BLOCK_M);
+                                for (int u = 0; u < 4; u++) t[q][u] = __ldcg(src + (size_t)u * BLOCK_M);
+                            }
 #pragma unroll
-                            for (int u = 0; u < 8; u++) acc[u] += t[u];
+                            for (int q = 0; q < 4; q++) {
+                                if (sp0 + q >= item.n_parts) break;
+#pragma unroll
+                                for (int u = 0; u < 4; u++) {
+                                    if (sp0 + q == 0) {
+                                        acc[4 * u] = t[q][u].x; acc[4 * u + 1] = t[q][u].y;
+                                        acc[4 * u + 2] = t[q][u].z; acc[4 * u + 3] = t[q][u].w;
+                                    } else {
+                                        acc[4 * u] += t[q][u].x; acc[4 * u + 1] += t[q][u].y;
+                                        acc[4 * u + 2] += t[q][u].z; acc[4 * u + 3] += t[q][u].w;
+                                    }
+                                }
+                            }
                         }
-                        emit<8>(g, a_row, tile_b * g.n_tile + c0, acc);
+                        emit<16>(g, a_row, tile_b * g.n_tile + c0, acc);
                     }
                     if (warp == 2 && lane == 0) g.counters[tile_id] = 0;
                 }
@@ -444,6 +615,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // host side
 // ---------------------------------------------------------------------------------------
 PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+inline long long kb_ns(int n_tile) { return n_tile <= 128 ? 280 : n_tile <= 192 ? 417 : 482; }   // measured, one k-block
+int g_force_tile = 0;       // measurements only: tile width and schedule for many tokens (0, -1: chosen here)
+int g_force_streamk = -1;
 std::mutex g_mutex;
 
 int get_encode() {
@@ -498,7 +672,7 @@ int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, 
     if (rc) return rc;
     GemmArgs g;
     g.C = C; g.ldc = ldc; g.K = K; g.out_kind = out_kind;
-    g.workspace = workspace; g.counters = counters; g.splits = 1;
+    g.workspace = workspace; g.counters = counters; g.splits = 1; g.streamk = 0; g.sk_tiles = 0;
     CUtensorMap map_a, map_b;
     dim3 grid;
     const int n_kb = (K + BLOCK_K - 1) / BLOCK_K;
@@ -543,24 +717,56 @@ int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, 
         if (N < 256) {
             g.n_tile = ((N + 15) / 16) * 16;
         } else {
-            // tile width that wastes the least in the last wave of CTAs (one CTA per SM)
+            // The tile width with the shortest rounds of CTAs (one CTA per SM).  A k-block takes
+            // about 280, 417 and 482 ns at 128, 192 and 256 columns (measured; a wide instruction
+            // costs little more than a narrow one); over 13 token counts from 256 to 8,192 and this
+            // model's four shapes that choice was within 1% of the best of the three.
             const int tiles_m = (M + BLOCK_M - 1) / BLOCK_M;
             long long best = -1;
             for (int nt = 256; nt >= 128; nt -= 64) {
                 const long long tiles = (long long)tiles_m * ((N + nt - 1) / nt);
-                const long long cost = ((tiles + sm_count - 1) / sm_count) * nt;
+                const long long cost = ((tiles + sm_count - 1) / sm_count) * kb_ns(nt);
                 if (best < 0 || cost < best) { best = cost; g.n_tile = nt; }
             }
+            if (g_force_tile >= 16 && g_force_tile <= 256 && g_force_tile % 16 == 0) g.n_tile = g_force_tile;
         }
         g.rows_a = M; g.rows_b = N;
+        g.tiles_a = (M + BLOCK_M - 1) / BLOCK_M;
+        // Stream-K (see ItemIter) where it saves a tenth or more over whole tiles of the width
+        // chosen above, and the round of whole tiles after the shared part lasts longer than
+        // the adding up of a shared tile's pieces (about 10 us a piece while the other SMs
+        // multiply), which then costs nothing.  (2,048 tokens: 3072 -> 5120 72 -> 68 us,
+        // 8192 -> 3072 117 -> 100 us; 8,192 tokens: 8192 -> 3072 386 -> 353 us; 3072 -> 3072 at
+        // 2,048 tokens stays with whole tiles: its round of whole tiles is too short, 46 -> 65 us.)
+        const int sk = g_force_streamk;
+        const long long tiles256 = (long long)g.tiles_a * ((N + 255) / 256);
+        if (sk != 0 && N >= 256 && workspace && counters && tiles256 <= n_counters &&
+            2LL * sm_count * 256 * BLOCK_M * 4 <= ws_bytes) {
+            const long long tiles_now = (long long)g.tiles_a * ((N + g.n_tile - 1) / g.n_tile);
+            const double whole = (double)((tiles_now + sm_count - 1) / sm_count) * (double)kb_ns(g.n_tile);
+            const double shared_k = (double)tiles256 / (double)sm_count * 482.0;
+            const long long rounds = tiles256 / sm_count, rest = tiles256 % sm_count;
+            if (sk == 1 ? rest > 0 : (rounds >= 1 && rest > 0 && shared_k < 0.9 * whole)) {
+                // the shared part: the remainder, plus one full round if the remainder alone would
+                // cut its tiles into more than four pieces and a round of whole tiles is still left
+                long long shared = rest;
+                if (rounds >= 2 && rest * 4 < sm_count) shared += sm_count;
+                const long long run = shared * n_kb / sm_count;
+                const long long pieces = run > 0 ? (n_kb + run - 1) / run + 1 : 1000;
+                if (sk == 1 ? run >= 1 : (run >= 8 && (double)pieces * 10000.0 <= (double)n_kb * 482.0)) {
+                    g.streamk = 1;
+                    g.sk_tiles = (int)shared;
+                    g.n_tile = 256;
+                }
+            }
+        }
         if ((rc = make_map(&map_a, A, M, K, lda, BLOCK_M))) return rc;
         if ((rc = make_map(&map_b, W, N, K, K, g.n_tile))) return rc;
-        g.tiles_a = (M + BLOCK_M - 1) / BLOCK_M;
         g.tiles_b = (N + g.n_tile - 1) / g.n_tile;
     }
     const long long n_work = (long long)g.tiles_a * g.tiles_b * g.splits;
     if (n_work > 2147483647LL) return OE_ERR_UNSUPPORTED;
-    grid = dim3((unsigned)(n_work < sm_count ? n_work : sm_count));
+    grid = dim3((unsigned)((n_work < sm_count && !g.streamk) ? n_work : sm_count));
     const int b_tile_bytes = g.n_tile * BLOCK_K * 2;
     const int stage_bytes = A_TILE_BYTES + ((b_tile_bytes + 1023) & ~1023);
     int stages = (200 * 1024) / stage_bytes;
@@ -578,6 +784,10 @@ int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, 
     const int launch_rc = oe_launch(gemm_tc_kernel, dim3(grid), dim3(THREADS), smem, st, map_a, map_b, g);
     return launch_rc;
 }
+
+// For measurements: forces the tile width (0: chosen by the shape) and the schedule (1: stream-K
+// wherever a remainder exists, 0: whole tiles, -1: chosen by the shape) of products over many tokens.
+void oe_gemm_tc_force(int n_tile, int streamk) { g_force_tile = n_tile; g_force_streamk = streamk; }
 
 // Reads and clears the device-side error flag (0 = no wait ran out).
 int oe_gemm_tc_error() {

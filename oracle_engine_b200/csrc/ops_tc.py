@@ -87,6 +87,13 @@ def _skinny():
     return lib
 
 
+def force_schedule(n_tile: int = 0, stream_k: int = -1) -> None:
+    """Measurements and tests: the one-SM tcgen05 kernel's tile width for many tokens (0: chosen
+    by the shape) and its schedule (1: stream-K wherever the tiles leave a remainder, 0: whole
+    tiles, -1: chosen by the shape)."""
+    _lib().oe_gemm_tc_force(int(n_tile), int(stream_k))
+
+
 def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool = False, split_k: bool = True,
          swiglu: bool = False, kernel: str = "auto", early: bool = False) -> None:
     """out (+)= a @ w.T, a [M, K] and w [N, K] bfloat16; out bfloat16 or float32 [M, N].

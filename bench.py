@@ -204,7 +204,7 @@ def time_e2e(engine, batch, steps, warmup, vocab):
             "h2d_bytes_per_step": int(backend.h2d_bytes / n_steps), "d2h_bytes_per_step": int(backend.d2h_bytes / n_steps)}
 
 
-def time_prefill(engine, vocab, runs=5, warmup=3):
+def time_prefill(engine, vocab, runs=9, warmup=3):
     import torch
     from oracle_engine_b200 import SequenceStep
     prompt = random_prompts(1, PREFILL_TOKENS, vocab, 3000)[0]

@@ -62,6 +62,29 @@ static inline int oe_launch_ex(bool early, void (*kernel)(KArgs...), dim3 grid, 
     return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// The same with clusters of cluster_x consecutive CTAs along x (the grid's x is a multiple of it).
+template <typename... KArgs, typename... Args>
+static inline int oe_launch_cluster(void (*kernel)(KArgs...), unsigned cluster_x, dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+#ifndef __CUDA_ARCH__
+    attr[0].val.programmaticStreamSerializationAllowed = oe_pdl_enabled();
+#endif
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = cluster_x;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // early = true: the kernel may start before the one before it has finished (see above).
 template <typename... KArgs, typename... Args>
 static inline int oe_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {

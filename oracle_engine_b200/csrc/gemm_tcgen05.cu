@@ -48,6 +48,28 @@ struct SharedCtl {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// The address of this CTA's shared-memory address `a` in the CTA of rank `rank` of the cluster.
+__device__ __forceinline__ uint32_t peer_smem(uint32_t a, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t a) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a) : "memory");
+    return v;
+}
+// Every thread of every CTA of the cluster calls it (threads that have left count as arrived).
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -142,6 +164,7 @@ struct GemmArgs {
     int tiles_a, tiles_b;       // output tiles along the A and the B operand
     int streamk;                // 1: the CTAs share the k-blocks of the first sk_tiles tiles equally (see ItemIter)
     int sk_tiles;
+    int cluster;                // > 1: the K splits of a tile are the CTAs of one cluster, which add up through shared memory
     float* workspace;           // [splits][tiles_a][tiles_b][n_tile][128] float32 when splits > 1
     int* counters;              // [tiles_a * tiles_b], zero between launches
 };
@@ -253,7 +276,7 @@ struct Item {
     int c_first;                // stream-K: the CTA that has the tile's first k-block
 };
 struct ItemIter {
-    int streamk, tiles_a, tiles_b, splits, n_kb_total, kb_per;
+    int streamk, cluster, tiles_a, tiles_b, splits, n_kb_total, kb_per;
     int w, step, n_work;                        // tile mode
     long long u, u0, u1, T;                     // stream-K: this CTA's run of k-block units and the total
     long long dp, n_tiles;                      // stream-K: the next whole tile of this CTA
@@ -292,8 +315,9 @@ struct ItemIter {
             return true;
         }
         if (w >= n_work) return false;
-        const int rem = w % (tiles_a * tiles_b);
-        it.split = w / (tiles_a * tiles_b); it.tile_b = rem / tiles_a; it.tile_a = rem % tiles_a;
+        // in a cluster the splits of a tile are neighbours (the cluster's ranks)
+        const int rem = cluster > 1 ? w / splits : w % (tiles_a * tiles_b);
+        it.split = cluster > 1 ? w % splits : w / (tiles_a * tiles_b); it.tile_b = rem / tiles_a; it.tile_a = rem % tiles_a;
         it.kb0 = it.split * kb_per;
         it.n_kb = min(n_kb_total, it.kb0 + kb_per) - it.kb0;
         it.n_parts = splits; it.my_part = it.split; it.c_first = 0;
@@ -303,7 +327,7 @@ struct ItemIter {
 };
 __device__ __forceinline__ ItemIter make_iter(const GemmArgs& g) {
     ItemIter t;
-    t.streamk = g.streamk; t.tiles_a = g.tiles_a; t.tiles_b = g.tiles_b; t.splits = g.splits;
+    t.streamk = g.streamk; t.cluster = g.cluster; t.tiles_a = g.tiles_a; t.tiles_b = g.tiles_b; t.splits = g.splits;
     t.n_kb_total = (g.K + BLOCK_K - 1) / BLOCK_K;
     t.kb_per = (t.n_kb_total + g.splits - 1) / g.splits;
     t.w = blockIdx.x; t.step = gridDim.x; t.n_work = g.tiles_a * g.tiles_b * g.splits;
@@ -356,6 +380,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *(volatile uint32_t*)&ctl->tmem_base;
 
+    int cl_tile_a = 0, cl_tile_b = 0;             // cluster mode: the tile of this CTA's work item
     pdl_launch_dependents();
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -450,6 +475,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (*(volatile int*)&ctl->epi_ok == 0) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * g.n_tile);
+            if (g.cluster > 1) {
+                // This CTA's sums go to its own shared memory (the ring is free: every MMA that read
+                // it has completed) as [column / 4][row][4]; the cluster adds them up below.
+                float4* dump = reinterpret_cast<float4*>(smem);
+                for (int c0 = 0; c0 < g.n_tile; c0 += 16) {
+                    uint32_t r[16];
+                    tmem_ld16(taddr + (uint32_t)c0, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+                        dump[(size_t)(c0 / 4 + j) * BLOCK_M + row] =
+                            make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                        __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                cl_tile_a = tile_a; cl_tile_b = tile_b;
+                break;                                      // one work item per CTA in this mode
+            }
             const bool shared_tile = item.n_parts > 1;      // several work items add up to this tile
             const int tile_id = tile_a * tiles_b + tile_b;
             // A piece lies in the workspace as [column / 4][row][4] floats: a thread's four columns
@@ -598,6 +641,54 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 
     __syncthreads();
+    if (g.cluster > 1) {
+        // The K splits of the tile are this cluster's CTAs, in rank order.  Each CTA adds up its
+        // share of the rows from all the CTAs' shared memory, always in rank order, and stores:
+        // no scratch in global memory, no counter, and every SM of the cluster adds.
+        cluster_sync();
+        if (warp >= 2 && *(volatile int*)&ctl->abort_flag == 0 && *(volatile int*)&ctl->epi_ok) {
+            const int S = g.cluster, rank = (int)cluster_rank();
+            // even shares of rows: a gate row and its up row stay with neighbouring lanes (emit)
+            const int r0 = rank * (BLOCK_M / 2) / S * 2, nrows = (rank + 1) * (BLOCK_M / 2) / S * 2 - r0;
+            const int groups = g.n_tile / 16;
+            const int t = (int)threadIdx.x - 64;
+            const uint32_t base = smem_u32(smem);
+            uint32_t peer[8];
+#pragma unroll
+            for (int q = 0; q < 8; q++) peer[q] = peer_smem(base, (uint32_t)(q < S ? q : 0));
+            for (int u0 = t - lane; u0 < nrows * groups; u0 += 128) {       // whole warps call emit
+                const int u = u0 + lane;
+                const bool mine = u < nrows * groups;
+                const int row = mine ? r0 + u % nrows : 0, grp = mine ? u / nrows : 0;
+                const uint32_t off = (uint32_t)(((grp * 4) * BLOCK_M + row) * 16);
+                float acc[16];
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    float4 v[4][4];
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        if (4 * h + q >= S) break;
+#pragma unroll
+                        for (int j = 0; j < 4; j++) v[q][j] = ld_cluster_f4(peer[4 * h + q] + off + (uint32_t)(j * BLOCK_M * 16));
+                    }
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        if (4 * h + q >= S) break;
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            if (4 * h + q == 0) {
+                                acc[4 * j] = v[q][j].x; acc[4 * j + 1] = v[q][j].y; acc[4 * j + 2] = v[q][j].z; acc[4 * j + 3] = v[q][j].w;
+                            } else {
+                                acc[4 * j] += v[q][j].x; acc[4 * j + 1] += v[q][j].y; acc[4 * j + 2] += v[q][j].z; acc[4 * j + 3] += v[q][j].w;
+                            }
+                        }
+                    }
+                }
+                emit<16>(g, mine ? cl_tile_a * BLOCK_M + row : 0x3fffffff, cl_tile_b * g.n_tile + grp * 16, acc);
+            }
+        }
+        cluster_sync();                               // nobody leaves while its shared memory is read
+    }
     if (*(volatile int*)&ctl->abort_flag) {
         // a wait ran out: give copies and MMAs in flight a fixed time to land before the
         // shared and tensor memory of this CTA are released
@@ -618,6 +709,9 @@ PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
 inline long long kb_ns(int n_tile) { return n_tile <= 128 ? 280 : n_tile <= 192 ? 417 : 482; }   // measured, one k-block
 int g_force_tile = 0;       // measurements only: tile width and schedule for many tokens (0, -1: chosen here)
 int g_force_streamk = -1;
+int g_force_narrow = -1;      // 48..128 tokens: 1 narrow tiles, 0 swap-AB with split K, -1 by the shape
+int g_force_cluster = -1;     // 0: K splits add up through the workspace even where a cluster could
+int g_max_clusters[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};   // clusters of that many CTAs that fit on the GPU at once
 std::mutex g_mutex;
 
 int get_encode() {
@@ -641,6 +735,25 @@ int make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, lon
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+}
+
+// Clusters of cs CTAs of the kernel that the GPU holds at once (one CTA per SM); < 0: -error.
+int max_clusters(int cs) {
+    if (cs < 1 || cs > 8) return 0;
+    if (g_max_clusters[cs] >= 0) return g_max_clusters[cs];
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return -(int)e;
+    cudaLaunchConfig_t probe = {};
+    probe.gridDim = dim3((unsigned)cs); probe.blockDim = dim3(THREADS); probe.dynamicSmemBytes = 227 * 1024;
+    cudaLaunchAttribute pa[1];
+    pa[0].id = cudaLaunchAttributeClusterDimension;
+    pa[0].val.clusterDim.x = (unsigned)cs; pa[0].val.clusterDim.y = 1; pa[0].val.clusterDim.z = 1;
+    probe.attrs = pa; probe.numAttrs = 1;
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel, &probe);
+    if (e != cudaSuccess) { cudaGetLastError(); n = 0; }
+    g_max_clusters[cs] = n;
+    return n;
 }
 
 }  // namespace
@@ -672,15 +785,18 @@ int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, 
     if (rc) return rc;
     GemmArgs g;
     g.C = C; g.ldc = ldc; g.K = K; g.out_kind = out_kind;
-    g.workspace = workspace; g.counters = counters; g.splits = 1; g.streamk = 0; g.sk_tiles = 0;
+    g.workspace = workspace; g.counters = counters; g.splits = 1; g.streamk = 0; g.sk_tiles = 0; g.cluster = 1;
     CUtensorMap map_a, map_b;
     dim3 grid;
     const int n_kb = (K + BLOCK_K - 1) / BLOCK_K;
-    // 48..128 tokens with a short K: no split over K.  The activations stay the 128-row
-    // operand (rows beyond M are not fetched) and a narrow weight tile per CTA gives about one
-    // CTA per SM; measured faster than swap + split-K there (e.g. 96 tokens, 3072x3072: 21 vs
-    // 28 us), slower for long K (128 tokens, 3072x8192: 50 vs 39 us) or fewer tokens.
-    const bool narrow = M <= 128 && M >= 48 && K <= 4096;
+    // 48..128 tokens, a short K and so many weight rows that swap-AB could not split K (fewer than
+    // two CTAs per 128 rows): the activations stay the 128-row operand (rows beyond M are not
+    // fetched) and a narrow weight tile per CTA gives about one CTA per SM, no split.  Measured at
+    // 64 tokens: 16384x3072 27.7 us against 31.4 with swap-AB; with a split the swapped form wins
+    // (5120x3072 22 -> 16 us, 3072x3072 21 -> 14 us) since its splits add up inside a cluster.
+    const bool can_split = sm_count / ((N + BLOCK_M - 1) / BLOCK_M) >= 2 && workspace != nullptr;
+    const bool narrow = g_force_narrow >= 0 ? (g_force_narrow == 1 && M <= 128)
+                                            : (M <= 128 && M >= 48 && K <= 4096 && !can_split);
     if (narrow) {
         g.swap = 0;
         int nt = ((N + sm_count - 1) / sm_count + 15) / 16 * 16;
@@ -709,6 +825,20 @@ int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, 
             splits = (n_kb + kb_per - 1) / kb_per;          // no split without work
         }
         g.splits = splits;
+        // The splits of a tile as one cluster: the largest number of splits, at most 8 (the
+        // portable cluster size), with which all clusters run at once (a cluster lies within one
+        // GPC, so fewer clusters of 6 fit than 148 / 6).
+        if (splits >= 2 && g_force_cluster != 0) {
+            for (int cs = splits < 8 ? splits : 8; cs >= 2; cs--) {
+                const int fit = max_clusters(cs);
+                if (fit < 0) return -fit;
+                if (fit < tiles_a) continue;
+                const int kb_per = (n_kb + cs - 1) / cs;
+                g.splits = (n_kb + kb_per - 1) / kb_per;
+                g.cluster = g.splits;
+                break;
+            }
+        }
         if ((rc = make_map(&map_a, W, N, K, K, BLOCK_M))) return rc;
         if ((rc = make_map(&map_b, A, M, K, lda, g.n_tile))) return rc;
         g.tiles_a = tiles_a; g.tiles_b = 1;
@@ -781,13 +911,22 @@ int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, 
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
+    if (g.cluster > 1)
+        return oe_launch_cluster(gemm_tc_kernel, (unsigned)g.cluster, dim3(grid), dim3(THREADS), smem, st, map_a, map_b, g);
     const int launch_rc = oe_launch(gemm_tc_kernel, dim3(grid), dim3(THREADS), smem, st, map_a, map_b, g);
     return launch_rc;
 }
 
 // For measurements: forces the tile width (0: chosen by the shape) and the schedule (1: stream-K
-// wherever a remainder exists, 0: whole tiles, -1: chosen by the shape) of products over many tokens.
-void oe_gemm_tc_force(int n_tile, int streamk) { g_force_tile = n_tile; g_force_streamk = streamk; }
+// wherever a remainder exists, 0: whole tiles, -1: chosen by the shape) of products over many tokens,
+// (cluster = 0) K splits of few tokens through the workspace instead of a cluster, and (narrow = 1 / 0)
+// up to 128 tokens narrow tiles without a split or swap-AB with split K.
+void oe_gemm_tc_force(int n_tile, int streamk, int cluster, int narrow) {
+    g_force_tile = n_tile; g_force_streamk = streamk; g_force_cluster = cluster; g_force_narrow = narrow;
+}
+
+// Diagnostics: how many clusters of cs CTAs of the kernel run at once.
+int oe_gemm_tc_max_clusters(int cs) { return max_clusters(cs); }
 
 // Reads and clears the device-side error flag (0 = no wait ran out).
 int oe_gemm_tc_error() {

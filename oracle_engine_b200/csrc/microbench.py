@@ -79,7 +79,7 @@ def run_gemm(a):
     swiglu, acc = a.out == "swiglu", a.out == "accumulate"
     dtype = torch.float32 if a.out in ("float32", "accumulate") else torch.bfloat16
     out = torch.zeros(M, N // 2 if swiglu else N, device=dev, dtype=dtype)
-    ops_tc.force_schedule(a.tile, a.stream_k)
+    ops_tc.force_schedule(a.tile, a.stream_k, a.cluster, a.narrow)
     ops_tc.gemm(out, x, ws[0], accumulate=acc, swiglu=swiglu, kernel=a.kernel)
     ref = x[:64].double() @ ws[0].double().T
     if swiglu:
@@ -158,6 +158,10 @@ def main(argv=None):
     g.add_argument("--out", default="bfloat16", choices=["bfloat16", "float32", "accumulate", "swiglu"])
     g.add_argument("--kernel", default="auto", choices=["auto", "tcgen05", "pair", "skinny"])
     g.add_argument("--tile", type=int, default=0, help="one-SM tcgen05 kernel, many tokens: this tile width (0: by the shape)")
+    g.add_argument("--cluster", type=int, default=-1, choices=[-1, 0],
+                   help="one-SM tcgen05 kernel, few tokens: 0 adds the K splits up through the workspace, never in a cluster")
+    g.add_argument("--narrow", type=int, default=-1, choices=[-1, 0, 1],
+                   help="one-SM tcgen05 kernel, up to 128 tokens: 1 narrow tiles without a split, 0 swap-AB with split K")
     g.add_argument("--stream-k", type=int, default=-1, choices=[-1, 0, 1],
                    help="one-SM tcgen05 kernel, many tokens: 1 stream-K wherever a remainder exists, 0 whole tiles, -1 by the shape")
     at = sub.add_parser("attention")

@@ -87,11 +87,13 @@ def _skinny():
     return lib
 
 
-def force_schedule(n_tile: int = 0, stream_k: int = -1) -> None:
+def force_schedule(n_tile: int = 0, stream_k: int = -1, cluster: int = -1, narrow: int = -1) -> None:
     """Measurements and tests: the one-SM tcgen05 kernel's tile width for many tokens (0: chosen
-    by the shape) and its schedule (1: stream-K wherever the tiles leave a remainder, 0: whole
-    tiles, -1: chosen by the shape)."""
-    _lib().oe_gemm_tc_force(int(n_tile), int(stream_k))
+    by the shape), its schedule (1: stream-K wherever the tiles leave a remainder, 0: whole
+    tiles, -1: chosen by the shape); for up to 128 tokens whether the K splits of a tile may be
+    the CTAs of a cluster (0: never, they add up through the workspace) and whether narrow
+    tiles without a split (1) or swap-AB with split K (0) are used (-1: by the shape)."""
+    _lib().oe_gemm_tc_force(int(n_tile), int(stream_k), int(cluster), int(narrow))
 
 
 def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool = False, split_k: bool = True,

@@ -229,6 +229,42 @@ def test_gemm_stream_k(M, N, K):
         ops_tc.force_schedule(0, -1)
 
 
+@pytest.mark.parametrize("M,N,K", [(64, 3072, 3072), (17, 640, 1024), (100, 520, 4096), (128, 264, 8192), (33, 1000, 328)])
+@pytest.mark.parametrize("cluster", [-1, 0])
+def test_gemm_few_tokens_split_k(M, N, K, cluster):
+    """Up to 128 tokens, swap-AB with K split: the splits of a tile add up inside a cluster
+    (2 to 8 CTAs, shares of rows that are not equal, a last weight tile that is partly empty)
+    or through the workspace; all epilogues; the same bits every time."""
+    from oracle_engine_b200.csrc import ops_tc
+    ops_tc.force_schedule(0, -1, cluster, 0)
+    try:
+        a, w = _rand(M, K, dtype=torch.bfloat16, scale=0.5, seed=1), _rand(N, K, dtype=torch.bfloat16, scale=0.5, seed=2)
+        want = a.double() @ w.double().T
+        tol = 2e-6 * K + 1e-5
+        out32 = torch.full((M, N), 9.0, device=DEV)
+        ops_tc.gemm(out32, a, w, kernel="tcgen05")
+        assert (out32.double() - want).abs().max() < tol
+        for _ in range(3):
+            again = torch.empty(M, N, device=DEV)
+            ops_tc.gemm(again, a, w, kernel="tcgen05")
+            assert torch.equal(again, out32)
+        out16 = torch.full((M, N), 9.0, dtype=torch.bfloat16, device=DEV)
+        ops_tc.gemm(out16, a, w, kernel="tcgen05")
+        assert (out16.double() - want).abs().max() < 0.005 * want.abs().max() + tol
+        base = _rand(M, N, seed=3)
+        acc = base.clone()
+        ops_tc.gemm(acc, a, w, accumulate=True, kernel="tcgen05")
+        assert (acc.double() - (base.double() + want)).abs().max() < tol
+        act = torch.full((M, N // 2), 9.0, dtype=torch.bfloat16, device=DEV)
+        ops_tc.gemm(act, a, w, swiglu=True, kernel="tcgen05")
+        gate, up = want[:, 0::2], want[:, 1::2]
+        ref = gate / (1 + torch.exp(-gate)) * up
+        assert (act.double() - ref).abs().max() < 0.005 * ref.abs().max() + 10 * tol
+        assert ops_tc.device_error() == 0
+    finally:
+        ops_tc.force_schedule()
+
+
 def _paged(k, v, lens, dtype, extra_pages=3, seed=0):
     """Dense per-sequence K/V [len, KVH, hd] -> one cache entry [pages, 2, KVH, 64, hd] with
     shuffled pages, and the page tables."""

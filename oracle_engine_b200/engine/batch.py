@@ -163,7 +163,8 @@ class StepBuffers:
         token ids, positions and starts change.  Rewrites those and copies the buffer."""
         if self._pending:
             self._copied.synchronize()
-        self._host_view(0)[:n] = tokens
+        if tokens is not None:                # else the caller writes them on the device
+            self._host_view(0)[:n] = tokens
         self._host_view(2)[:n] = starts
         self._host_view(4)[:n] = starts
         self.dev.copy_(self.host, non_blocking=True)

@@ -57,6 +57,7 @@ class Engine:
         self.sampler = Sampler(self.state, self.device)
         self.stepper = Stepper(self.model, self.cache, self.state, self.rt, use_graphs)
         self._row_slot = torch.empty(self.cache.n_slots, dtype=torch.int32, device=self.device)
+        self._ahead = None        # token buffers of the generation loop's step ahead (device, pinned host, event) x 2
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -87,9 +88,9 @@ class Engine:
     def free(self, slot: int) -> None:
         self.cache.free_slot(slot)
 
-    def step(self, seqs: list[SequenceStep]):
+    def step(self, seqs: list[SequenceStep], device_tokens=None):
         """Float32 logits [wanted, vocab] on the device, or None; see Stepper.step."""
-        return self.stepper.step(seqs)
+        return self.stepper.step(seqs, device_tokens)
 
     def check_device_errors(self) -> None:
         err = self.model.embedding.err
@@ -104,11 +105,15 @@ class Engine:
 
     # ------------------------------------------------------------------ generation
     def generate(self, prompts, params: GenParams | None = None, batch_size: int | None = None,
-                 on_token=None, return_results: bool = False):
+                 on_token=None, return_results: bool = False, lookahead: bool = True):
         """prompts: lists of token ids.  Returns the new tokens of each request (or
-        GenerationResult objects with the finish reason)."""
+        GenerationResult objects with the finish reason).  lookahead: the next step is queued
+        before the host has read the last tokens (same tokens either way; `on_token` then hears
+        of a token while the step after it is already running)."""
         params = params or GenParams()
-        results = run_generation(_Backend(self), prompts, params, batch_size, self.spec.stop_ids, on_token)
+        backend = _Backend(self)
+        backend.supports_lookahead = bool(lookahead)
+        results = run_generation(backend, prompts, params, batch_size, self.spec.stop_ids, on_token)
         return results if return_results else [r.tokens for r in results]
 
 
@@ -121,6 +126,7 @@ class _Backend:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self._last_slots = None
+        self._turn = 0
 
     def alloc(self, request_index, prompt, params):
         slot = self.e.alloc()
@@ -135,15 +141,47 @@ class _Backend:
         self.h2d_bytes += self.e.stepper.last_h2d_bytes
         return logits
 
-    def sample(self, logits, slots, params):
+    def _row_slots(self, slots, params):
         e = self.e
-        rows = len(slots)
-        row_slot = e._row_slot[:rows]
+        row_slot = e._row_slot[:len(slots)]
         if params.temperature > 0.0 or params.repeat_penalty > 1.0:      # greedy needs no per-sequence state
             if slots != self._last_slots:
                 row_slot.copy_(torch.tensor(slots, dtype=torch.int32))
                 self._last_slots = list(slots)
-                self.h2d_bytes += rows * 4
-        out = e.sampler.sample(logits[:rows], row_slot, params)
+                self.h2d_bytes += len(slots) * 4
+        return row_slot
+
+    def sample(self, logits, slots, params):
+        rows = len(slots)
+        out = self.e.sampler.sample(logits[:rows], self._row_slots(slots, params), params)
         self.d2h_bytes += rows * 4
         return out.tolist()
+
+    # ---- one step ahead of the host (see run_generation)
+    supports_lookahead = True
+
+    def sample_async(self, logits, slots, params):
+        """Samples on the device and starts the copy of the tokens to pinned host memory;
+        returns (tokens on the device, pinned host tensor, event after the copy)."""
+        rows = len(slots)
+        e = self.e
+        self._turn = (self._turn + 1) % 2                          # the host may still read the other pair
+        if e._ahead is None:
+            n = e._row_slot.numel()
+            e._ahead = [(torch.empty(n, dtype=torch.int32, device=e.device),
+                         torch.empty(n, dtype=torch.int32, pin_memory=True), torch.cuda.Event()) for _ in range(2)]
+        dev, host, event = e._ahead[self._turn]
+        self.e.sampler.sample(logits[:rows], self._row_slots(slots, params), params, out=dev[:rows])
+        host[:rows].copy_(dev[:rows], non_blocking=True)
+        event.record(torch.cuda.current_stream())
+        self.d2h_bytes += rows * 4
+        return dev[:rows], host[:rows], event
+
+    def read(self, handle):
+        handle[2].synchronize()
+        return handle[1].tolist()
+
+    def step_ahead(self, slots, handle):
+        logits = self.e.step([SequenceStep(s, [0], [0]) for s in slots], device_tokens=handle[0])
+        self.h2d_bytes += self.e.stepper.last_h2d_bytes
+        return logits

@@ -96,25 +96,31 @@ class Stepper:
                                 f"{self.model.spec.max_positions} positions the model was built for")
 
     # ------------------------------------------------------------------ the step
-    def step(self, seqs: list[SequenceStep]) -> torch.Tensor | None:
+    def step(self, seqs: list[SequenceStep], device_tokens: torch.Tensor | None = None) -> torch.Tensor | None:
         """Returns float32 logits [wanted, vocab] on the device (order: sequences, then
         each sequence's `want`), or None if nothing is wanted.  The tensor may be reused
-        by the next step."""
+        by the next step.
+
+        device_tokens (int32 on the device, one per sequence; only for steps of one token
+        each): the tokens are taken from there instead of from `seqs`, whose token values
+        are placeholders; the host need not have seen them yet."""
         self._validate(seqs)
+        if device_tokens is not None and not all(len(s.tokens) == 1 for s in seqs):
+            raise StepError("tokens on the device can only feed a step of one token per sequence")
         starts = [self.cache.length(s.slot) for s in seqs]
         tables_changed = False
         for s, st in zip(seqs, starts):
             tables_changed |= self.cache.reserve(s.slot, st + len(s.tokens))
         decode = all(len(s.tokens) == 1 for s in seqs)
         if decode and self.use_graphs:
-            logits = self._step_graph(seqs, starts, tables_changed)
+            logits = self._step_graph(seqs, starts, tables_changed, device_tokens)
         else:
-            logits = self._step_eager(seqs, starts)
+            logits = self._step_eager(seqs, starts, device_tokens)
         for s, st in zip(seqs, starts):
             self.cache.commit(s.slot, st + len(s.tokens))
         return logits
 
-    def _step_eager(self, seqs, starts):
+    def _step_eager(self, seqs, starts, device_tokens=None):
         plan = build_plan(seqs, starts)
         key = (plan.n_tokens, plan.n_seqs, plan.want_rows.size)
         buf = self._eager_buffers.get(key)
@@ -126,10 +132,12 @@ class Stepper:
             self._eager_buffers[key] = buf
         tables = [self.cache.tables_for(g.index, plan.seq_slot) for g in self.cache.groups]
         ctx = buf.upload(plan, tables)
+        if device_tokens is not None:
+            ctx.token_ids[:len(seqs)].copy_(device_tokens[:len(seqs)])
         self.last_h2d_bytes = buf.bytes()
         return self.model.forward(ctx, self._cache_views(ctx), self._state_views)
 
-    def _step_graph(self, seqs, starts, tables_changed=True):
+    def _step_graph(self, seqs, starts, tables_changed=True, device_tokens=None):
         B = len(seqs)
         bucket = _bucket(B)
         # one graph per padded batch size and context class: kernels chosen by the class stay right
@@ -141,13 +149,15 @@ class Stepper:
         key = tuple(s.slot for s in seqs)
         if key == g.key and g.version == self.cache.version:
             # the same sequences one token further: only tokens and positions change
-            g.buffers.update_decode([s.tokens[0] for s in seqs], starts, B)
+            g.buffers.update_decode(None if device_tokens is not None else [s.tokens[0] for s in seqs], starts, B)
             ctx = g.ctx
         else:
             plan = build_plan(seqs, starts, pad_seqs=bucket, pad_tokens=bucket, want_all_rows=True)
             tables = [self.cache.tables_for(gr.index, plan.seq_slot) for gr in self.cache.groups]
             ctx = g.buffers.upload(plan, tables)
             g.key, g.ctx, g.version = key, ctx, self.cache.version
+        if device_tokens is not None:         # after the copy of the step's tables, before the kernels
+            ctx.token_ids[:B].copy_(device_tokens[:B])
         self.last_h2d_bytes = g.buffers.bytes()
         g.runs += 1
         if g.graph is None and g.runs == 1:

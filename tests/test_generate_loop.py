@@ -42,6 +42,70 @@ class Scripted:
         return out
 
 
+class ScriptedAhead(Scripted):
+    """The same backend with the step ahead: a handle is the list of tokens not yet read."""
+    supports_lookahead = True
+
+    def sample_async(self, logits, slots, params):
+        return {"tokens": self.sample(logits, slots, params), "read": False}
+
+    def read(self, handle):
+        handle["read"] = True
+        return handle["tokens"]
+
+    def step_ahead(self, slots, handle):
+        assert not handle["read"], "a step ahead is queued before its tokens are read"
+        self.steps.append([(self.owner[s], ["ahead"] + [t], [0]) for s, t in zip(slots, handle["tokens"])])
+        return [self.owner[s] for s in slots]
+
+    def sample(self, logits, slots, params):
+        assert [self.owner[s] for s in slots] == logits
+        out = []
+        for i in logits:
+            sc = self.scripts[i]
+            out.append(sc[self.pos[i]] if self.pos[i] < len(sc) else 1000 + self.pos[i])    # beyond a stop: anything
+            self.pos[i] += 1
+        return out
+
+
+def test_step_ahead_gives_the_same_results():
+    scripts = {0: [5, 6, 99], 1: [7, 99], 2: [8, 9, 10, 11, 12, 13, 14], 3: [99], 4: [3, 4, 5, 6, 7, 8]}
+    prompts = [[1, 2, 3], [4], [1, 1, 1, 1, 1], [2, 2], [9]]
+    for n_predict, bs, ctx in [(n, b, c) for n in (1, 2, 4, 6) for b in (1, 2, 3, 5) for c in (64, 7)]:
+        plain = run_generation(Scripted(scripts, n_slots=5, max_seq_len=ctx), prompts, GenParams.greedy(n_predict),
+                               batch_size=bs, stop_ids=(99,))
+        be = ScriptedAhead(scripts, n_slots=5, max_seq_len=ctx)
+        seen = []
+        ahead = run_generation(be, prompts, GenParams.greedy(n_predict), batch_size=bs, stop_ids=(99,),
+                               on_token=lambda i, t: seen.append((i, t)))
+        assert [r.tokens for r in ahead] == [r.tokens for r in plain]
+        assert [r.finish_reason for r in ahead] == [r.finish_reason for r in plain]
+        assert sorted(seen) == sorted((i, t) for i, r in enumerate(plain) for t in r.tokens)
+        assert sorted(be.free_slots) == list(range(5))
+        # no step holds more tokens of a sequence than its slot takes
+        fed = {}
+        for st in be.steps:
+            for (i, toks, _) in st:
+                fed[i] = fed.get(i, 0) + (1 if toks[0] == "ahead" else len(toks))
+                assert fed[i] <= ctx
+    assert any(r.finish_reason == "context" for r in plain)
+
+
+def test_step_ahead_decisions():
+    be = ScriptedAhead({0: [5, 6, 7, 8, 9, 10], 1: [7, 8, 99]})
+    res = run_generation(be, [[1, 2], [3]], GenParams.greedy(6), batch_size=2, stop_ids=(99,))
+    assert [r.tokens for r in res] == [[5, 6, 7, 8, 9, 10], [7, 8]]
+    assert be.steps == [
+        [(0, [1, 2], [1]), (1, [3], [0])],                    # the prompts
+        [(0, ["ahead", 5], [0]), (1, ["ahead", 7], [0])],     # queued before 5 and 7 were read
+        [(0, ["ahead", 6], [0]), (1, ["ahead", 8], [0])],
+        [(0, ["ahead", 7], [0]), (1, ["ahead", 99], [0])],    # ran with the sequence that had stopped: its row is dropped
+        [(0, [8], [0])],                                      # the survivor alone, its token from the host again
+        [(0, ["ahead", 9], [0])],
+        # the sixth token ends request 0 by its count: no step is queued for it
+    ]
+
+
 def test_unequal_prompts_stops_and_batches():
     scripts = {0: [5, 6, 99], 1: [7, 99], 2: [8, 9, 10, 11, 12], 3: [99]}
     be = Scripted(scripts)

@@ -122,6 +122,20 @@ def test_stop_tokens_batches_and_slot_reuse(model_dirs, plain_models):
     assert any(len(w) < 20 for w in want) and any(len(w) == 20 for w in want)
     eng.cache.check()
     assert eng.cache.slots.n_free == 3
+    # without the step ahead of the host: the same tokens, and in both ways with sampling
+    # (a step that ran with a sequence that had just stopped changes nothing for the others)
+    res = eng.generate(prompts, GenParams.greedy(20, stop_ids=tuple(stop)), batch_size=3, return_results=True,
+                       lookahead=False)
+    assert [r.tokens for r in res] == want
+    sampled = GenParams(n_predict=20, temperature=0.9, top_k=12, top_p=0.8, repeat_penalty=1.3, repeat_last_n=8,
+                        seed=5, stop_ids=tuple(stop))
+    heard = []
+    one = eng.generate(prompts, sampled, batch_size=3, on_token=lambda i, t: heard.append((i, t)))
+    two = eng.generate(prompts, sampled, batch_size=3, lookahead=False)
+    assert one == two and any(len(o) < 20 for o in one)
+    assert sorted(heard) == sorted((i, t) for i, o in enumerate(one) for t in o)
+    eng.cache.check()
+    assert eng.cache.slots.n_free == 3
     # the model's own eos ids stop a sequence unless told otherwise
     eos = plain.cfg["eos_token_id"]
     forced = [t for t in range(256) if t != eos][:3]

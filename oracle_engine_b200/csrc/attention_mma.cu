@@ -723,6 +723,17 @@ extern "C" {
 
 int oe_attn_mma_head_dim() { return HD; }
 
+// How many CTAs of the one-warp decode kernel with a double buffer (the form that splits the keys)
+// an SM holds; <= 0 on error.
+int oe_attn_mma_decode_ctas_per_sm() {
+    const size_t smem = (size_t)2 * 2 * TILE_BYTES;
+    if (cudaFuncSetAttribute(attn_mma_kernel<1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)(2 * 2 * TILE_BYTES + 2 * 64 * 32 * sizeof(float))) != cudaSuccess) return 0;
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn_mma_kernel<1, 2>, 32, smem) != cudaSuccess) return 0;
+    return n;
+}
+
 // Floats of scratch the split path needs for a step of n_tokens rows.
 long long oe_attn_mma_partial_floats(int n_tokens, int H, int n_splits) {
     return (long long)n_tokens * H * n_splits * (HD + 2);

@@ -23,6 +23,7 @@ from types import SimpleNamespace
 
 import torch
 
+from ..engine.batch import context_class
 from . import ops, ops_tc
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
@@ -93,6 +94,7 @@ def run_gemm(a):
 
 
 def run_attention(a):
+    ops_tc.DECODE_SPLITS[0] = a.splits
     dev = torch.device("cuda:0")
     H, KVH, hd, B = a.heads, a.kv_heads, a.head_dim, a.batch
     qlen = a.prompt if a.prompt else 1
@@ -108,7 +110,8 @@ def run_attention(a):
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)          # noqa: E731
     ctx = SimpleNamespace(cu_q=i32([b * qlen for b in range(B + 1)]), seq_start=i32([ctx_len - qlen] * B),
                           seq_qlen=i32([qlen] * B), tok_seq=i32([b for b in range(B) for _ in range(qlen)]),
-                          n_seqs=B, n_tokens=T, max_qlen=qlen, all_decode=(qlen == 1))
+                          n_seqs=B, n_tokens=T, max_qlen=qlen, all_decode=(qlen == 1),
+                          context_class=context_class(ctx_len))
     scale = 1 / math.sqrt(hd)
     if a.decode != "split" and not a.prompt:
         # the one-launch decode kernels: rotation, cache write, attention and merge together
@@ -171,6 +174,7 @@ def main(argv=None):
     at.add_argument("--heads", type=int, default=24)
     at.add_argument("--kv-heads", type=int, default=8)
     at.add_argument("--head-dim", type=int, default=128)
+    at.add_argument("--splits", type=int, default=0, help="split kernel: CTAs per (sequence, KV head) (0: the rule's)")
     at.add_argument("--decode", default="split", choices=["split", "warps", "fused"],
                     help="decode kernel: keys split over CTAs plus a merge (after a separate rotation kernel, not timed "
                          "here), over the warps of one CTA, or the one-warp fused kernel")

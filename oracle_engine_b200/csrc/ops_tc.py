@@ -210,17 +210,50 @@ def _attn_tc5_lib(head_dim: int):
     return lib
 
 
-def decode_splits(n_seqs: int, n_kv_heads: int, sm_count: int, max_pages: int) -> int:
-    """How many CTAs share one (sequence, KV head) of a decode step: enough to occupy the
-    GPU about twice, never more than the pages a sequence can have.  Depends on the batch
-    size and the cache geometry only, so a captured graph stays valid."""
+DECODE_SPLITS = [0]          # measurements: this many CTAs per (sequence, KV head) instead of the rule's
+
+
+def decode_splits(n_seqs: int, n_kv_heads: int, sm_count: int, max_pages: int, context_class: int = 0,
+                  ctas_per_sm: int = 3) -> int:
+    """How many CTAs share one (sequence, KV head) of a decode step, never more than the pages a
+    sequence can have.  Depends on the batch size, the step's context class and the cache
+    geometry only, so a captured graph stays valid.
+    Short contexts: enough CTAs to occupy the GPU about twice.  Long contexts, where the time is
+    the keys' bytes: the fewest splits that fill the last round of resident CTAs (ctas_per_sm x SMs)
+    to 85 %, else the best-filled; measured at 8,000 keys (us): 8 sequences 5 / 6 splits 57 / 50,
+    32 sequences 2 / 3 splits 246 / 175, 40 sequences 1 / 4 splits 362 / 206."""
+    if DECODE_SPLITS[0] > 0:
+        return max(1, min(max_pages, 32, DECODE_SPLITS[0]))
     ctas = max(1, n_seqs * n_kv_heads)
-    return max(1, min(max_pages, 32, (2 * sm_count + ctas - 1) // ctas))
+    cap = max(1, min(max_pages, 32))
+    if context_class <= 0:
+        return max(1, min(cap, (2 * sm_count + ctas - 1) // ctas))
+    resident = max(1, ctas_per_sm) * sm_count
+    best, best_fill = 1, 0.0
+    for s in range(1, cap + 1):
+        rounds = (ctas * s + resident - 1) // resident
+        fill = ctas * s / (rounds * resident)
+        if fill >= 0.85:
+            return s
+        if fill > best_fill + 1e-9:
+            best, best_fill = s, fill
+    return best
 
 
-def decode_splits_for(n_seqs: int, n_kv_heads: int, tables) -> int:
+def decode_splits_for(n_seqs: int, n_kv_heads: int, tables, context_class: int = 0, head_dim: int = 0) -> int:
     sms = torch.cuda.get_device_properties(tables.device).multi_processor_count
-    return decode_splits(n_seqs, n_kv_heads, sms, tables.shape[1])
+    per_sm = _decode_ctas_per_sm(head_dim) if head_dim and context_class > 0 else 3
+    return decode_splits(n_seqs, n_kv_heads, sms, tables.shape[1], context_class, per_sm)
+
+
+def _decode_ctas_per_sm(head_dim: int) -> int:
+    key = ("decode_ctas_per_sm", head_dim)
+    if key not in _state:
+        n = int(_attn_lib(head_dim).oe_attn_mma_decode_ctas_per_sm())
+        if n <= 0:
+            raise KernelError("attention: the decode kernel does not fit an SM")
+        _state[key] = n
+    return _state[key]
 
 
 def attention(out, qkv, cache, tables, ctx, n_heads: int, n_kv_heads: int, head_dim: int, window: int,
@@ -248,8 +281,7 @@ def attention(out, qkv, cache, tables, ctx, n_heads: int, n_kv_heads: int, head_
     lib = _attn_lib(head_dim)
     n_splits, partial = 1, None
     if ctx.all_decode and group <= 16:
-        sms = torch.cuda.get_device_properties(out.device).multi_processor_count
-        n_splits = decode_splits(ctx.n_seqs, n_kv_heads, sms, tables.shape[1])
+        n_splits = decode_splits_for(ctx.n_seqs, n_kv_heads, tables, getattr(ctx, "context_class", 0), head_dim)
         if n_splits > 1:
             partial = torch.empty(lib.oe_attn_mma_partial_floats(T, n_heads, n_splits), dtype=torch.float32,
                                   device=out.device)
@@ -269,28 +301,45 @@ def decode_fused_supported(head_dim: int, n_heads: int, n_kv_heads: int) -> bool
 
 
 DECODE_KERNEL = ["auto"]     # "auto", "warps", "split" (tests pin a kernel)
-DECODE_WARPS_FULL_CTAS = 48  # (sequence, KV head) pairs from which long contexts stay on the warps kernel too
-DECODE_WARPS_MAX_CTAS = 300  # more pairs than this: the one-warp kernel, several CTAs an SM
+DECODE_WARPS_FULL_CTAS = 48  # (sequence, KV head) pairs from which contexts of class 1 stay on the warps kernel too
+DECODE_WARPS_LONG_CTAS = 96  # ... and contexts of class 2
+DECODE_WARPS_MAX_CTAS = 300  # short contexts with more pairs than this: the one-warp kernel, several CTAs an SM
+DECODE_WARPS_MIN_FILL = 0.75 # long contexts, more pairs than SMs: the share of the last round of CTAs that must be full
 
 
 def decode_warps_supported(head_dim: int, n_heads: int, n_kv_heads: int) -> bool:
     return decode_fused_supported(head_dim, n_heads, n_kv_heads) and n_heads // n_kv_heads <= 16
 
 
-def decode_uses_warps(n_seqs: int, long_context: bool, head_dim: int, n_heads: int, n_kv_heads: int) -> bool:
+def decode_uses_warps(n_seqs: int, context_class: int, head_dim: int, n_heads: int, n_kv_heads: int) -> bool:
     """Whether a decode step goes to the kernel whose warps split the keys (one launch, no
-    scratch) rather than to CTAs that split the keys plus a merge.  Short contexts: always (a
-    warp walks a few half pages).  Long contexts: when the (sequence, KV head) pairs alone give
-    enough CTAs; with few sequences more CTAs per sequence win.  Depends on the batch size and
-    the step's context class only; a captured graph is kept per class."""
+    scratch) rather than to CTAs that split the keys plus a merge, or to the one-warp kernel.
+    Depends on the batch size and the step's context class (engine/batch.py) only; a captured
+    graph is kept per class.  Measured (us, 24 heads over 8 KV heads of 128; warps / split / one-warp):
+    class 0 (640 keys): 8 sequences 10.6 / 10.8+rotation / 28, 64 sequences 43 / 38+rotation / 40;
+    class 1 (2,048): 1 sequence 20 / 12 / 28, 8: 21 / 22 / 43, 64: 93 / 105 / 108;
+    class 2 (8,000): 1: 63 / 18 / 33, 8: 66 / 56 / 109, 16: 90 / 90, 24: 150 / 130, 32: 159 / 246,
+    64: 316 / 390 / 391."""
     if DECODE_KERNEL[0] == "split" or not decode_warps_supported(head_dim, n_heads, n_kv_heads):
         return False
     if DECODE_KERNEL[0] == "warps":
         return True
     pairs = n_seqs * n_kv_heads
-    if pairs > DECODE_WARPS_MAX_CTAS:
-        return False                      # every SM has several one-warp CTAs of the fused kernel: measured faster
-    return not long_context or pairs >= DECODE_WARPS_FULL_CTAS
+    if context_class <= 0:
+        return pairs <= DECODE_WARPS_MAX_CTAS     # beyond: every SM has several one-warp CTAs, measured faster
+    sms = _sm_count()
+    if pairs <= sms:                              # with few sequences more CTAs per sequence win
+        return pairs >= (DECODE_WARPS_FULL_CTAS if context_class == 1 else DECODE_WARPS_LONG_CTAS)
+    # One CTA of this kernel fills an SM's shared memory, and one SM streams about 40 GB/s: a last
+    # round with few CTAs is a slow tail (192 pairs at 8,000 keys: 150 us against 130 split; 256: 159 / 246).
+    rounds = (pairs + sms - 1) // sms
+    return pairs >= DECODE_WARPS_MIN_FILL * rounds * sms
+
+
+def _sm_count() -> int:
+    if "sms" not in _state:
+        _state["sms"] = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    return _state["sms"]
 
 
 def attention_decode_warps(out, qkv, cos, sin, cache, tables, ctx, n_heads: int, n_kv_heads: int, head_dim: int,

@@ -87,7 +87,13 @@ def build_plan(seqs: list, starts: list, pad_seqs: int = 0, pad_tokens: int = 0,
 
 # Steps are classed by the longest sequence they touch: kernels may be chosen by the class, and a
 # captured decode graph is kept per class, so the choice stays valid as sequences grow.
-LONG_CONTEXT_TOKENS = 1536
+CONTEXT_CLASS_TOKENS = [1536, 4096]      # class 0 up to the first, 1 up to the second, 2 beyond
+
+
+def context_class(n_tokens: int) -> int:
+    """The class of a step by its longest sequence; kernels may be chosen by it, and a decode
+    graph is kept per class."""
+    return sum(1 for t in CONTEXT_CLASS_TOKENS if n_tokens > t)
 
 
 @dataclass
@@ -108,7 +114,7 @@ class StepContext:
     max_qlen: int
     max_kvlen: int
     all_decode: bool
-    long_context: bool = False      # some sequence is longer than LONG_CONTEXT_TOKENS (kernels may choose by it)
+    context_class: int = 0          # context_class() of the longest sequence (kernels may choose by it)
 
 
 class StepBuffers:
@@ -182,4 +188,4 @@ class StepBuffers:
             n_tokens=self.n_tokens, n_seqs=self.n_seqs, n_want=self.n_want, token_ids=v[0], tok_seq=v[1],
             tok_pos=v[2], seq_slot=v[3], seq_start=v[4], seq_qlen=v[5], cu_q=v[6], want_rows=v[7], tables=tabs,
             max_qlen=plan.max_qlen, max_kvlen=plan.max_kvlen, all_decode=plan.all_decode,
-            long_context=plan.max_kvlen > LONG_CONTEXT_TOKENS)
+            context_class=context_class(plan.max_kvlen))

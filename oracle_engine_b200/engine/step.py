@@ -21,7 +21,7 @@ import torch
 
 from ..cache.kv_cache import CacheView
 from ..csrc import ops
-from .batch import LONG_CONTEXT_TOKENS, SequenceStep, StepBuffers, build_plan
+from .batch import SequenceStep, StepBuffers, build_plan, context_class
 
 _BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 
@@ -141,7 +141,7 @@ class Stepper:
         B = len(seqs)
         bucket = _bucket(B)
         # one graph per padded batch size and context class: kernels chosen by the class stay right
-        gkey = (bucket, max(starts) + 1 > LONG_CONTEXT_TOKENS)
+        gkey = (bucket, context_class(max(starts) + 1))
         g = self._graphs.get(gkey)
         if g is None:
             g = _DecodeGraph(bucket, StepBuffers(bucket, bucket, bucket, self._table_shapes(bucket), self.rt.device))

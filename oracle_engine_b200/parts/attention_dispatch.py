@@ -18,13 +18,13 @@ def mixer_core(rt, out, qkv, cos, sin, cache, ctx, H, KVH, hd, window, scale, ow
         from ..csrc import ops_tc
         # One CTA per (sequence, KV head) whose warps split the keys: one launch for rotation, cache
         # write, attention and the merge, no scratch in global memory.
-        if ops_tc.decode_uses_warps(ctx.n_seqs, getattr(ctx, "long_context", False), hd, H, KVH):
+        if ops_tc.decode_uses_warps(ctx.n_seqs, getattr(ctx, "context_class", 0), hd, H, KVH):
             ops_tc.attention_decode_warps(out, qkv, cos, sin, cache.storage, cache.tables, ctx, H, KVH, hd, window,
                                           scale, owns_cache)
             return
         # One kernel when the batch alone fills the GPU (no split over the keys); for small
         # batches the split kernels plus a parallel merge are faster (measured).
-        if ops_tc.decode_fused_supported(hd, H, KVH) and ops_tc.decode_splits_for(ctx.n_seqs, KVH, cache.tables) == 1:
+        if ops_tc.decode_fused_supported(hd, H, KVH) and ops_tc.decode_splits_for(ctx.n_seqs, KVH, cache.tables, getattr(ctx, "context_class", 0), hd) == 1:
             ops_tc.attention_decode_fused(out, qkv, cos, sin, cache.storage, cache.tables, ctx, H, KVH, hd, window,
                                           scale, owns_cache)
             return

@@ -159,18 +159,17 @@ def test_long_decoding_from_the_first_token(model_dirs, plain_models, tmp_path, 
         want = plain.logits(toks).numpy()
         err = np.abs(got[i] - want).max(axis=1)
         assert err.max() < TOL[dtype], f"request {i}: first bad position {int((err >= TOL[dtype]).argmax())}"
-    assert eng.stepper.use_graphs and eng.stepper._graphs[(2, False)].graph is not None
+    assert eng.stepper.use_graphs and eng.stepper._graphs[(2, 0)].graph is not None
     eng.cache.check()
 
 
 def test_decoding_across_the_context_classes(model_dirs, plain_models, tmp_path, monkeypatch):
     """Decode graphs are kept per context class (kernels may be chosen by it): sequences that grow
-    across the boundary while they decode, with the boundary moved down to 96 tokens so that the
-    tiny model crosses it; both decode attention kernels run in one generation."""
+    across the boundaries while they decode, with the boundaries moved down to 96 and 170 tokens so
+    that the tiny model crosses them; both decode attention kernels run in one generation."""
     from oracle_engine_b200.engine import batch, step
     from oracle_engine_b200.engine.engine import Engine
-    monkeypatch.setattr(batch, "LONG_CONTEXT_TOKENS", 96)
-    monkeypatch.setattr(step, "LONG_CONTEXT_TOKENS", 96)
+    monkeypatch.setattr(batch, "CONTEXT_CLASS_TOKENS", [96, 170])
     plain = plain_models["E"]
     eng = Engine.from_pretrained(model_dirs["E"], dtype="bfloat16", max_tokens=704)
     requests = [helpers.random_tokens(n, plain.cfg["vocab_size"], 90 + i) for i, n in enumerate((200, 140))]
@@ -182,7 +181,8 @@ def test_decoding_across_the_context_classes(model_dirs, plain_models, tmp_path,
         err = np.abs(got[i] - want).max(axis=1)
         assert err.max() < TOL["bfloat16"], f"request {i}: first bad position {int((err >= TOL['bfloat16']).argmax())}"
     graphs = eng.stepper._graphs
-    assert graphs[(2, False)].graph is not None and graphs[(2, True)].graph is not None
+    for key in ((2, 0), (2, 1), (1, 1), (1, 2)):
+        assert graphs[key].graph is not None, key
     eng.cache.check()
 
 

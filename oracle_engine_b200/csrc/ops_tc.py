@@ -311,7 +311,8 @@ def decode_warps_supported(head_dim: int, n_heads: int, n_kv_heads: int) -> bool
     return decode_fused_supported(head_dim, n_heads, n_kv_heads) and n_heads // n_kv_heads <= 16
 
 
-def decode_uses_warps(n_seqs: int, context_class: int, head_dim: int, n_heads: int, n_kv_heads: int) -> bool:
+def decode_uses_warps(n_seqs: int, context_class: int, head_dim: int, n_heads: int, n_kv_heads: int,
+                      sm_count: int | None = None) -> bool:
     """Whether a decode step goes to the kernel whose warps split the keys (one launch, no
     scratch) rather than to CTAs that split the keys plus a merge, or to the one-warp kernel.
     Depends on the batch size and the step's context class (engine/batch.py) only; a captured
@@ -327,7 +328,7 @@ def decode_uses_warps(n_seqs: int, context_class: int, head_dim: int, n_heads: i
     pairs = n_seqs * n_kv_heads
     if context_class <= 0:
         return pairs <= DECODE_WARPS_MAX_CTAS     # beyond: every SM has several one-warp CTAs, measured faster
-    sms = _sm_count()
+    sms = sm_count or _sm_count()
     if pairs <= sms:                              # with few sequences more CTAs per sequence win
         return pairs >= (DECODE_WARPS_FULL_CTAS if context_class == 1 else DECODE_WARPS_LONG_CTAS)
     # One CTA of this kernel fills an SM's shared memory, and one SM streams about 40 GB/s: a last

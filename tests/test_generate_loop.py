@@ -164,3 +164,22 @@ def test_reference_defaults():
     p = GenParams()
     assert (p.n_predict, p.temperature, p.top_p, p.top_k, p.repeat_penalty, p.repeat_last_n) == \
         (256, 0.7, 0.9, 40, 1.15, 64)
+
+
+def test_decode_kernel_rules_depend_on_sizes_only():
+    """Which decode attention kernel runs and how many CTAs share a sequence's keys are functions
+    of the batch size, the context class and the geometry (a captured graph stays valid), and
+    the context classes cut where they say."""
+    from oracle_engine_b200.csrc import ops_tc
+    from oracle_engine_b200.engine import batch
+    assert [batch.context_class(n) for n in (1, 1536, 1537, 4096, 4097, 100000)] == [0, 0, 1, 1, 2, 2]
+    uses = lambda n_seqs, cls: ops_tc.decode_uses_warps(n_seqs, cls, 128, 24, 8, sm_count=148)
+    assert [uses(b, 0) for b in (1, 8, 37, 38, 64)] == [True, True, True, False, False]      # 300 pairs at most
+    assert [uses(b, 1) for b in (1, 5, 6, 18, 19, 24, 28, 32, 64)] == \
+        [False, False, True, True, False, False, True, True, True]     # 48..148 pairs, then rounds three quarters full
+    assert [uses(b, 2) for b in (8, 11, 12, 18, 24, 32, 40, 64)] == [False, False, True, True, False, True, False, True]
+    assert not ops_tc.decode_uses_warps(8, 0, 128, 64, 2, sm_count=148)                      # 32 heads per KV head
+    splits = lambda n_seqs, cls, pages=128: ops_tc.decode_splits(n_seqs, 8, 148, pages, cls, 3)
+    assert [splits(b, 0) for b in (1, 8, 24, 64)] == [32, 5, 2, 1]                            # about two CTAs an SM
+    assert [splits(b, 2) for b in (1, 8, 24, 32, 40, 64)] == [32, 6, 2, 3, 4, 3]              # the last round filled
+    assert splits(8, 2, pages=4) == 4 and splits(1, 0, pages=3) == 3                          # never more than the pages

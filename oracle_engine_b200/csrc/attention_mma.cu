@@ -97,7 +97,11 @@ __global__ void __launch_bounds__(NWARPS * 32, NWARPS == 4 ? 2 : 1)
 attn_mma_kernel(const AttnArgs a) {
     extern __shared__ __align__(16) uint8_t smem[];
     pdl_launch_dependents();
-    pdl_wait();
+    // The kernel before this one (or, for a layer that reads another layer's cache, an earlier
+    // one) wrote this step's keys and values into the cache, unless this kernel writes them
+    // itself; see below.
+    const bool own_kv = a.fused && a.cache_w != nullptr;
+    if (!own_kv) pdl_wait();
     const int b = blockIdx.z, kvh = blockIdx.y;
     const int qlen = a.seq_qlen[b];
     if (qlen <= 0) return;
@@ -119,6 +123,15 @@ attn_mma_kernel(const AttnArgs a) {
         j_hi = min(j_hi, j_lo + per - 1);
     }
     const int* trow = a.tables + (size_t)b * a.max_pages;
+    const int n_blocks = j_hi - j_lo + 1;
+    if (own_kv) {
+        // The first tile holds keys and values of earlier steps (and the stale row of the new
+        // token, replaced below): its load overlaps the end of the kernel before this one, from
+        // which only the new token's q, k and v come.
+        if (n_blocks > 0) load_page<NWARPS * 32>(smem, smem + TILE_BYTES, a.cache, trow[j_lo], kvh, a.KVH);
+        cp_async_commit();
+        pdl_wait();
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, tig = lane & 3;
     const int row0 = warp * 16 + gid;                   // this thread's rows: row0 and row0 + 8
@@ -176,11 +189,10 @@ attn_mma_kernel(const AttnArgs a) {
     for (int n = 0; n < HD / 8; n++) { oacc[n][0] = oacc[n][1] = oacc[n][2] = oacc[n][3] = 0.f; }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
-    const int n_blocks = j_hi - j_lo + 1;
-    if (n_blocks > 0) {
-        load_page<NWARPS * 32>(smem, smem + TILE_BYTES, a.cache, trow[j_lo], kvh, a.KVH);
+    if (!own_kv) {
+        if (n_blocks > 0) load_page<NWARPS * 32>(smem, smem + TILE_BYTES, a.cache, trow[j_lo], kvh, a.KVH);
+        cp_async_commit();
     }
-    cp_async_commit();
     for (int it = 0; it < n_blocks; it++) {
         const int j = j_lo + it;
         constexpr bool dbl = STAGES > 1;
@@ -428,7 +440,10 @@ __global__ void __launch_bounds__(NW * 32, 1)
 attn_decode_warps_kernel(const AttnArgs a) {
     extern __shared__ __align__(16) uint8_t smem[];
     pdl_launch_dependents();
-    pdl_wait();
+    // A layer that reads another layer's cache finds the new token's key there, written by an
+    // earlier kernel of this step: it waits first.  Otherwise this kernel writes that key itself.
+    const bool own_kv = a.cache_w != nullptr;
+    if (!own_kv) pdl_wait();
     const int b = blockIdx.z, kvh = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, tig = lane & 3;
@@ -449,6 +464,10 @@ attn_decode_warps_kernel(const AttnArgs a) {
         load_half_page(mine, mine + TB_BYTES, a.cache, trow[hp >> 1], hp & 1, kvh, a.KVH, lane);
     }
     cp_async_commit();
+    // Up to here only the step's tables and keys and values of earlier steps were read, which no
+    // kernel of this step writes (the stale row of the new token is replaced below): those loads
+    // overlap the end of the kernel before this one.  The new token's q, k and v come from that kernel.
+    if (own_kv) pdl_wait();
 
     bool valid[2];
     int head[2];

@@ -8,7 +8,9 @@ Prints ONE JSON line.  `value` is decoded tokens per second at the given batch (
 steps; every sequence has a 512-token random prompt and a slot in a cache sized for a
 context of 8,192 tokens per sequence.  `e2e` is the same through the Python entry point
 `Engine.generate` (host token ids in, host token ids out, every step's inputs copied from
-pinned host memory and its tokens read back).  `prefill` is one 2,048-token prompt,
+pinned host memory and its tokens read back into pinned host memory; the loop queues step
+k + 1 while the host still waits for step k's tokens, as `generate` always does, and the time is
+taken between the arrivals of a sequence's tokens on the host).  `prefill` is one 2,048-token prompt,
 `points` are decode at batch 1 and 64, `roofline` compares the bytes a decode step has to
 read (every weight once, the cache of the live requests) with the measured HBM bandwidth.
 

@@ -40,10 +40,10 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
 template <int NT, int WARPS, int UNROLL>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_skinny_kernel(void* C, const bf16* A, const bf16* __restrict__ W,
-                   int M, int N, int K, long long lda, long long ldc, int out_kind) {
+                   int M, int N, int K, long long lda, long long ldc, int out_kind, int late_trigger) {
     __shared__ float red[WARPS][ROWS][8 * NT + 1];
     __shared__ float total[ROWS][8 * NT + 1];
-    pdl_launch_dependents();
+    if (!late_trigger) pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int row0 = blockIdx.x * ROWS;
@@ -92,6 +92,9 @@ gemm_skinny_kernel(void* C, const bf16* A, const bf16* __restrict__ W,
         }
     }
     if (!waited) pdl_wait();
+    // late_trigger: the kernel after this one may be scheduled only now, when this CTA has streamed
+    // its weights, so that its CTAs do not sit on the SMs while this kernel still needs them
+    if (late_trigger) pdl_launch_dependents();
 
     // add the warps' partial tiles in warp order
 #pragma unroll
@@ -137,22 +140,25 @@ int oe_gemm_skinny_supported(const void* A, const void* W, int M, int N, int K, 
 }
 
 // out_kind: 0 bf16, 1 float32, 2 float32 accumulate, 3 bf16 silu(gate)*up on interleaved rows (C is [M, N/2]).
-// early: launch with programmatic stream serialization (see below).
+// early: bit 0 start early, bit 1 trigger late (see below).
 int oe_gemm_skinny_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, long long lda, long long ldc,
                         int out_kind, int early, cudaStream_t st) {
     if (!oe_gemm_skinny_supported(A, W, M, N, K, lda)) return OE_ERR_UNSUPPORTED;
     if (out_kind < 0 || out_kind > 3 || (out_kind == 3 && (N & 1))) return OE_ERR_UNSUPPORTED;
     const int blocks = (N + ROWS - 1) / ROWS;
-    // early: the kernel may start (and request its first weights) while the kernel before it
-    // drains.  Measured on B200 in a decode step of the 3B shape (1.838 ms with no product early):
-    // each product alone gains about 1 %, qkv and o together 2.3 %, but o, gate/up and down
-    // together cost 30 % and all four 90 % (runs of early kernels with very many CTAs pile up on
-    // the SMs), so the caller decides.
+    // early bit 0: the kernel may start (and request its first weights) while the kernel before it
+    // drains.  early bit 1: this kernel releases the kernel after it only when its CTAs have
+    // streamed their weights (else at its top).  Measured on B200 in a decode step of the 3B
+    // shape, 8 sequences (1.768 ms with qkv and o starting early, every trigger at the top):
+    // gate/up or down starting early behind kernels that trigger at their top cost 20-50 %
+    // (their very many CTAs sit on the SMs while the kernel before still needs them); with o,
+    // gate/up and down starting early AND triggering late, qkv starting early and triggering at
+    // its top (the attention kernel asks for its keys meanwhile): 1.736 ms.  The caller decides.
     // Warps and loads in flight per shape, from a sweep on B200 at 8 tokens: matrices with
     // very many rows do best with small CTAs, long rows with more loads in flight.
 #define OE_SKINNY_LAUNCH(NT, WARPS, UNROLL)                                                                        \
-    return oe_launch_ex(early != 0, gemm_skinny_kernel<NT, WARPS, UNROLL>, dim3(blocks), dim3(WARPS * 32), 0, st, C, A, \
-                        W, M, N, K, lda, ldc, out_kind)
+    return oe_launch_ex((early & 1) != 0, gemm_skinny_kernel<NT, WARPS, UNROLL>, dim3(blocks), dim3(WARPS * 32), 0, st, C, A, \
+                        W, M, N, K, lda, ldc, out_kind, (early >> 1) & 1)
     if (M > 8) OE_SKINNY_LAUNCH(2, 8, 3);
     if (blocks >= 4 * 148) OE_SKINNY_LAUNCH(1, 4, 3);
     if (K > 4096) OE_SKINNY_LAUNCH(1, 8, 3);

@@ -97,7 +97,7 @@ def force_schedule(n_tile: int = 0, stream_k: int = -1, cluster: int = -1, narro
 
 
 def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool = False, split_k: bool = True,
-         swiglu: bool = False, kernel: str = "auto", early: bool = False) -> None:
+         swiglu: bool = False, kernel: str = "auto", early: int = 0) -> None:
     """out (+)= a @ w.T, a [M, K] and w [N, K] bfloat16; out bfloat16 or float32 [M, N].
 
     swiglu: w's rows alternate gate and up rows (g0, u0, g1, u1, ...) and out [M, N/2]
@@ -105,7 +105,8 @@ def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool =
     kernel: "auto" (weight-streaming kernel up to SKINNY_MAX_TOKENS rows, the two-SM tcgen05
     kernel from PAIR_MIN_TOKENS rows unless it accumulates, the one-SM tcgen05 kernel otherwise),
     "tcgen05", "pair" or "skinny".
-    early: the weight-streaming kernel may start while the kernel before it drains."""
+    early (weight-streaming kernel only): bit 0, it may start while the kernel before it drains;
+    bit 1, the kernel after it is released only when its CTAs have streamed their weights."""
     M, K = a.shape
     N = w.shape[0]
     if w.shape[1] != K or out.shape != (M, N // 2 if swiglu else N):

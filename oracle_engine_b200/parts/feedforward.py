@@ -6,7 +6,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
-from .linear import matmul_nt
+from .linear import START_EARLY, TRIGGER_LATE, matmul_nt
 from .registry import FEED_FORWARDS, Part
 from .spec import TensorDecl
 
@@ -46,9 +46,9 @@ class SwiGLU(Part):
         a = self.rt.empty(T, self.FF)
         if self.fused:
             from ..csrc import ops_tc
-            ops_tc.gemm(a, h, self.w_gu, swiglu=True)
+            ops_tc.gemm(a, h, self.w_gu, swiglu=True, early=START_EARLY | TRIGGER_LATE)
         else:
             gu = self.rt.empty(T, 2 * self.FF)
             matmul_nt(self.rt, gu, h, self.w_gu)
             ops.swiglu(a, gu)
-        matmul_nt(self.rt, residual, a, self.w_down, accumulate=True)
+        matmul_nt(self.rt, residual, a, self.w_down, accumulate=True, early=START_EARLY | TRIGGER_LATE)

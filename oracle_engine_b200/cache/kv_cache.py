@@ -1,10 +1,11 @@
 """The paged key/value cache: a slot per sequence, pages of PAGE tokens, one group of
 storage per kind of need.
 
-Every schedule entry whose mixer keeps keys and values gets a cache of its own.  Entries
-with the same `CacheNeed` (kind, KV heads, head size, window) form a group; a group owns
-its storage [entries, pages, 2 (K,V), kv_heads, PAGE, head_dim], its page pool and, for
-each slot, one page table shared by the group's entries (they all hold the same
+Every schedule entry whose mixer keeps something per token gets a cache of its own.
+Entries with the same `CacheNeed` (kind, per-token tensors, window) form a group; a group
+owns its storage (per declared tensor [entries, pages, *outer, PAGE, inner]; for attention
+the one tensor "kv" [entries, pages, 2 (K,V), kv_heads, PAGE, head_dim]), its page pool
+and, for each slot, one page table shared by the group's entries (they all hold the same
 positions).  A "full" group keeps every position of a sequence; a "window" group gives a
 page back as soon as all of its positions lie before the window of the next query, so its
 pool can be smaller.  Slots and pages return to their pools when a sequence ends and are
@@ -27,11 +28,25 @@ from .slots import CacheFull, PagePool, SlotAllocator
 
 @dataclass
 class CacheView:
-    """What a mixer sees of its entry: the entry's storage and its group's page tables
-    for the sequences of the current step ([B, max_pages] int32 on the device)."""
-    storage: torch.Tensor | None
+    """What a mixer sees of its entry: the entry's tensors (name -> [pages, *outer, PAGE,
+    inner], as its CacheNeed declared them) and its group's page tables for the sequences of
+    the current step ([B, max_pages] int32 on the device)."""
+    tensors: dict | None
     tables: torch.Tensor | None
     group: int
+
+    @property
+    def kv(self):
+        """Attention's tensor [pages, 2, kv_heads, PAGE, head_dim]."""
+        return None if self.tensors is None else self.tensors["kv"]
+
+
+def page_shape(per_token_shape) -> tuple:
+    """A page of a tensor with this per-token shape: the tokens run along the last but one axis."""
+    shape = tuple(int(d) for d in per_token_shape)
+    if not shape or min(shape) < 1:
+        raise ValueError(f"a cached tensor needs a per-token shape of positive sizes, got {per_token_shape}")
+    return shape[:-1] + (PAGE, shape[-1])
 
 
 class CacheGroup:
@@ -44,16 +59,15 @@ class CacheGroup:
         # per slot: pages [lo, hi) are mapped (lo > 0 only in window groups)
         self.lo = np.zeros(n_slots, dtype=np.int64)
         self.hi = np.zeros(n_slots, dtype=np.int64)
-        self.storage = None
+        self.storage: dict | None = None        # tensor name -> [entries, pages, *outer, PAGE, inner]
 
     def allocate(self, dtype, device) -> None:
-        n = self.need
-        self.storage = torch.zeros((len(self.entries), self.pool.n, 2, n.kv_heads, PAGE, n.head_dim),
-                                   dtype=dtype, device=device)
+        self.storage = {name: torch.zeros((len(self.entries), self.pool.n) + page_shape(shape), dtype=dtype,
+                                          device=device)
+                        for name, shape in self.need.tensors}
 
     def bytes_per_page(self, itemsize: int) -> int:
-        n = self.need
-        return len(self.entries) * 2 * n.kv_heads * PAGE * n.head_dim * itemsize
+        return len(self.entries) * PAGE * self.need.elements_per_token() * itemsize
 
 
 def pages_for(n_tokens: int) -> int:
@@ -86,6 +100,11 @@ class KVCache:
                 raise ValueError(f"entry {e}: unknown cache kind {need.kind!r}")
             if need.kind == "window" and need.window < 1:
                 raise ValueError(f"entry {e}: a window cache needs window >= 1")
+            names = [name for name, _ in need.tensors]
+            if not names or len(set(names)) != len(names):
+                raise ValueError(f"entry {e}: a cache need declares at least one tensor, each name once")
+            for _, shape in need.tensors:
+                page_shape(shape)
             by_need.setdefault(need, []).append(e)
         for gi, (need, entries) in enumerate(by_need.items()):
             pages = n_pages
@@ -183,9 +202,10 @@ class KVCache:
         return out
 
     def storage_of(self, entry: int):
+        """The entry's tensors: name -> [pages, *outer, PAGE, inner] (None before allocation)."""
         gi, j = self.entry_group[entry]
         st = self.groups[gi].storage
-        return None if st is None else st[j]
+        return None if st is None else {name: t[j] for name, t in st.items()}
 
     def group_of(self, entry: int) -> int:
         return self.entry_group[entry][0]

@@ -13,15 +13,18 @@
 // Same arguments and results as oe_attn_mma_bf16 (csrc/attention_mma.cu) without the
 // `partial` pointer.  Differences a caller has to know:
 //   * The scratch is OE_ATTN_NOALLOC_MAX_FLOATS float32 values (8 MiB).  Every GPU on which
-//     the library is loaded holds that array until the process exits.
+//     the library is loaded holds that array until the process exits.  The attention library
+//     is built once per head size, so a process that loads the libraries of several head
+//     sizes holds one such array per head size and GPU.
 //   * A call needs n_tokens * H * n_splits * (head_dim + 2) floats when n_splits > 1 (and
 //     none otherwise).  A call that needs more is refused with OE_ERR_SCRATCH_TOO_SMALL
 //     before anything is launched; oe_attn_mma_error_string() gives the text.
 //   * The first call on each device looks up the array's device address
-//     (cudaGetSymbolAddress, with that device current).  Make that first call outside any
-//     stream capture.
+//     (cudaGetSymbolAddress, with that device current) and keeps it.  Make that first call
+//     outside any stream capture, and from one thread: the look-up takes no lock (two
+//     threads that both make a first call would both store the same address).
 //   * Nothing in the array has to start at zero: each call writes every partial it later
-//     reads.  All calls share the one array, so two calls that may overlap on the GPU
+//     reads.  All calls of a head size share one array, so two calls that may overlap on the GPU
 //     (different streams without an ordering between them) race; keep them on one stream
 //     or order them with events.
 //   * It calls no cudaMalloc, cudaFree or other allocating routine.

@@ -16,11 +16,12 @@ import hashlib
 import os
 import shutil
 import subprocess
-import sys
 import tempfile
 import threading
 import time
 from pathlib import Path
+
+from ..utils.log import log
 
 CSRC = Path(__file__).resolve().parent
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -79,7 +80,7 @@ def _build_dir() -> Path:
 
 def _digest(source: Path, flags: list[str]) -> str:
     h = hashlib.sha1()
-    for p in [source] + sorted(CSRC.glob("*.cuh")):
+    for p in [source] + sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")):
         h.update(p.name.encode())
         h.update(p.read_bytes())
     h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + flags).encode())
@@ -114,28 +115,27 @@ def build(name: str, verbose: bool = True, defines=None) -> Path:
     cmd[cmd.index(None)] = str(tmp)
     t0 = time.time()
     if verbose:
-        print(f"[oracle_engine_b200] compiling {src} for sm_100a ...", file=sys.stderr, flush=True)
+        log.info("build", f"compiling {src}{tag} for sm_100a ...")
     env = dict(os.environ)
     env.setdefault("TMPDIR", tempfile.gettempdir())
     proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env)
     while True:
         try:
-            log, _ = proc.communicate(timeout=10)
+            output, _ = proc.communicate(timeout=10)
             break
         except subprocess.TimeoutExpired:
             if verbose:
-                print(f"[oracle_engine_b200]   ... still compiling {src} ({time.time() - t0:.0f} s)",
-                      file=sys.stderr, flush=True)
+                log.info("build", f"... still compiling {src}{tag} ({time.time() - t0:.0f} s)")
     if proc.returncode != 0:
         tmp.unlink(missing_ok=True)
-        raise BuildError(f"nvcc failed on {src} (exit {proc.returncode}):\n{' '.join(cmd)}\n{log}")
+        raise BuildError(f"nvcc failed on {src} (exit {proc.returncode}):\n{' '.join(cmd)}\n{output}")
     os.replace(tmp, out)
     # drop stale builds of the same library
     for old in out.parent.glob(f"liboe_{name}{tag}_*.so"):
         if old != out and len(old.name) == len(out.name):
             old.unlink(missing_ok=True)
     if verbose:
-        print(f"[oracle_engine_b200] built {out.name} in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
+        log.info("build", f"built {out.name} in {time.time() - t0:.1f} s")
     return out
 
 

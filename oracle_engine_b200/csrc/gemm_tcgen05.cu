@@ -27,11 +27,11 @@
 namespace {
 
 constexpr int BLOCK_M = 128;       // rows of the A tile = UMMA M
-constexpr int BLOCK_K = 64;        // bf16 per k-block = one 128-byte swizzled row
+constexpr int BLOCK_K = 64;        // bf16 per swizzle atom = one 128-byte swizzled row; a k-block is 1 or 2 atoms
 constexpr int UMMA_K = 16;
 constexpr int A_TILE_BYTES = BLOCK_M * BLOCK_K * 2;      // 16 KB
 constexpr int THREADS = 192;
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s: the default limit of every wait (GemmArgs::wait_ns)
 
 __device__ int g_error = 0;        // 0 = ok; else code of the wait that ran out
 
@@ -40,6 +40,7 @@ struct SharedCtl {
     uint64_t empty[12];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
+    unsigned long long wait_ns;      // limit of every wait on an mbarrier
     uint32_t tmem_base;
     int abort_flag;
     int is_last;
@@ -91,8 +92,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-// Waits for the phase with `parity` to complete; gives up after WAIT_LIMIT_NS or when
-// another role has given up, and then returns false.
+// Waits for the phase with `parity` to complete; gives up after the limit (ctl->wait_ns) or
+// when another role has given up, and then returns false.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, SharedCtl* ctl, int code) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
@@ -100,7 +101,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Shared
         if (mbar_try_wait(bar, parity)) return true;
         if ((spin & 255u) == 255u) {
             if (*(volatile int*)&ctl->abort_flag) return false;
-            if (global_ns() - t0 > WAIT_LIMIT_NS) {
+            if (global_ns() - t0 > ctl->wait_ns) {
                 atomicExch(&ctl->abort_flag, 1);
                 atomicCAS(&g_error, 0, code);
                 return false;
@@ -157,6 +158,7 @@ struct GemmArgs {
     long long ldc;
     int rows_a, rows_b, K;      // valid rows of the A (128-row) and B (n_tile-row) operands
     int n_tile;                 // rows of the B tile, multiple of 16, <= 256
+    int atoms;                  // 64-deep swizzle atoms per k-block and pipeline stage (1 or 2)
     int stages;
     int swap;                   // 1: C[b_row, a_row] (A = weights); 0: C[a_row, b_row] (A = activations)
     int out_kind;               // 0 bf16 store, 1 float32 store, 2 float32 accumulate, 3 bf16 silu(gate)*up
@@ -167,6 +169,9 @@ struct GemmArgs {
     int cluster;                // > 1: the K splits of a tile are the CTAs of one cluster, which add up through shared memory
     float* workspace;           // [splits][tiles_a][tiles_b][n_tile][128] float32 when splits > 1
     int* counters;              // [tiles_a * tiles_b], zero between launches
+    unsigned long long wait_ns; // after this long a wait on an mbarrier gives up (error flag, the kernel returns)
+    int withhold_release;       // tests of that path: the epilogue never hands an accumulator back, so that the
+                                // MMA role's wait for one runs out (0 in every other use)
 };
 
 // Accumulation into C goes out as reductions that the L2 performs (no load on the SM's side, so
@@ -328,7 +333,7 @@ struct ItemIter {
 __device__ __forceinline__ ItemIter make_iter(const GemmArgs& g) {
     ItemIter t;
     t.streamk = g.streamk; t.cluster = g.cluster; t.tiles_a = g.tiles_a; t.tiles_b = g.tiles_b; t.splits = g.splits;
-    t.n_kb_total = (g.K + BLOCK_K - 1) / BLOCK_K;
+    t.n_kb_total = (g.K + BLOCK_K * g.atoms - 1) / (BLOCK_K * g.atoms);
     t.kb_per = (t.n_kb_total + g.splits - 1) / g.splits;
     t.w = blockIdx.x; t.step = gridDim.x; t.n_work = g.tiles_a * g.tiles_b * g.splits;
     t.G = gridDim.x;
@@ -354,8 +359,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // tiles first (1024-byte aligned for the 128-byte swizzle), control block after them
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // a stage: the A tile's atoms (128 rows x 128 bytes each), then the B tile's
     const int b_tile_bytes = g.n_tile * BLOCK_K * 2;
-    const int stage_bytes = A_TILE_BYTES + ((b_tile_bytes + 1023) & ~1023);
+    const int b_atom_bytes = (b_tile_bytes + 1023) & ~1023;
+    const int stage_bytes = g.atoms * (A_TILE_BYTES + b_atom_bytes);
+    const int b_off = g.atoms * A_TILE_BYTES;
+    const int kb_elems = BLOCK_K * g.atoms;
+    const uint32_t stage_tx = (uint32_t)(g.atoms * (A_TILE_BYTES + b_tile_bytes));
     SharedCtl* ctl = (SharedCtl*)(smem + (size_t)g.stages * stage_bytes);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -367,6 +377,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int s = 0; s < g.stages; s++) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
         for (int b = 0; b < 2; b++) { mbar_init(&ctl->tmem_full[b], 1); mbar_init(&ctl->tmem_empty[b], 4); }
         ctl->abort_flag = 0;
+        ctl->wait_ns = g.wait_ns;
         ctl->is_last = 0;
         ctl->epi_ok = 1;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -399,16 +410,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const int first = min(n_kb, g.stages);
                     for (; i < first; i++) {
                         uint8_t* a_dst = smem + (size_t)i * stage_bytes;
-                        mbar_expect_tx(&ctl->full[i], (uint32_t)(A_TILE_BYTES + b_tile_bytes));
-                        if (g.swap) tma_load_2d(a_dst, &map_a, &ctl->full[i], (kb0 + i) * BLOCK_K, tile_a * BLOCK_M);
-                        else tma_load_2d(a_dst + A_TILE_BYTES, &map_b, &ctl->full[i], (kb0 + i) * BLOCK_K, tile_b * g.n_tile);
+                        mbar_expect_tx(&ctl->full[i], stage_tx);
+                        for (int h = 0; h < g.atoms; h++) {
+                            if (g.swap) tma_load_2d(a_dst + h * A_TILE_BYTES, &map_a, &ctl->full[i], (kb0 + i) * kb_elems + h * BLOCK_K, tile_a * BLOCK_M);
+                            else tma_load_2d(a_dst + b_off + h * b_atom_bytes, &map_b, &ctl->full[i], (kb0 + i) * kb_elems + h * BLOCK_K, tile_b * g.n_tile);
+                        }
                     }
                     pdl_wait();
                     waited = true;
                     for (int j = 0; j < first; j++) {
                         uint8_t* a_dst = smem + (size_t)j * stage_bytes;
-                        if (g.swap) tma_load_2d(a_dst + A_TILE_BYTES, &map_b, &ctl->full[j], (kb0 + j) * BLOCK_K, tile_b * g.n_tile);
-                        else tma_load_2d(a_dst, &map_a, &ctl->full[j], (kb0 + j) * BLOCK_K, tile_a * BLOCK_M);
+                        for (int h = 0; h < g.atoms; h++) {
+                            if (g.swap) tma_load_2d(a_dst + b_off + h * b_atom_bytes, &map_b, &ctl->full[j], (kb0 + j) * kb_elems + h * BLOCK_K, tile_b * g.n_tile);
+                            else tma_load_2d(a_dst + h * A_TILE_BYTES, &map_a, &ctl->full[j], (kb0 + j) * kb_elems + h * BLOCK_K, tile_a * BLOCK_M);
+                        }
                     }
                     it = first;
                 }
@@ -417,9 +432,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const uint32_t phase = (uint32_t)(it / g.stages) & 1u;
                     if (!mbar_wait(&ctl->empty[s], phase ^ 1u, ctl, 1)) { ok = false; break; }
                     uint8_t* a_dst = smem + (size_t)s * stage_bytes;
-                    mbar_expect_tx(&ctl->full[s], (uint32_t)(A_TILE_BYTES + b_tile_bytes));
-                    tma_load_2d(a_dst, &map_a, &ctl->full[s], (kb0 + i) * BLOCK_K, tile_a * BLOCK_M);
-                    tma_load_2d(a_dst + A_TILE_BYTES, &map_b, &ctl->full[s], (kb0 + i) * BLOCK_K, tile_b * g.n_tile);
+                    mbar_expect_tx(&ctl->full[s], stage_tx);
+                    for (int h = 0; h < g.atoms; h++) {
+                        tma_load_2d(a_dst + h * A_TILE_BYTES, &map_a, &ctl->full[s], (kb0 + i) * kb_elems + h * BLOCK_K, tile_a * BLOCK_M);
+                        tma_load_2d(a_dst + b_off + h * b_atom_bytes, &map_b, &ctl->full[s], (kb0 + i) * kb_elems + h * BLOCK_K, tile_b * g.n_tile);
+                    }
                 }
             }
         }
@@ -443,12 +460,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const uint32_t phase = (uint32_t)(it / g.stages) & 1u;
                     if (!mbar_wait(&ctl->full[s], phase, ctl, 2)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a_addr = smem_u32(smem + (size_t)s * stage_bytes);
-                    const uint32_t b_addr = a_addr + A_TILE_BYTES;
+                    for (int h = 0; h < g.atoms; h++) {
+                        const uint32_t a_addr = smem_u32(smem + (size_t)s * stage_bytes) + (uint32_t)(h * A_TILE_BYTES);
+                        const uint32_t b_addr = smem_u32(smem + (size_t)s * stage_bytes) + (uint32_t)(b_off + h * b_atom_bytes);
 #pragma unroll
-                    for (int k = 0; k < BLOCK_K / UMMA_K; k++) {
-                        umma_bf16(tmem_d, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc,
-                                  (i > 0 || k > 0) ? 1u : 0u);
+                        for (int k = 0; k < BLOCK_K / UMMA_K; k++) {
+                            umma_bf16(tmem_d, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc,
+                                      (i > 0 || h > 0 || k > 0) ? 1u : 0u);
+                        }
                     }
                     umma_commit(&ctl->empty[s]);          // frees the stage when these MMAs have read it
                 }
@@ -582,7 +601,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // the accumulator has been read: the MMA warp may reuse it
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&ctl->tmem_empty[buf])) : "memory");
+            if (lane == 0 && !g.withhold_release)
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&ctl->tmem_empty[buf])) : "memory");
             if (shared_tile) {
                 // the CTA that arrives last adds the partial sums in k order
                 __threadfence();
@@ -711,6 +731,9 @@ int g_force_tile = 0;       // measurements only: tile width and schedule for ma
 int g_force_streamk = -1;
 int g_force_narrow = -1;      // 48..128 tokens: 1 narrow tiles, 0 swap-AB with split K, -1 by the shape
 int g_force_cluster = -1;     // 0: K splits add up through the workspace even where a cluster could
+int g_force_atoms = -1;       // up to 128 tokens, swap-AB: 64-deep atoms per k-block (1 or 2; -1 by the shape)
+unsigned long long g_wait_ns = WAIT_LIMIT_NS;   // the limit the next launches give their waits
+int g_withhold_release = 0;   // tests: see GemmArgs::withhold_release
 int g_max_clusters[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};   // clusters of that many CTAs that fit on the GPU at once
 std::mutex g_mutex;
 
@@ -786,9 +809,11 @@ int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, 
     GemmArgs g;
     g.C = C; g.ldc = ldc; g.K = K; g.out_kind = out_kind;
     g.workspace = workspace; g.counters = counters; g.splits = 1; g.streamk = 0; g.sk_tiles = 0; g.cluster = 1;
+    g.atoms = 1;
+    g.wait_ns = g_wait_ns; g.withhold_release = g_withhold_release;
     CUtensorMap map_a, map_b;
     dim3 grid;
-    const int n_kb = (K + BLOCK_K - 1) / BLOCK_K;
+    int n_kb = (K + BLOCK_K - 1) / BLOCK_K;
     // 48..128 tokens, a short K and so many weight rows that swap-AB could not split K (fewer than
     // two CTAs per 128 rows): the activations stay the 128-row operand (rows beyond M are not
     // fetched) and a narrow weight tile per CTA gives about one CTA per SM, no split.  Measured at
@@ -804,6 +829,8 @@ int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, 
         if (nt > 256) nt = 256;
         g.n_tile = nt;
         g.rows_a = M; g.rows_b = N;
+        g.atoms = g_force_atoms > 0 ? g_force_atoms : (K >= 1024 ? 2 : 1);    // gate/up at 64 tokens: 30.5 -> 25.6 us
+        n_kb = (K + BLOCK_K * g.atoms - 1) / (BLOCK_K * g.atoms);
         if ((rc = make_map(&map_a, A, M, K, lda, BLOCK_M))) return rc;
         if ((rc = make_map(&map_b, W, N, K, K, g.n_tile))) return rc;
         g.tiles_a = 1;
@@ -813,11 +840,20 @@ int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, 
         g.swap = 1;
         g.n_tile = ((M + 15) / 16) * 16;
         g.rows_a = N; g.rows_b = M;
+        // One CTA alone on the GPU streams 38 GB/s of weights with k-blocks of one 64-deep atom
+        // (24 KB a stage at 64 tokens, 417 ns each) and 53 GB/s with two atoms (48 KB, 600 ns): a
+        // k-block costs about 230 ns whatever it brings, plus its bytes at about 130 GB/s.  With two
+        // atoms the layer products at 64 tokens take 11.8, 13.8, 16.7 us instead of 13.0, 15.7, 19.9;
+        // a product with many tiles per CTA (the logits) streams at 0.9 of the HBM figure either way.
+        g.atoms = g_force_atoms > 0 ? g_force_atoms
+                                    : ((K >= 1024 && (N + BLOCK_M - 1) / BLOCK_M <= 2 * sm_count) ? 2 : 1);
+        n_kb = (K + BLOCK_K * g.atoms - 1) / (BLOCK_K * g.atoms);
         const int tiles_a = (N + BLOCK_M - 1) / BLOCK_M;
         int splits = 1;
         if (workspace && counters && tiles_a <= n_counters) {
             splits = sm_count / tiles_a;                      // one wave of CTAs
-            if (splits > n_kb / 4) splits = n_kb / 4;
+            if (splits > n_kb * g.atoms / 4) splits = n_kb * g.atoms / 4;
+            if (splits > n_kb) splits = n_kb;
             if (splits < 1) splits = 1;
             const long long need = (long long)splits * tiles_a * g.n_tile * BLOCK_M * 4;
             if (need > ws_bytes) splits = 1;
@@ -898,7 +934,7 @@ int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, 
     if (n_work > 2147483647LL) return OE_ERR_UNSUPPORTED;
     grid = dim3((unsigned)((n_work < sm_count && !g.streamk) ? n_work : sm_count));
     const int b_tile_bytes = g.n_tile * BLOCK_K * 2;
-    const int stage_bytes = A_TILE_BYTES + ((b_tile_bytes + 1023) & ~1023);
+    const int stage_bytes = g.atoms * (A_TILE_BYTES + ((b_tile_bytes + 1023) & ~1023));
     int stages = (200 * 1024) / stage_bytes;
     if (stages > 10) stages = 10;
     if (stages > n_kb && n_kb > 0) stages = n_kb < 2 ? 2 : n_kb;
@@ -920,9 +956,20 @@ int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, 
 // For measurements: forces the tile width (0: chosen by the shape) and the schedule (1: stream-K
 // wherever a remainder exists, 0: whole tiles, -1: chosen by the shape) of products over many tokens,
 // (cluster = 0) K splits of few tokens through the workspace instead of a cluster, and (narrow = 1 / 0)
-// up to 128 tokens narrow tiles without a split or swap-AB with split K.
-void oe_gemm_tc_force(int n_tile, int streamk, int cluster, int narrow) {
+// up to 128 tokens narrow tiles without a split or swap-AB with split K, and (atoms = 1 / 2) how many
+// 64-deep swizzle atoms a k-block of those products holds.
+void oe_gemm_tc_force(int n_tile, int streamk, int cluster, int narrow, int atoms) {
     g_force_tile = n_tile; g_force_streamk = streamk; g_force_cluster = cluster; g_force_narrow = narrow;
+    g_force_atoms = atoms;
+}
+
+// The limit (nanoseconds; <= 0: the default of 2 s) that the waits of the following launches get, and, for
+// the test of the path a run-out wait takes, whether their epilogues withhold the release of their
+// accumulators (the MMA role's wait then runs out on a CTA's third tile, the kernel sets the error flag,
+// waits for what is in flight, frees its tensor memory and returns; its output is then not valid).
+void oe_gemm_tc_waits(long long wait_ns, int withhold_release) {
+    g_wait_ns = wait_ns > 0 ? (unsigned long long)wait_ns : WAIT_LIMIT_NS;
+    g_withhold_release = withhold_release ? 1 : 0;
 }
 
 // Diagnostics: how many clusters of cs CTAs of the kernel run at once.

@@ -80,21 +80,28 @@ def run_gemm(a):
     swiglu, acc = a.out == "swiglu", a.out == "accumulate"
     dtype = torch.float32 if a.out in ("float32", "accumulate") else torch.bfloat16
     out = torch.zeros(M, N // 2 if swiglu else N, device=dev, dtype=dtype)
-    ops_tc.force_schedule(a.tile, a.stream_k, a.cluster, a.narrow)
-    ops_tc.gemm(out, x, ws[0], accumulate=acc, swiglu=swiglu, kernel=a.kernel)
-    ref = x[:64].double() @ ws[0].double().T
-    if swiglu:
-        ref = ref[:, 0::2] / (1 + torch.exp(-ref[:, 0::2])) * ref[:, 1::2]
-    err = ((out[:64].double() - ref).abs().max() / ref.abs().max()).item()
-    us = timed(lambda i: ops_tc.gemm(out, x, ws[i % copies], accumulate=acc, swiglu=swiglu, kernel=a.kernel),
-               a.iters, a.once)
+    with ops_tc.knobs(gemm_schedule=(a.tile, a.stream_k, a.cluster, a.narrow, a.atoms), sm_count=a.sms):
+        ops_tc.gemm(out, x, ws[0], accumulate=acc, swiglu=swiglu, kernel=a.kernel)
+        ref = x[:64].double() @ ws[0].double().T
+        if swiglu:
+            ref = ref[:, 0::2] / (1 + torch.exp(-ref[:, 0::2])) * ref[:, 1::2]
+        err = ((out[:64].double() - ref).abs().max() / ref.abs().max()).item()
+        us = timed(lambda i: ops_tc.gemm(out, x, ws[i % copies], accumulate=acc, swiglu=swiglu, kernel=a.kernel),
+                   a.iters, a.once)
+    extra = "(relative)"
+    if a.sms and us is not None:
+        extra += f"  {N * K * 2 / us / 1e3 / a.sms:.1f} GB/s of weights per SM on {a.sms} SMs"
     report(f"gemm M={M} N={N} K={K} out={a.out} kernel={a.kernel}", us, N * K * 2 + M * K * 2 + out.numel() * out.element_size(),
-           2.0 * M * N * K, err, "(relative)")
+           2.0 * M * N * K, err, extra)
     assert ops_tc.device_error() == 0
 
 
 def run_attention(a):
-    ops_tc.DECODE_SPLITS[0] = a.splits
+    with ops_tc.knobs(decode_splits=a.splits):
+        _run_attention(a)
+
+
+def _run_attention(a):
     dev = torch.device("cuda:0")
     H, KVH, hd, B = a.heads, a.kv_heads, a.head_dim, a.batch
     qlen = a.prompt if a.prompt else 1
@@ -167,6 +174,10 @@ def main(argv=None):
                    help="one-SM tcgen05 kernel, up to 128 tokens: 1 narrow tiles without a split, 0 swap-AB with split K")
     g.add_argument("--stream-k", type=int, default=-1, choices=[-1, 0, 1],
                    help="one-SM tcgen05 kernel, many tokens: 1 stream-K wherever a remainder exists, 0 whole tiles, -1 by the shape")
+    g.add_argument("--atoms", type=int, default=-1, choices=[-1, 1, 2],
+                   help="one-SM tcgen05 kernel, up to 128 tokens: 64-deep swizzle atoms per k-block (-1: by the shape)")
+    g.add_argument("--sms", type=int, default=0,
+                   help="one-SM tcgen05 kernel: plan the grid for this many SMs (0: the device's); shows what one SM streams")
     at = sub.add_parser("attention")
     at.add_argument("--batch", type=int, default=8)
     at.add_argument("--context", type=int, default=640)

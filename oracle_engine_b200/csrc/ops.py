@@ -16,6 +16,7 @@ from . import build as _build
 
 ERR_UNSUPPORTED = 100001
 PAGE = 64            # tokens per cache page; must equal OE_PAGE of common.cuh
+MAX_HEAD_DIM = 256   # the largest head size the attention kernels take; must equal MAX_HD of attention.cu
 
 
 class KernelError(RuntimeError):
@@ -77,11 +78,14 @@ def _stream() -> int:
 
 
 LAUNCHES = [0]          # kernels launched through this module (or captured into a graph)
+OBSERVER = [None]       # engine/profile.py: an object whose mark(what, detail) hears of every launch
 
 
-def _check(code: int, what: str) -> None:
+def _check(code: int, what: str, detail=None) -> None:
     if code == 0:
         LAUNCHES[0] += 1
+        if OBSERVER[0] is not None:
+            OBSERVER[0].mark(what, detail)
         return
     if code == ERR_UNSUPPORTED:
         raise KernelError(f"{what}: sizes outside what this kernel takes")

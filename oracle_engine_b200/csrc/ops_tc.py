@@ -7,6 +7,7 @@ on shapes only.
 """
 from __future__ import annotations
 
+import contextlib
 from ctypes import c_int, c_longlong, c_void_p
 
 import torch
@@ -16,6 +17,55 @@ from . import ops
 from .ops import KernelError
 
 _state: dict = {}
+
+
+class _Knobs:
+    """Choices that measurements and tests may pin; the defaults are what serving uses.
+    They are set only through `knobs(...)`, which puts the old values back when its block ends."""
+    prompt_kernel = "tcgen05"      # "tcgen05" or "mma": the prompt attention kernel for head sizes 64 / 128
+    decode_kernel = "auto"         # "auto", "warps", "split": the decode attention kernel
+    decode_splits = 0              # > 0: this many CTAs per (sequence, KV head) instead of the rule's
+    pair_max_tile = 0              # > 0: an upper limit for the two-SM product's tile width
+    sm_count = 0                   # > 0: the products plan their grids for this many SMs
+    gemm_schedule = (0, -1, -1, -1, -1)     # one-SM tcgen05 product: tile width, stream-K, cluster, narrow, atoms (see knobs)
+    gemm_waits = (0, 0)            # one-SM tcgen05 product: the limit of its waits in ns (0: 2 s), and whether its
+                                   # epilogues withhold their accumulators (the test of a wait that runs out)
+
+
+KNOBS = _Knobs()
+
+
+@contextlib.contextmanager
+def knobs(**kw):
+    """with knobs(prompt_kernel="mma", decode_splits=4): ...   pins choices inside the block.
+
+    gemm_schedule = (n_tile, stream_k, cluster, narrow[, atoms]) of the one-SM tcgen05 product: its tile
+    width for many tokens (0: chosen by the shape), its schedule (1: stream-K wherever the tiles
+    leave a remainder, 0: whole tiles, -1: by the shape); for up to 128 tokens whether the K
+    splits of a tile may be the CTAs of a cluster (0: never, they add up through the workspace)
+    and whether narrow tiles without a split (1) or swap-AB with split K (0) are used (-1: by
+    the shape), and how many 64-deep swizzle atoms a k-block of those products holds (1, 2; -1: by
+    the shape)."""
+    old = {}
+    for k, v in kw.items():
+        if not hasattr(_Knobs, k):
+            raise KeyError(f"unknown knob {k!r}")
+        old[k] = getattr(KNOBS, k)
+    try:
+        for k, v in kw.items():
+            setattr(KNOBS, k, (tuple(v) + (-1,) * 5)[:5] if k == "gemm_schedule" else v)
+        if "gemm_schedule" in kw:
+            _lib().oe_gemm_tc_force(*[int(x) for x in KNOBS.gemm_schedule])
+        if "gemm_waits" in kw:
+            _lib().oe_gemm_tc_waits(c_longlong(int(KNOBS.gemm_waits[0])), int(KNOBS.gemm_waits[1]))
+        yield KNOBS
+    finally:
+        for k, v in old.items():
+            setattr(KNOBS, k, v)
+        if "gemm_schedule" in old:
+            _lib().oe_gemm_tc_force(*[int(x) for x in KNOBS.gemm_schedule])
+        if "gemm_waits" in old:
+            _lib().oe_gemm_tc_waits(c_longlong(int(KNOBS.gemm_waits[0])), int(KNOBS.gemm_waits[1]))
 
 
 def _lib():
@@ -61,7 +111,6 @@ SKINNY_MAX_TOKENS = 16      # up to here the weight-streaming kernel (gemm_skinn
                             # for a layer's four products at 16 tokens; from 24 tokens on tcgen05 wins)
 PAIR_MIN_TOKENS = 256       # from here on the two-SM kernel (gemm_tcgen05_pair.cu) for stores; measured the
                             # same speed as the one-SM kernel or a little faster, except with the accumulate epilogue
-PAIR_MAX_TILE = [0]         # tests: an upper limit for the pair kernel's tile width (0 = none)
 
 
 def _pair():
@@ -85,15 +134,6 @@ def _skinny():
         lib.oe_gemm_skinny_bf16.restype = c_int
         _state["skinny"] = lib
     return lib
-
-
-def force_schedule(n_tile: int = 0, stream_k: int = -1, cluster: int = -1, narrow: int = -1) -> None:
-    """Measurements and tests: the one-SM tcgen05 kernel's tile width for many tokens (0: chosen
-    by the shape), its schedule (1: stream-K wherever the tiles leave a remainder, 0: whole
-    tiles, -1: chosen by the shape); for up to 128 tokens whether the K splits of a tile may be
-    the CTAs of a cluster (0: never, they add up through the workspace) and whether narrow
-    tiles without a split (1) or swap-AB with split K (0) are used (-1: by the shape)."""
-    _lib().oe_gemm_tc_force(int(n_tile), int(stream_k), int(cluster), int(narrow))
 
 
 def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool = False, split_k: bool = True,
@@ -130,19 +170,20 @@ def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool =
     if kernel == "skinny" or (kernel == "auto" and M <= SKINNY_MAX_TOKENS):
         code = _skinny().oe_gemm_skinny_bf16(out.data_ptr(), a.data_ptr(), w.data_ptr(), M, N, K, a.stride(0),
                                              out.stride(0), kind, int(early), ops._stream())
-        ops._check(code, "gemm_skinny")
+        ops._check(code, "gemm_skinny", (M, N, K))
         return
     if kernel == "pair" or (kernel == "auto" and M >= PAIR_MIN_TOKENS and N >= 32 and not accumulate):
         code = _pair().oe_gemm_pair_bf16(out.data_ptr(), a.data_ptr(), w.data_ptr(), M, N, K, a.stride(0), out.stride(0),
-                                         kind, PAIR_MAX_TILE[0], ops._stream())
-        ops._check(code, "gemm_pair")
+                                         kind, int(KNOBS.pair_max_tile), ops._stream())
+        ops._check(code, "gemm_pair", (M, N, K))
         return
     ws, counters, sms = _scratch(a.device)
+    sms = KNOBS.sm_count or sms
     code = _lib().oe_gemm_tc_bf16(out.data_ptr(), a.data_ptr(), w.data_ptr(), M, N, K, a.stride(0), out.stride(0), kind,
                                   ws.data_ptr() if split_k else None, ws.numel() * 4,
                                   counters.data_ptr() if split_k else None, counters.numel(), sms,
                                   ops._stream())
-    ops._check(code, "gemm_tc")
+    ops._check(code, "gemm_tc", (M, N, K))
 
 
 def device_error() -> int:
@@ -194,7 +235,6 @@ def _attn_lib(head_dim: int):
 
 
 TCGEN05_ATTENTION_HEAD_DIMS = (64, 128)
-PROMPT_KERNEL = ["tcgen05"]          # "tcgen05" or "mma": which prompt kernel head sizes 64 / 128 use
 
 
 def _attn_tc5_lib(head_dim: int):
@@ -211,9 +251,6 @@ def _attn_tc5_lib(head_dim: int):
     return lib
 
 
-DECODE_SPLITS = [0]          # measurements: this many CTAs per (sequence, KV head) instead of the rule's
-
-
 def decode_splits(n_seqs: int, n_kv_heads: int, sm_count: int, max_pages: int, context_class: int = 0,
                   ctas_per_sm: int = 3) -> int:
     """How many CTAs share one (sequence, KV head) of a decode step, never more than the pages a
@@ -223,8 +260,8 @@ def decode_splits(n_seqs: int, n_kv_heads: int, sm_count: int, max_pages: int, c
     the keys' bytes: the fewest splits that fill the last round of resident CTAs (ctas_per_sm x SMs)
     to 85 %, else the best-filled; measured at 8,000 keys (us): 8 sequences 5 / 6 splits 57 / 50,
     32 sequences 2 / 3 splits 246 / 175, 40 sequences 1 / 4 splits 362 / 206."""
-    if DECODE_SPLITS[0] > 0:
-        return max(1, min(max_pages, 32, DECODE_SPLITS[0]))
+    if KNOBS.decode_splits > 0:
+        return max(1, min(max_pages, 32, KNOBS.decode_splits))
     ctas = max(1, n_seqs * n_kv_heads)
     cap = max(1, min(max_pages, 32))
     if context_class <= 0:
@@ -270,7 +307,7 @@ def attention(out, qkv, cache, tables, ctx, n_heads: int, n_kv_heads: int, head_
     if tuple(cache.shape[1:]) != (2, n_kv_heads, ops.PAGE, head_dim):
         raise KernelError("attention: cache entry must be [pages, 2, KVH, PAGE, head_dim]")
     group = n_heads // n_kv_heads
-    if (PROMPT_KERNEL[0] == "tcgen05" and head_dim in TCGEN05_ATTENTION_HEAD_DIMS and ctx.max_qlen * group > 64
+    if (KNOBS.prompt_kernel == "tcgen05" and head_dim in TCGEN05_ATTENTION_HEAD_DIMS and ctx.max_qlen * group > 64
             and group <= 128 and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0):
         # prompts: S and O_blk in tensor memory (csrc/attention_tcgen05.cu)
         code = _attn_tc5_lib(head_dim).oe_attn_tc_bf16(
@@ -292,7 +329,7 @@ def attention(out, qkv, cache, tables, ctx, n_heads: int, n_kv_heads: int, head_
                                 n_heads, n_kv_heads, int(window), float(scale), n_splits,
                                 None if partial is None else partial.data_ptr(),
                                 ops._stream())
-    ops._check(code, "attention_mma")
+    ops._check(code, "attention_mma", {"splits": n_splits})
     if n_splits > 1:
         ops.LAUNCHES[0] += 1
 
@@ -301,7 +338,6 @@ def decode_fused_supported(head_dim: int, n_heads: int, n_kv_heads: int) -> bool
     return attention_supported(head_dim, n_heads, n_kv_heads) and head_dim % 32 == 0
 
 
-DECODE_KERNEL = ["auto"]     # "auto", "warps", "split" (tests pin a kernel)
 DECODE_WARPS_FULL_CTAS = 48  # (sequence, KV head) pairs from which contexts of class 1 stay on the warps kernel too
 DECODE_WARPS_LONG_CTAS = 96  # ... and contexts of class 2
 DECODE_WARPS_MAX_CTAS = 300  # short contexts with more pairs than this: the one-warp kernel, several CTAs an SM
@@ -322,9 +358,9 @@ def decode_uses_warps(n_seqs: int, context_class: int, head_dim: int, n_heads: i
     class 1 (2,048): 1 sequence 20 / 12 / 28, 8: 21 / 22 / 43, 64: 93 / 105 / 108;
     class 2 (8,000): 1: 63 / 18 / 33, 8: 66 / 56 / 109, 16: 90 / 90, 24: 150 / 130, 32: 159 / 246,
     64: 316 / 390 / 391."""
-    if DECODE_KERNEL[0] == "split" or not decode_warps_supported(head_dim, n_heads, n_kv_heads):
+    if KNOBS.decode_kernel == "split" or not decode_warps_supported(head_dim, n_heads, n_kv_heads):
         return False
-    if DECODE_KERNEL[0] == "warps":
+    if KNOBS.decode_kernel == "warps":
         return True
     pairs = n_seqs * n_kv_heads
     if context_class <= 0:
@@ -375,9 +411,11 @@ def _attn_counters(device):
 
 
 def attention_decode_fused(out, qkv, cos, sin, cache, tables, ctx, n_heads: int, n_kv_heads: int, head_dim: int,
-                           window: int, scale: float, has_kv: bool) -> None:
+                           window: int, scale: float, has_kv: bool, n_splits: int | None = None) -> None:
     """One kernel for a decode step's mixer core: rotates q and the new k, stores k and v
     in the cache (has_kv), attends over the sequence's pages split across CTAs and merges.
+    n_splits: CTAs per (sequence, KV head); None: the rule of `decode_splits_for` for the step's
+    context class (the caller that chose this kernel by that rule passes what it got).
 
     qkv [B, (H + 2 KVH) hd] (or [B, H hd] when has_kv is false) before rotation; cos/sin
     float32 [max_pos, hd/2] or None; every sequence of the step brings exactly one token."""
@@ -392,8 +430,8 @@ def attention_decode_fused(out, qkv, cos, sin, cache, tables, ctx, n_heads: int,
     if ctx.n_seqs * n_kv_heads > (1 << 16):
         raise KernelError("attention_decode_fused: too many sequences for the merge counters")
     lib = _attn_lib(head_dim)
-    sms = torch.cuda.get_device_properties(out.device).multi_processor_count
-    n_splits = decode_splits(ctx.n_seqs, n_kv_heads, sms, tables.shape[1])
+    if n_splits is None:
+        n_splits = decode_splits_for(ctx.n_seqs, n_kv_heads, tables, getattr(ctx, "context_class", 0), head_dim)
     partial = None
     if n_splits > 1:
         partial = torch.empty(lib.oe_attn_mma_partial_floats(B, n_heads, n_splits), dtype=torch.float32,
@@ -404,4 +442,4 @@ def attention_decode_fused(out, qkv, cos, sin, cache, tables, ctx, n_heads: int,
         ctx.cu_q.data_ptr(), ctx.seq_start.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.n_seqs, n_heads, n_kv_heads,
         int(window), float(scale), n_splits, None if partial is None else partial.data_ptr(),
         _attn_counters(out.device).data_ptr(), ops._stream())
-    ops._check(code, "attention_decode_fused")
+    ops._check(code, "attention_decode_fused", {"splits": n_splits})

@@ -18,6 +18,8 @@ This library's own:
     --stop-id <N>   extra stop id (repeatable)   --ignore-eos
     --dtype bfloat16|float32 (default bfloat16)   --max-tokens <N> cache size in tokens
     --batch <N>     requests per batch (default: all at once)
+    --step-tokens <N>  most prompt tokens per step (longer prompts go through in portions)
+    --profile       device time per kind of kernel, on standard error (runs without CUDA graphs)
     --random-weights <seed> --config <config.json>   run a configuration with seeded random weights
 Unknown option or missing -m / prompt: usage, exit 2.  Model cannot be loaded: exit 1.
 The reference's --system and --draft (chat template, speculative decoding) are not part of
@@ -35,7 +37,7 @@ USAGE = """Usage: {exe} -m <model_dir> (-p <prompt> | --tokens <ids>) [options]
   --top-k <N>     top-k                   (default 40)
   --tokens a,b,c  prompt as token ids (repeatable)
   --seed <N>  --repeat-penalty <f>  --repeat-last-n <N>  --stop-id <N>  --ignore-eos
-  --dtype bfloat16|float32  --max-tokens <N>  --batch <N>
+  --dtype bfloat16|float32  --max-tokens <N>  --batch <N>  --step-tokens <N>  --profile
   --random-weights <seed> --config <config.json>
   --no-stream     print the answer in one block
 """
@@ -47,7 +49,7 @@ def main(argv=None) -> int:
     from ..sampling.params import GenParams
     params = GenParams()
     opt = {"model": "", "prompt": "", "tokens": [], "stream": True, "dtype": "bfloat16", "max_tokens": 0,
-           "batch": None, "stop": [], "random": None, "config": ""}
+           "batch": None, "stop": [], "random": None, "config": "", "step_tokens": None, "profile": False}
     i = 0
 
     def val(name):
@@ -91,6 +93,10 @@ def main(argv=None) -> int:
                 opt["max_tokens"] = int(val(k))
             elif k == "--batch":
                 opt["batch"] = int(val(k))
+            elif k == "--step-tokens":
+                opt["step_tokens"] = int(val(k))
+            elif k == "--profile":
+                opt["profile"] = True
             elif k == "--random-weights":
                 opt["random"] = int(val(k))
             elif k == "--config":
@@ -122,10 +128,12 @@ def main(argv=None) -> int:
             from ..config.base import architecture_name, get_architecture
             raw = json.loads(open(opt["config"]).read())
             config = get_architecture(architecture_name(raw)).config_cls.from_dict(raw)
-            engine = Engine.from_config(config, seed=opt["random"], dtype=opt["dtype"], max_tokens=max_tokens)
+            engine = Engine.from_config(config, seed=opt["random"], dtype=opt["dtype"], max_tokens=max_tokens,
+                                        use_graphs=not opt["profile"])
             tok = None
         else:
-            engine = Engine.from_pretrained(opt["model"], dtype=opt["dtype"], max_tokens=max_tokens)
+            engine = Engine.from_pretrained(opt["model"], dtype=opt["dtype"], max_tokens=max_tokens,
+                                            use_graphs=not opt["profile"])
             tok = Tokenizer.from_folder(opt["model"], engine.spec.bos_id)
     except Exception as e:                                   # noqa: BLE001 - reported, exit code 1 as the reference
         sys.stderr.write(f"error: failed to load model '{opt['model'] or opt['config']}': {e}\n")
@@ -160,8 +168,16 @@ def main(argv=None) -> int:
         sys.stdout.flush()
 
     try:
-        outs = engine.generate(prompts, params, batch_size=opt["batch"], on_token=on_token)
-    except Exception as e:                                   # noqa: BLE001
+        if opt["profile"]:
+            from .profile import KernelProfile
+            with KernelProfile() as prof:
+                outs = engine.generate(prompts, params, batch_size=opt["batch"], on_token=on_token,
+                                       max_step_tokens=opt["step_tokens"])
+            prof.report(sys.stderr)
+        else:
+            outs = engine.generate(prompts, params, batch_size=opt["batch"], on_token=on_token,
+                                   max_step_tokens=opt["step_tokens"])
+    except Exception as e:                                   # noqa: BLE001 - a kernel's error flag included
         sys.stderr.write(f"error: {e}\n")
         return 1
     if opt["stream"] and single:

@@ -43,7 +43,7 @@ class Engine:
         self.rt = Runtime(parse_dtype(dtype), self.device, tensor_cores)
         page = ops.PAGE
         max_tokens = max(page, (int(max_tokens) + page - 1) // page * page)
-        limit = getattr(config, "max_position_embeddings", max_tokens)
+        limit = arch.build_spec(config, None).max_positions        # the architecture's own limit
         self.max_seq_len = min(int(max_seq_len or limit), limit, max_tokens)
         self.spec = arch.build_spec(config, self.max_seq_len)
         self.model = DecoderModel(self.spec, self.rt)
@@ -105,15 +105,20 @@ class Engine:
 
     # ------------------------------------------------------------------ generation
     def generate(self, prompts, params: GenParams | None = None, batch_size: int | None = None,
-                 on_token=None, return_results: bool = False, lookahead: bool = True):
+                 on_token=None, return_results: bool = False, lookahead: bool = True,
+                 max_step_tokens: int | None = None):
         """prompts: lists of token ids.  Returns the new tokens of each request (or
         GenerationResult objects with the finish reason).  lookahead: the next step is queued
         before the host has read the last tokens (same tokens either way; `on_token` then hears
-        of a token while the step after it is already running)."""
+        of a token while the step after it is already running).  max_step_tokens: the most
+        prompt tokens a step takes; longer prompts go through in portions (bounds the memory
+        of a step's activations; None: every prompt whole).  Raises RuntimeError if a kernel
+        reported an error during a batch (the tokens of that batch are then not returned)."""
         params = params or GenParams()
         backend = _Backend(self)
         backend.supports_lookahead = bool(lookahead)
-        results = run_generation(backend, prompts, params, batch_size, self.spec.stop_ids, on_token)
+        results = run_generation(backend, prompts, params, batch_size, self.spec.stop_ids, on_token,
+                                 max_step_tokens)
         return results if return_results else [r.tokens for r in results]
 
 
@@ -135,6 +140,9 @@ class _Backend:
 
     def free(self, slot):
         self.e.free(slot)
+
+    def check(self):
+        self.e.check_device_errors()
 
     def step(self, seqs):
         logits = self.e.step(seqs)

@@ -40,6 +40,9 @@ class GenerationBackend:
     def step(self, seqs) -> object: ...                     # logits for the wanted rows
     def sample(self, logits, slots, params) -> list: ...    # one token id per row, on the host
 
+    # Optional: check() raises if the device reported an error since the last call (a bounded wait
+    # that ran out, a token id outside the vocabulary); the loop calls it once per batch.
+
     # A backend that can run one step ahead of the host sets `supports_lookahead` and has:
     #   sample_async(logits, slots, params) -> handle     sampling started, tokens not yet read
     #   read(handle) -> list                               the tokens of that sampling, on the host
@@ -49,7 +52,12 @@ class GenerationBackend:
 
 
 def run_generation(backend: GenerationBackend, prompts, params, batch_size: int | None = None,
-                   stop_ids=(), on_token=None) -> list[GenerationResult]:
+                   stop_ids=(), on_token=None, max_step_tokens: int | None = None) -> list[GenerationResult]:
+    """max_step_tokens: the most prompt tokens one step takes (None: every prompt whole, in the
+    batch's first step).  With a limit, prompts are cut into portions, in request order: a
+    portion that does not end its prompt wants no logits; a request whose prompt is complete
+    decodes one token per step in the same steps in which later requests still bring portions;
+    a request that got no room in a step is left out of it.  The tokens are the same either way."""
     params.validate()
     prompts = [list(p) for p in prompts]
     for i, p in enumerate(prompts):
@@ -58,11 +66,14 @@ def run_generation(backend: GenerationBackend, prompts, params, batch_size: int 
         if len(p) > backend.max_seq_len:
             raise ValueError(f"request {i}: prompt of {len(p)} tokens exceeds the context of "
                              f"{backend.max_seq_len}")
+    if max_step_tokens is not None and max_step_tokens < 1:
+        raise ValueError("max_step_tokens must be at least 1")
     stop = set() if params.ignore_eos else set(stop_ids if params.stop_ids is None else params.stop_ids)
     results = [GenerationResult() for _ in prompts]
     if batch_size is None or batch_size < 1:
         batch_size = max(1, len(prompts))
     lookahead = bool(getattr(backend, "supports_lookahead", False))
+    check = getattr(backend, "check", None)
     for b0 in range(0, len(prompts), batch_size):
         batch = list(range(b0, min(len(prompts), b0 + batch_size)))
         slots: dict[int, int] = {}
@@ -74,8 +85,9 @@ def run_generation(backend: GenerationBackend, prompts, params, batch_size: int 
                     results[i].finish_reason = "length"
                 continue
             length = {i: len(prompts[i]) for i in batch}
+            fed = {i: 0 for i in batch}            # prompt tokens given to the step function so far
+            last = {}                              # request -> its newest token, to be fed next
             active = list(batch)
-            seqs = [SequenceStep(slots[i], prompts[i], [len(prompts[i]) - 1]) for i in active]
 
             def accept(i, tok) -> bool:
                 """Takes request i's next sampled token; True if the request goes on."""
@@ -98,14 +110,49 @@ def run_generation(backend: GenerationBackend, prompts, params, batch_size: int 
                 """Request i ends with its next token whatever that token is."""
                 return len(results[i].tokens) + 1 >= params.n_predict or length[i] + 1 > backend.max_seq_len
 
+            def next_step():
+                """The next step's sequences and the requests whose logits it yields, in order."""
+                room = max_step_tokens
+                seqs, sampled = [], []
+                for i in active:
+                    if fed[i] == len(prompts[i]):                      # decoding: its newest token
+                        seqs.append(SequenceStep(slots[i], [last[i]], [0]))
+                        sampled.append(i)
+                        continue
+                    n = len(prompts[i]) - fed[i]
+                    if room is not None:
+                        n = min(n, room)
+                        room -= n
+                    if n == 0:
+                        continue                                       # no room in this step
+                    ends = fed[i] + n == len(prompts[i])
+                    seqs.append(SequenceStep(slots[i], prompts[i][fed[i]:fed[i] + n], [n - 1] if ends else []))
+                    fed[i] += n
+                    if ends:
+                        sampled.append(i)
+                return seqs, sampled
+
+            def take(sampled, tokens):
+                """Accepts one sampled token per request of `sampled`; drops the requests that end."""
+                nonlocal active
+                ended = set()
+                for i, t in zip(sampled, tokens):
+                    if accept(i, int(t)):
+                        last[i] = int(t)
+                    else:
+                        ended.add(i)
+                active = [i for i in active if i not in ended]
+                return not ended
+
             while active:
+                seqs, sampled = next_step()
                 logits = backend.step(seqs)
-                act_slots = [slots[i] for i in active]
-                if not lookahead:
-                    tokens = [int(t) for t in backend.sample(logits, act_slots, params)]
-                    went_on = [accept(i, t) for i, t in zip(active, tokens)]
-                    seqs = [SequenceStep(slots[i], [t], [0]) for i, t, ok in zip(active, tokens, went_on) if ok]
-                    active = [i for i, ok in zip(active, went_on) if ok]
+                if not sampled:
+                    continue                                           # portions only: nothing to sample yet
+                act_slots = [slots[i] for i in sampled]
+                all_decoding = all(fed[i] == len(prompts[i]) for i in active)
+                if not (lookahead and all_decoding and sampled == active):
+                    take(sampled, backend.sample(logits, act_slots, params))
                     continue
                 # One step ahead: while the host still waits for the tokens of step k, step k + 1 of
                 # the same sequences is already queued, fed with those tokens where they lie.  It
@@ -117,17 +164,18 @@ def run_generation(backend: GenerationBackend, prompts, params, batch_size: int 
                     ahead = None
                     if not any(ends_by_count(i) for i in active):
                         ahead = backend.sample_async(backend.step_ahead(act_slots, pending), act_slots, params)
-                    tokens = [int(t) for t in backend.read(pending)]
-                    went_on = [accept(i, t) for i, t in zip(active, tokens)]
-                    if ahead is not None and all(went_on):
+                    rows = list(active)
+                    all_on = take(rows, backend.read(pending))
+                    if ahead is not None and all_on:
                         pending = ahead
                         continue
                     if ahead is not None:
-                        tokens = [int(t) for t in backend.read(ahead)]
-                        went_on = [ok and accept(i, t) for i, t, ok in zip(active, tokens, went_on)]
-                    seqs = [SequenceStep(slots[i], [t], [0]) for i, t, ok in zip(active, tokens, went_on) if ok]
-                    active = [i for i, ok in zip(active, went_on) if ok]
+                        tokens = backend.read(ahead)
+                        alive = [(i, t) for i, t in zip(rows, tokens) if i in active]
+                        take([i for i, _ in alive], [t for _, t in alive])
                     break
+            if check is not None:
+                check()                # device-side error flags, read once per batch; raises
         finally:
             for s in slots.values():
                 backend.free(s)

@@ -38,10 +38,15 @@ def _bucket(n: int) -> int:
 
 
 class _DecodeGraph:
+    """The decode step of one padded batch size and context class: its staging buffers, its
+    residual stream, and the forward pass as a list of captured graphs and, between them, the
+    stages that must run eagerly."""
+
     def __init__(self, bucket: int, buffers: StepBuffers):
         self.bucket = bucket
         self.buffers = buffers
-        self.graph = None
+        self.graph = None              # [(CUDAGraph | None, first stage, one past the last stage)]
+        self.x = None                  # the residual stream, [bucket, hidden] float32, kept between the pieces
         self.logits = None
         self.runs = 0
         self.n_kernels = 0
@@ -62,8 +67,8 @@ class Stepper:
                                for e in range(self.n_entries)]
         self._entry_group = [cache.group_of(e) if e in cache.entry_group else -1 for e in range(self.n_entries)]
         self._state_views = [state.views(e) for e in range(self.n_entries)]
-        parts_ok = all(getattr(p, "graph_safe", False) for layer in model.layers for p in layer.parts())
-        self.use_graphs = bool(use_graphs and parts_ok)
+        self._stages = model.stages()
+        self.use_graphs = bool(use_graphs and any(safe for safe, _, _ in self._stages))
         self._graphs: dict[tuple, _DecodeGraph] = {}      # (padded batch size, long context) -> graph
         self._eager_buffers: dict[tuple, StepBuffers] = {}
         self.launch_counter = None         # set by the bench to count kernel launches
@@ -91,6 +96,11 @@ class Stepper:
             if not (0 <= min(s.tokens) and max(s.tokens) < self.vocab):
                 bad = [t for t in s.tokens if not 0 <= int(t) < self.vocab]
                 raise StepError(f"sequence {i}: token id {bad[0]} is outside the vocabulary [0, {self.vocab})")
+            for w in s.want:
+                if not 0 <= int(w) < len(s.tokens):
+                    raise StepError(f"sequence {i}: wanted place {w} is outside its {len(s.tokens)} tokens")
+            if len(set(s.want)) != len(s.want):
+                raise StepError(f"sequence {i}: a place is wanted twice")
             if self.cache.length(s.slot) + len(s.tokens) > self.model.spec.max_positions:
                 raise StepError(f"sequence {i}: {self.cache.length(s.slot)} + {len(s.tokens)} tokens exceed the "
                                 f"{self.model.spec.max_positions} positions the model was built for")
@@ -160,27 +170,43 @@ class Stepper:
             ctx.token_ids[:B].copy_(device_tokens[:B])
         self.last_h2d_bytes = g.buffers.bytes()
         g.runs += 1
+        views = self._cache_views(ctx)
         if g.graph is None and g.runs == 1:
             # first use of this batch size: run directly (loads the kernels' modules)
-            all_logits = self.model.forward(ctx, self._cache_views(ctx), self._state_views)
+            all_logits = self.model.forward(ctx, views, self._state_views)
         else:
             if g.graph is None:
+                # Capture (nothing runs yet): every run of graph-safe stages becomes one graph; the
+                # stages between them run eagerly at every replay, on the same residual stream.
                 torch.cuda.synchronize()
-                graph = torch.cuda.CUDAGraph()
-                before = ops.LAUNCHES[0]
-                with torch.cuda.graph(graph):
-                    g.logits = self.model.forward(ctx, self._cache_views(ctx), self._state_views)
-                g.n_kernels = ops.LAUNCHES[0] - before
-                ops.LAUNCHES[0] = before          # captured, not launched
-                g.graph = graph
-            g.graph.replay()
+                g.x = self.rt.empty(g.bucket, self.model.spec.hidden_size, dtype=torch.float32)
+                pieces, g.n_kernels = [], 0
+                for safe, lo, hi in self._stages:
+                    if not safe:
+                        pieces.append((None, lo, hi))
+                        continue
+                    graph = torch.cuda.CUDAGraph()
+                    before = ops.LAUNCHES[0]
+                    with torch.cuda.graph(graph):
+                        out = self.model.run_stages(g.x, ctx, views, self._state_views, lo, hi)
+                    g.n_kernels += ops.LAUNCHES[0] - before
+                    ops.LAUNCHES[0] = before          # captured, not launched
+                    pieces.append((graph, lo, hi))
+                    if out is not None:
+                        g.logits = out                 # the captured head's output buffer
+                g.graph = pieces
+            logits_now = None
+            for graph, lo, hi in g.graph:
+                if graph is None:
+                    out = self.model.run_stages(g.x, ctx, views, self._state_views, lo, hi)
+                    if out is not None:
+                        logits_now = out
+                else:
+                    graph.replay()
             ops.LAUNCHES[0] += g.n_kernels
-            all_logits = g.logits
+            all_logits = logits_now if logits_now is not None else g.logits
         # rows wanted by the caller, in order
         rows = [b for b, s in enumerate(seqs) if s.want]
-        for b, s in enumerate(seqs):
-            if s.want and list(s.want) != [0]:
-                raise StepError(f"sequence {b}: a one-token step can only want place 0")
         if not rows:
             return None
         if rows == list(range(all_logits.shape[0])):

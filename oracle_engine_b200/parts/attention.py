@@ -18,7 +18,7 @@ import torch
 from ..csrc import ops
 from .linear import START_EARLY, TRIGGER_LATE, matmul_nt
 from .registry import MIXERS, Part
-from .spec import CacheNeed, TensorDecl
+from .spec import TensorDecl, attention_cache_need
 
 _NAMES = {"q": "self_attn.q_proj.weight", "k": "self_attn.k_proj.weight", "v": "self_attn.v_proj.weight",
           "o": "self_attn.o_proj.weight"}
@@ -39,6 +39,9 @@ class GQAAttention(Part):
         self.hd = int(self._need("head_dim"))
         if self.H % self.KVH:
             raise ValueError(f"gqa_attention: {self.H} heads are not a multiple of {self.KVH} KV heads")
+        if self.hd % 2 or not 2 <= self.hd <= ops.MAX_HEAD_DIM:
+            raise ValueError(f"gqa_attention: head_dim {self.hd} is outside what the attention kernels take "
+                             f"(even, 2..{ops.MAX_HEAD_DIM})")
         self.window = int(self.params.get("window", 0) or 0)
         self.scale = float(self.params.get("scale") or 1.0 / math.sqrt(self.hd))
         self.position = self.params.get("position")
@@ -56,7 +59,26 @@ class GQAAttention(Part):
         self.w_o = to(get(self.names["o"]))
 
     def cache_need(self):
-        return CacheNeed("window" if self.window else "full", self.KVH, self.hd, self.window)
+        return attention_cache_need(self.KVH, self.hd, self.window)
+
+    def weight_bytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.w_qkv, self.w_o) if t is not None)
+
+    def cache_bytes_per_query(self, context):
+        seen = min(context, self.window) if self.window else context
+        return seen * 2 * self.KVH * self.hd * (2 if self.rt.dtype == torch.bfloat16 else 4)
+
+    def flops(self, start, count):
+        products = 2.0 * self.D * (2 * self.H + 2 * self.KVH) * self.hd        # q, k, v and o projections
+        # positions seen by the tokens: sum over t = start + 1 .. start + count of t (or min(t, window))
+        first, last = start + 1, start + count
+        tri = lambda a, b: (a + b) * (b - a + 1) / 2.0 if b >= a else 0.0      # noqa: E731
+        if self.window:
+            w = self.window
+            seen = tri(first, min(last, w)) + w * max(0, last - max(first, w + 1) + 1)
+        else:
+            seen = tri(first, last)
+        return count * products + 4.0 * self.H * self.hd * seen                  # q.k and p.v
 
     def forward(self, h, residual, ctx, cache, state, owns_cache=True):
         T = h.shape[0]

@@ -19,21 +19,22 @@ def mixer_core(rt, out, qkv, cos, sin, cache, ctx, H, KVH, hd, window, scale, ow
         # One CTA per (sequence, KV head) whose warps split the keys: one launch for rotation, cache
         # write, attention and the merge, no scratch in global memory.
         if ops_tc.decode_uses_warps(ctx.n_seqs, getattr(ctx, "context_class", 0), hd, H, KVH):
-            ops_tc.attention_decode_warps(out, qkv, cos, sin, cache.storage, cache.tables, ctx, H, KVH, hd, window,
+            ops_tc.attention_decode_warps(out, qkv, cos, sin, cache.kv, cache.tables, ctx, H, KVH, hd, window,
                                           scale, owns_cache)
             return
         # One kernel when the batch alone fills the GPU (no split over the keys); for small
         # batches the split kernels plus a parallel merge are faster (measured).
-        if ops_tc.decode_fused_supported(hd, H, KVH) and ops_tc.decode_splits_for(ctx.n_seqs, KVH, cache.tables, getattr(ctx, "context_class", 0), hd) == 1:
-            ops_tc.attention_decode_fused(out, qkv, cos, sin, cache.storage, cache.tables, ctx, H, KVH, hd, window,
-                                          scale, owns_cache)
+        if ops_tc.decode_fused_supported(hd, H, KVH) and \
+                ops_tc.decode_splits_for(ctx.n_seqs, KVH, cache.tables, getattr(ctx, "context_class", 0), hd) == 1:
+            ops_tc.attention_decode_fused(out, qkv, cos, sin, cache.kv, cache.tables, ctx, H, KVH, hd, window,
+                                          scale, owns_cache, n_splits=1)
             return
     rope_and_cache(rt, qkv, cos, sin, cache, ctx, H, KVH, hd, owns_cache)
     attend(rt, out, qkv, cache, ctx, H, KVH, hd, window, scale)
 
 
 def rope_and_cache(rt, qkv, cos, sin, cache, ctx, H, KVH, hd, owns_cache) -> None:
-    ops.rope_kv_write(qkv, cos, sin, cache.storage if owns_cache else None, cache.tables, ctx.tok_seq,
+    ops.rope_kv_write(qkv, cos, sin, cache.kv if owns_cache else None, cache.tables, ctx.tok_seq,
                       ctx.tok_pos, H, KVH, hd, owns_cache)
 
 
@@ -41,6 +42,6 @@ def attend(rt, out, qkv, cache, ctx, H, KVH, hd, window, scale) -> None:
     if rt.dtype == torch.bfloat16 and rt.tensor_cores:
         from ..csrc import ops_tc
         if ops_tc.attention_supported(hd, H, KVH):
-            ops_tc.attention(out, qkv, cache.storage, cache.tables, ctx, H, KVH, hd, window, scale)
+            ops_tc.attention(out, qkv, cache.kv, cache.tables, ctx, H, KVH, hd, window, scale)
             return
-    ops.attn_paged(out, qkv, cache.storage, cache.tables, ctx.tok_seq, ctx.tok_pos, H, KVH, hd, window, scale)
+    ops.attn_paged(out, qkv, cache.kv, cache.tables, ctx.tok_seq, ctx.tok_pos, H, KVH, hd, window, scale)

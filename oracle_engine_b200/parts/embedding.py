@@ -16,6 +16,7 @@ from .spec import TensorDecl
 @EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Part):
     """params: vocab_size, hidden_size, name."""
+    graph_safe = True
 
     def __init__(self, params, prefix, runtime):
         super().__init__(params, prefix, runtime)
@@ -32,8 +33,9 @@ class TokenEmbedding(Part):
         self.table = self.rt.to_compute(get(self.name))
         self.err = torch.zeros(1, dtype=torch.int32, device=self.rt.device)
 
-    def forward(self, ids, n_tokens):
-        x = self.rt.empty(n_tokens, self.D, dtype=torch.float32)
+    def forward(self, ids, n_tokens, out=None):
+        """The residual stream [n_tokens, hidden] float32 (written into `out` if given)."""
+        x = self.rt.empty(n_tokens, self.D, dtype=torch.float32) if out is None else out
         ops.embed_gather(x, self.table, ids, self.err)
         return x
 
@@ -41,6 +43,7 @@ class TokenEmbedding(Part):
 @HEADS.register("lm_head")
 class LMHead(Part):
     """params: vocab_size, hidden_size, tied, name; `embedding` is handed in when tied."""
+    graph_safe = True
 
     def __init__(self, params, prefix, runtime):
         super().__init__(params, prefix, runtime)
@@ -56,6 +59,12 @@ class LMHead(Part):
 
     def load(self, get):
         self.weight = self.embedding.table if self.tied else self.rt.to_compute(get(self.name))
+
+    def weight_bytes(self):
+        return 0 if self.weight is None else self.weight.numel() * self.weight.element_size()
+
+    def flops(self, start, count):
+        return count * 2.0 * self.V * self.D
 
     def forward(self, xn):
         logits = self.rt.empty(xn.shape[0], self.V, dtype=torch.float32)

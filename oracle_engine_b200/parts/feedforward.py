@@ -41,6 +41,12 @@ class SwiGLU(Part):
             self.w_gu = torch.cat([gate, up], 0)
         self.w_down = to(get(self.names["down"]))
 
+    def weight_bytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.w_gu, self.w_down) if t is not None)
+
+    def flops(self, start, count):
+        return count * 2.0 * 3 * self.D * self.FF
+
     def forward(self, h, residual, ctx):
         T = h.shape[0]
         a = self.rt.empty(T, self.FF)

@@ -83,16 +83,73 @@ class DecoderModel:
         """Per schedule entry: dict name -> StateNeed of its mixer."""
         return [dict(self.layers[e.layer].mixer.state_need()) for e in self.schedule]
 
+    # ------------------------------------------------------------------ what a step costs
+    def step_bytes(self, contexts) -> int:
+        """Bytes a step has to read from memory: every weight it uses once, and for each of its
+        sequences (newest token at `contexts[i]` positions) the cache that every schedule entry's
+        mixer reads.  Summed from the parts; the roofline of a decode step."""
+        weights = sum(p.weight_bytes() for p in self._all_parts())
+        cache = 0
+        for e in self.schedule:
+            mixer = self.layers[e.layer].mixer
+            cache += sum(mixer.cache_bytes_per_query(int(c)) for c in contexts)
+        return int(weights + cache)
+
+    def step_flops(self, starts, counts, n_want) -> float:
+        """Floating-point operations of a step whose sequence i brings counts[i] tokens on top of
+        starts[i] cached ones, with the head applied to n_want rows."""
+        total = 0.0
+        for e in self.schedule:
+            for part in self.layers[e.layer].parts():
+                total += sum(part.flops(int(st), int(n)) for st, n in zip(starts, counts))
+        return total + self.head.flops(0, n_want)
+
     # ------------------------------------------------------------------ one step
     def forward(self, ctx, cache_views, state_views):
         """Runs the step's tokens through the schedule; returns float32 logits
         [n_want, vocab] at ctx.want_rows, or None if nothing is wanted."""
-        x = self.embedding.forward(ctx.token_ids, ctx.n_tokens)
-        for i, e in enumerate(self.schedule):
+        x = self.embed(ctx)
+        self.run_entries(x, ctx, cache_views, state_views, 0, len(self.schedule))
+        return self.logits(x, ctx)
+
+    # The forward pass in stages: stage 0 is the embedding, stage 1 + i schedule entry i, the last
+    # stage the final norm and head.  `stages()` groups them into runs that can (or cannot) be
+    # captured in a CUDA graph, so that one part that must run eagerly (a mixer that reads its state
+    # on the host, say) does not take the graphs away from every other layer.
+    def embed(self, ctx, out=None):
+        return self.embedding.forward(ctx.token_ids, ctx.n_tokens, out)
+
+    def run_entries(self, x, ctx, cache_views, state_views, lo: int, hi: int) -> None:
+        for i in range(lo, hi):
+            e = self.schedule[i]
             owner = i if e.cache_from is None else e.cache_from
             self.layers[e.layer].forward(x, ctx, cache_views[owner], state_views[i], e.cache_from is None)
+
+    def logits(self, x, ctx):
         if ctx.n_want == 0:
             return None
         xr = self.rt.empty(ctx.n_want, x.shape[1], dtype=torch.float32)
         ops.gather_rows_f32(xr, x, ctx.want_rows)
         return self.head.forward(self.final_norm.forward(xr))
+
+    def stages(self) -> list[tuple[bool, int, int]]:
+        """[(graph_safe, first stage, one past the last stage)]: maximal runs of stages that are all
+        safe to capture in a CUDA graph, or all not."""
+        ok = lambda parts: all(getattr(p, "graph_safe", False) for p in parts)          # noqa: E731
+        flags = [ok([self.embedding])] + [ok(self.layers[e.layer].parts()) for e in self.schedule] + \
+                [ok([self.final_norm, self.head])]
+        runs, lo = [], 0
+        for i in range(1, len(flags) + 1):
+            if i == len(flags) or flags[i] != flags[lo]:
+                runs.append((flags[lo], lo, i))
+                lo = i
+        return runs
+
+    def run_stages(self, x, ctx, cache_views, state_views, lo: int, hi: int):
+        """Runs stages lo .. hi - 1 on the residual stream `x` (stage 0 fills it); returns the
+        logits if the last stage is among them, else None."""
+        n = len(self.schedule)
+        if lo == 0:
+            self.embed(ctx, out=x)
+        self.run_entries(x, ctx, cache_views, state_views, max(lo, 1) - 1, min(hi, n + 1) - 1)
+        return self.logits(x, ctx) if hi == n + 2 else None

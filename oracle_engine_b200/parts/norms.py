@@ -26,6 +26,9 @@ class RMSNorm(Part):
     def load(self, get):
         self.weight = self.rt.to_f32(get(self.name))
 
+    def weight_bytes(self):
+        return 0 if self.weight is None else self.weight.numel() * self.weight.element_size()
+
     def forward(self, x):
         y = self.rt.empty(*x.shape)
         ops.rmsnorm(y, x, self.weight, self.eps)

@@ -10,6 +10,8 @@ Every part
     tensors() -> list[TensorDecl]        weights it reads (full names, shapes)
     load(get)                            takes them: get(name) -> CUDA tensor as stored
                                          (bfloat16, or float32 if the file holds 32-bit)
+    weight_bytes(), cache_bytes_per_query(context), flops(start, count)
+                                         what it reads and computes (for rooflines; default 0)
 
 Mixer  (MIXERS; e.g. attention)
     cache_need() -> CacheNeed | None     what it keeps per token in the paged cache
@@ -19,7 +21,8 @@ Mixer  (MIXERS; e.g. attention)
         residual [T, hidden] float32; the mixer ADDS its output into it
         ctx      StepContext (engine/batch.py): per-token sequence index and position,
                  per-sequence slot / start / length, the group's page tables
-        cache    the entry's storage [pages, 2, kv_heads, PAGE, head_dim] or None
+        cache    CacheView: the entry's tensors as its CacheNeed declared them (attention:
+                 cache.kv [pages, 2, kv_heads, PAGE, head_dim]) and the page tables
         state    dict name -> tensor [slots, *shape] (index rows with ctx.seq_slot)
         owns_cache  False when the entry reads another entry's cache (write nothing)
 
@@ -98,6 +101,21 @@ class Part:
 
     def state_need(self):
         return {}
+
+    # What a part costs, for rooflines (a bench sums these over the model; it needs no knowledge of
+    # the architecture).  Defaults: a part that streams no weights and computes next to nothing.
+    def weight_bytes(self) -> int:
+        """Bytes of weights the part reads in a step, whatever the number of tokens."""
+        return 0
+
+    def cache_bytes_per_query(self, context: int) -> int:
+        """Bytes of cache a mixer reads for ONE sequence whose newest token sees `context` positions."""
+        return 0
+
+    def flops(self, start: int, count: int) -> float:
+        """Floating-point operations for `count` tokens of one sequence at positions start ..
+        start + count - 1 (each sees the positions up to its own)."""
+        return 0.0
 
     def _need(self, key: str):
         try:

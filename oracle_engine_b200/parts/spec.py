@@ -54,12 +54,33 @@ class ScheduleEntry:
 
 @dataclass(frozen=True)
 class CacheNeed:
-    """What a mixer keeps per token: `kind` "full" (every key and value) or "window" (the
-    last `window` of them); entries with equal needs share one group of storage."""
+    """What a mixer keeps per token in the paged cache.
+
+    `tensors`: ((name, per-token shape), ...), one entry per tensor the mixer keeps.  A tensor
+    whose per-token shape is (a, ..., z) is stored per page as [a, ..., PAGE, z] (the page's
+    tokens run along the last but one axis, so that a token's innermost vector is contiguous
+    and a page of one outer index is one block).  Attention keeps one tensor "kv" of shape
+    (2, kv_heads, head_dim); a mixer that keeps one latent vector per token would declare
+    (("latent", (rank,)),), keys and values of different widths two tensors.
+    `kind`: "full" (every position) or "window" (the last `window` of them; older pages are
+    given back).  Entries with equal needs share one group of storage and page tables."""
     kind: str
-    kv_heads: int
-    head_dim: int
+    tensors: tuple
     window: int = 0
+
+    def elements_per_token(self) -> int:
+        n = 0
+        for _, shape in self.tensors:
+            e = 1
+            for d in shape:
+                e *= int(d)
+            n += e
+        return n
+
+
+def attention_cache_need(kv_heads: int, head_dim: int, window: int = 0) -> CacheNeed:
+    """Keys and values of grouped-query attention: one tensor "kv", per page [2, kv_heads, PAGE, head_dim]."""
+    return CacheNeed("window" if window else "full", (("kv", (2, int(kv_heads), int(head_dim))),), int(window))
 
 
 @dataclass(frozen=True)

@@ -50,6 +50,16 @@ TINY_E = dict(architectures=["LlamaForCausalLM"], vocab_size=389, hidden_size=20
 TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 5), "D": (TINY_D, 8), "E": (TINY_E, 11)}
 
 
+@pytest.fixture
+def pin():
+    """pin(prompt_kernel="mma", ...) pins kernel choices (csrc/ops_tc.py: knobs) until the test ends,
+    however it ends."""
+    import contextlib
+    from oracle_engine_b200.csrc import ops_tc
+    with contextlib.ExitStack() as stack:
+        yield lambda **kw: stack.enter_context(ops_tc.knobs(**kw))
+
+
 @pytest.fixture(scope="session")
 def model_dirs(tmp_path_factory):
     """Model folders (config.json + model.safetensors) of the tiny configurations,

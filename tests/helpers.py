@@ -117,6 +117,40 @@ def batched_steps(requests, prompt_lens, batch_size):
     return steps
 
 
+def piece_steps(requests, plans, batch_size=None, step0=0):
+    """Every request goes through in the pieces its plan lists (plans[i] sums to len(requests[i])):
+    in step s of a batch each live request brings its piece s, so one step may hold a long prompt
+    piece of one request beside single tokens of others; a request with fewer pieces ends earlier.
+    Every position is wanted."""
+    steps, k = [], step0
+    batch_size = batch_size or len(requests)
+    for b0 in range(0, len(requests), batch_size):
+        ids = list(range(b0, min(len(requests), b0 + batch_size)))
+        for i in ids:
+            assert sum(plans[i]) == len(requests[i]) and min(plans[i]) >= 1, (i, plans[i], len(requests[i]))
+        pos = {i: 0 for i in ids}
+        for s in range(max(len(plans[i]) for i in ids)):
+            live = [i for i in ids if s < len(plans[i])]
+            entries = []
+            for i in live:
+                n = plans[i][s]
+                entries.append({"id": f"r{i}", "tokens": requests[i][pos[i]:pos[i] + n], "want": list(range(n))})
+                pos[i] += n
+            steps.append({"step": k, "entries": entries, "end": [f"r{i}" for i in live if s == len(plans[i]) - 1]})
+            k += 1
+    return steps
+
+
+def cut(n, sizes):
+    """n as a list of pieces that cycle through `sizes` (the last one is what is left)."""
+    out, j = [], 0
+    while n > 0:
+        out.append(min(n, sizes[j % len(sizes)]))
+        n -= out[-1]
+        j += 1
+    return out
+
+
 def collect(steps, outputs, requests):
     """Reassembles per-request logits [len, vocab] from a trace's outputs."""
     vocab = next(iter(outputs.values())).shape[1]

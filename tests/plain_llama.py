@@ -1,8 +1,10 @@
 """Plain, slow implementation of the Llama dense decoder, used only by the tests.
 
 It rests on the formulas of the reference engine (Titouan935/oracle-engine), restated
-with whole-sequence tensor operations on the CPU: no cache, no batching, one function per
-part, and no code shared with the product package.  Two things the reference does not
+with whole-sequence float64 tensor operations on the CPU: no cache, no batching, one
+function per part, and no code shared with the product package.  (`PlainLlama(folder,
+device="cuda")` holds the same float64 tensors on the GPU; only the tests with sequences of
+thousands of tokens use it, to stay within minutes.)  Two things the reference does not
 have are taken from the model's config.json instead: the llama3 frequency scaling of the
 rotary angles, and a norm epsilon that is actually passed to the norm (the reference
 reads it, core/model.cpp:61, but calls rmsnorm with the default of core/ops.hpp:43).
@@ -107,7 +109,7 @@ def rope_rotate(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor
     x'_i = x_i cos - x_{i+half} sin;  x'_{i+half} = x_i sin + x_{i+half} cos
     (core/ops.cpp:467-474)."""
     half = x.shape[-1] // 2
-    ang = positions.to(torch.float64)[:, None] * inv_freq[None, :]      # [n, half]
+    ang = positions.to(device=x.device, dtype=torch.float64)[:, None] * inv_freq.to(x.device)[None, :]      # [n, half]
     cos = torch.cos(ang)[:, None, :].to(x.dtype)
     sin = torch.sin(ang)[:, None, :].to(x.dtype)
     x0, x1 = x[..., :half], x[..., half:]
@@ -132,8 +134,8 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     KVH = k.shape[1]
     group = H // KVH
     scale = 1.0 / math.sqrt(hd)
-    out = torch.zeros(n, H, hd, dtype=q.dtype)
-    pos = torch.arange(n)
+    out = torch.zeros(n, H, hd, dtype=q.dtype, device=q.device)
+    pos = torch.arange(n, device=q.device)
     allowed = pos[None, :] <= pos[:, None]
     if window is not None:
         allowed &= pos[None, :] > pos[:, None] - window
@@ -167,10 +169,11 @@ def lm_head(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 class PlainLlama:
     """config.json + model.safetensors -> logits of a whole sequence."""
 
-    def __init__(self, folder, dtype=torch.float64):
+    def __init__(self, folder, dtype=torch.float64, device="cpu"):
         self.cfg = read_config(folder)
         self.dtype = dtype
-        self.w = {k: (v.to(dtype) if v.dtype.is_floating_point else v)
+        self.device = device
+        self.w = {k: (v.to(dtype) if v.dtype.is_floating_point else v).to(device)
                   for k, v in read_safetensors(Path(folder) / "model.safetensors").items()}
         c = self.cfg
         self.n_layers = c["num_hidden_layers"]
@@ -186,9 +189,9 @@ class PlainLlama:
     def hidden(self, tokens) -> torch.Tensor:
         """Residual stream after the last layer, [n, D]  (core/model.cpp:361-474)."""
         w = self.w
-        tokens = torch.as_tensor(tokens, dtype=torch.int64)
+        tokens = torch.as_tensor(tokens, dtype=torch.int64).to(self.device)
         n = tokens.numel()
-        pos = torch.arange(n)
+        pos = torch.arange(n, device=self.device)
         x = embed(tokens, w["model.embed_tokens.weight"])
         for l in range(self.n_layers):
             p = f"model.layers.{l}."

@@ -7,10 +7,10 @@ import pytest
 
 from oracle_engine_b200.cache.kv_cache import KVCache, pages_for
 from oracle_engine_b200.cache.slots import CacheFull, PagePool, SlotAllocator
-from oracle_engine_b200.parts.spec import CacheNeed
+from oracle_engine_b200.parts.spec import CacheNeed, attention_cache_need
 
-FULL = CacheNeed("full", 2, 16)
-WIN = CacheNeed("window", 2, 16, 100)
+FULL = attention_cache_need(2, 16)
+WIN = attention_cache_need(2, 16, 100)
 
 
 def test_slot_allocator():
@@ -41,9 +41,9 @@ def test_page_pool():
 
 
 def test_groups_have_their_own_storage():
-    needs = [FULL, WIN, FULL, None, CacheNeed("full", 1, 32), WIN]
+    needs = [FULL, WIN, FULL, None, attention_cache_need(1, 32), WIN]
     c = KVCache(needs, max_tokens=640, max_seq_len=512, allocate=False, window_pool_tokens=256)
-    assert [g.need for g in c.groups] == [FULL, WIN, CacheNeed("full", 1, 32)]
+    assert [g.need for g in c.groups] == [FULL, WIN, attention_cache_need(1, 32)]
     assert [g.entries for g in c.groups] == [[0, 2], [1, 5], [4]]
     assert c.entry_group[2] == (0, 1) and 3 not in c.entry_group
     assert [g.pool.n for g in c.groups] == [10, 4, 10]

@@ -31,7 +31,7 @@ class Scripted:
 
     def step(self, seqs):
         self.steps.append([(self.owner[s.slot], list(s.tokens), list(s.want)) for s in seqs])
-        return [self.owner[s.slot] for s in seqs]
+        return [self.owner[s.slot] for s in seqs if s.want]       # one row of "logits" per wanted place
 
     def sample(self, logits, slots, params):
         assert [self.owner[s] for s in slots] == logits
@@ -158,6 +158,55 @@ def test_refusals_and_cleanup():
     be = Scripted({0: [1]}, n_slots=1)
     res = run_generation(be, [[1, 2]], GenParams.greedy(0))
     assert res[0].tokens == [] and be.steps == [] and be.free_slots == [0]
+
+
+def test_prompts_in_portions():
+    """A limit on the prompt tokens per step: portions in request order, logits wanted only where a
+    prompt ends, finished prompts decode beside later portions, a request without room waits."""
+    scripts = {0: [5, 6, 7], 1: [8, 9, 10], 2: [11, 99]}
+    prompts = [[1, 2, 3], [4, 5, 6, 7, 8], [9]]
+    be = Scripted(scripts, n_slots=3)
+    res = run_generation(be, prompts, GenParams.greedy(3), stop_ids=(99,), max_step_tokens=4)
+    assert [r.tokens for r in res] == [[5, 6, 7], [8, 9, 10], [11]]
+    assert be.steps == [
+        [(0, [1, 2, 3], [2]), (1, [4], [])],                       # request 2 got no room
+        [(0, [5], [0]), (1, [5, 6, 7, 8], [3])],                   # a decoded token beside a portion that ends
+        [(0, [6], [0]), (1, [8], [0]), (2, [9], [0])],             # request 2 starts two steps late
+        [(1, [9], [0]), (2, [11], [0])],                           # request 0 ended by its count
+    ]
+    # two-token portions, and a portion that is the prompt's last token alone
+    be = Scripted({0: [5, 6]}, n_slots=1)
+    res = run_generation(be, [[1, 2, 3, 4, 5]], GenParams.greedy(2), max_step_tokens=2)
+    assert be.steps == [[(0, [1, 2], [])], [(0, [3, 4], [])], [(0, [5], [0])], [(0, [5], [0])]]
+    assert res[0].tokens == [5, 6]
+    # the tokens do not depend on the limit, with and without the step ahead
+    scripts = {0: [5, 6, 99], 1: [7, 99], 2: [8, 9, 10, 11, 12, 13, 14], 3: [99], 4: [3, 4, 5, 6, 7, 8]}
+    prompts = [[1, 2, 3], [4], [1, 1, 1, 1, 1], [2, 2], [9]]
+    whole = run_generation(Scripted(scripts, n_slots=5), prompts, GenParams.greedy(5), stop_ids=(99,))
+    for limit in (1, 2, 3, 100):
+        for cls in (Scripted, ScriptedAhead):
+            got = run_generation(cls(scripts, n_slots=5), prompts, GenParams.greedy(5), stop_ids=(99,),
+                                 max_step_tokens=limit, batch_size=3)
+            assert [(r.tokens, r.finish_reason) for r in got] == [(r.tokens, r.finish_reason) for r in whole]
+    with pytest.raises(ValueError, match="max_step_tokens"):
+        run_generation(Scripted(scripts), prompts, GenParams.greedy(1), max_step_tokens=0)
+
+
+def test_device_errors_end_the_batch():
+    """The backend's check (error flags that kernels set) is read once per batch; what it raises
+    reaches the caller, and the slots still come back."""
+    class Flagged(Scripted):
+        checks = 0
+
+        def check(self):
+            self.checks += 1
+            if self.checks == 2:
+                raise RuntimeError("a bounded wait inside a kernel ran out")
+    be = Flagged({0: [1, 2], 1: [3, 4], 2: [5, 6]}, n_slots=1)
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        run_generation(be, [[1], [2], [3]], GenParams.greedy(2), batch_size=1)
+    assert be.checks == 2 and be.free_slots == [0]
+    assert [e[0] for e in be.events] == ["alloc", "free", "alloc", "free"]      # the third batch never started
 
 
 def test_reference_defaults():

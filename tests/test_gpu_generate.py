@@ -307,3 +307,45 @@ def test_real_widths_bfloat16_against_float32():
     clear = (top2[..., 0] - top2[..., 1]) > 4 * err
     assert clear.any()
     assert torch.equal(ref.argmax(-1)[clear], got.argmax(-1)[clear])
+
+
+def test_generate_raises_when_a_kernel_reports_an_error(model_dirs):
+    """A bounded wait that runs out inside a kernel during generation (made to, see the kernel test
+    of the same path) reaches the caller of Engine.generate as an error, not as tokens; the engine
+    generates as before afterwards."""
+    from oracle_engine_b200 import GenParams
+    from oracle_engine_b200.csrc import ops_tc
+    eng = _engine(model_dirs, "E", "bfloat16", max_tokens=2048)
+    prompts = [helpers.random_tokens(600, 389, 5)]
+    good = eng.generate(prompts, GenParams.greedy(3, ignore_eos=True))
+    with ops_tc.knobs(sm_count=1, gemm_waits=(2_000_000, 1)):           # five row tiles of the prompt on one CTA
+        with pytest.raises(RuntimeError, match="bounded wait"):
+            eng.generate(prompts, GenParams.greedy(3, ignore_eos=True))
+    assert eng.cache.slots.n_free == eng.cache.n_slots                  # the slots came back
+    assert eng.generate(prompts, GenParams.greedy(3, ignore_eos=True)) == good
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_checksum_of_the_references_own_bench(tmp_path, dtype):
+    """The engine's greedy tokens hash to the checksum that the reference's unmodified benchmark
+    program printed on the same model and prompt (tests/golden/bench_checksum_B0.json)."""
+    import json
+    import plain_llama
+    from test_plain import fnv1a
+    from oracle_engine_b200 import GenParams, LlamaConfig, write_model_folder
+    from oracle_engine_b200.engine.engine import Engine
+    g = json.loads((helpers.ROOT / "tests" / "golden" / "bench_checksum_B0.json").read_text())
+    write_model_folder(tmp_path / "m", LlamaConfig.from_dict(g["config"]), seed=g["seed"], std=g["std"])
+    eng = Engine.from_pretrained(str(tmp_path / "m"), dtype=dtype, max_tokens=512)
+    toks = eng.generate([g["prompt"]], GenParams.greedy(g["gen_tokens"], ignore_eos=True))[0]
+    if dtype == "float32":
+        assert f"{fnv1a(toks):016x}" == g["gen_checksum"]
+        return
+    # bfloat16: the same tokens up to a near tie, if there is one
+    want = plain_llama.generate(plain_llama.PlainLlama(tmp_path / "m"), g["prompt"], g["gen_tokens"])
+    k = next((i for i, (a, b) in enumerate(zip(toks, want)) if a != b), None)
+    if k is not None:
+        lg = plain_llama.PlainLlama(tmp_path / "m").logits(g["prompt"] + want[:k])[-1]
+        assert float(lg[want[k]] - lg[toks[k]]) < 0.1, f"token {k}: {toks[k]} vs {want[k]}"
+        assert k > 8

@@ -156,8 +156,7 @@ def test_gemm_tcgen05(M, N, K):
 def test_gemm_pair(M, N, K, max_tile):
     """The two-SM kernel: row and column edges, both halves of the weight tile, all epilogues."""
     from oracle_engine_b200.csrc import ops_tc
-    ops_tc.PAIR_MAX_TILE[0] = max_tile
-    try:
+    with ops_tc.knobs(pair_max_tile=max_tile):
         a, w = _rand(M, K, dtype=torch.bfloat16, scale=0.5, seed=1), _rand(N, K, dtype=torch.bfloat16, scale=0.5, seed=2)
         want = a.double() @ w.double().T
         tol = 2e-6 * K + 1e-5
@@ -185,8 +184,6 @@ def test_gemm_pair(M, N, K, max_tile):
         ops_tc.gemm(one, a, w, kernel="tcgen05", split_k=False)
         assert torch.equal(one, out32)
         assert ops_tc.device_error() == 0
-    finally:
-        ops_tc.PAIR_MAX_TILE[0] = 0
 
 
 @pytest.mark.parametrize("M,N,K", [(300, 512, 1664), (2048, 3072, 512), (1100, 5000, 328)])
@@ -195,8 +192,7 @@ def test_gemm_stream_k(M, N, K):
     added up at a time), whole tiles after the shared ones, row, column and K edges; all
     epilogues; the same bits every time and whichever CTA adds up."""
     from oracle_engine_b200.csrc import ops_tc
-    ops_tc.force_schedule(0, 1)
-    try:
+    with ops_tc.knobs(gemm_schedule=(0, 1, -1, -1)):
         a, w = _rand(M, K, dtype=torch.bfloat16, scale=0.5, seed=1), _rand(N, K, dtype=torch.bfloat16, scale=0.5, seed=2)
         want = a.double() @ w.double().T
         tol = 2e-6 * K + 1e-5
@@ -220,13 +216,11 @@ def test_gemm_stream_k(M, N, K):
         ref = gate / (1 + torch.exp(-gate)) * up
         assert (act.double() - ref).abs().max() < 0.005 * ref.abs().max() + 10 * tol
         # whole tiles give the same sums up to the order of the pieces
-        ops_tc.force_schedule(0, 0)
-        whole = torch.empty(M, N, device=DEV)
-        ops_tc.gemm(whole, a, w, kernel="tcgen05")
+        with ops_tc.knobs(gemm_schedule=(0, 0, -1, -1)):
+            whole = torch.empty(M, N, device=DEV)
+            ops_tc.gemm(whole, a, w, kernel="tcgen05")
         assert (whole.double() - out32.double()).abs().max() < tol
         assert ops_tc.device_error() == 0
-    finally:
-        ops_tc.force_schedule(0, -1)
 
 
 @pytest.mark.parametrize("M,N,K", [(64, 3072, 3072), (17, 640, 1024), (100, 520, 4096), (128, 264, 8192), (33, 1000, 328)])
@@ -236,8 +230,7 @@ def test_gemm_few_tokens_split_k(M, N, K, cluster):
     (2 to 8 CTAs, shares of rows that are not equal, a last weight tile that is partly empty)
     or through the workspace; all epilogues; the same bits every time."""
     from oracle_engine_b200.csrc import ops_tc
-    ops_tc.force_schedule(0, -1, cluster, 0)
-    try:
+    with ops_tc.knobs(gemm_schedule=(0, -1, cluster, 0)):
         a, w = _rand(M, K, dtype=torch.bfloat16, scale=0.5, seed=1), _rand(N, K, dtype=torch.bfloat16, scale=0.5, seed=2)
         want = a.double() @ w.double().T
         tol = 2e-6 * K + 1e-5
@@ -261,8 +254,6 @@ def test_gemm_few_tokens_split_k(M, N, K, cluster):
         ref = gate / (1 + torch.exp(-gate)) * up
         assert (act.double() - ref).abs().max() < 0.005 * ref.abs().max() + 10 * tol
         assert ops_tc.device_error() == 0
-    finally:
-        ops_tc.force_schedule()
 
 
 def _paged(k, v, lens, dtype, extra_pages=3, seed=0):
@@ -302,13 +293,13 @@ def _attn_case(H, KVH, hd, lens, qlens, dtype, seed):
 @pytest.mark.parametrize("H,KVH,hd,window", [(4, 2, 16, 0), (6, 2, 32, 0), (5, 1, 48, 0), (8, 8, 64, 0),
                                              (24, 8, 128, 0), (6, 3, 32, 70), (4, 4, 16, 5), (10, 2, 64, 70),
                                              (3, 1, 128, 129)])
-def test_attention_kernels(dtype, kernel, H, KVH, hd, window):
+def test_attention_kernels(pin, dtype, kernel, H, KVH, hd, window):
     """Ragged prompts and decoded tokens over a shuffled paged cache with stale pages."""
     from types import SimpleNamespace
     from oracle_engine_b200.csrc import ops, ops_tc
     if kernel == "tcgen05" and hd not in ops_tc.TCGEN05_ATTENTION_HEAD_DIMS:
         pytest.skip("the tcgen05 prompt kernel is built for head_dim 64 and 128")
-    ops_tc.PROMPT_KERNEL[0] = "tcgen05" if kernel == "tcgen05" else "mma"
+    pin(prompt_kernel="tcgen05" if kernel == "tcgen05" else "mma")
     lens = [1, 64, 65, 200, 130, 17]
     g = torch.Generator().manual_seed(H * 100 + hd)
     k = [torch.randn(n, KVH, hd, generator=g) for n in lens]
@@ -351,19 +342,18 @@ def test_attention_kernels(dtype, kernel, H, KVH, hd, window):
         got = out[:T - 1].double().cpu()
         err = (got - torch.stack(want)).abs().max().item()
         assert err < tol, f"{kernel} {mode}: {err}"
-    ops_tc.PROMPT_KERNEL[0] = "tcgen05"
     assert ops_tc.device_error() == 0
 
 
 @pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
 @pytest.mark.parametrize("hd,step", [(64, 12.0), (128, 4.0), (128, -6.0)])
-def test_attention_moving_maximum(kernel, hd, step):
+def test_attention_moving_maximum(pin, kernel, hd, step):
     """Scores that climb (or fall) by `step` from one block of 64 keys to the next: the running maximum
     moves at every block (12), at every second or third block (4: in between, probabilities above 1
     are summed against an older maximum), or never (falling: the first block outweighs all later ones)."""
     from types import SimpleNamespace
     from oracle_engine_b200.csrc import ops_tc
-    ops_tc.PROMPT_KERNEL[0] = kernel
+    pin(prompt_kernel=kernel)
     H, KVH, n = 4, 2, 700
     g = torch.Generator().manual_seed(int(hd + step))
     u = torch.randn(hd, generator=g)
@@ -386,7 +376,6 @@ def test_attention_moving_maximum(kernel, hd, step):
                           max_qlen=n, all_decode=False)
     ops_tc.attention(out, qbuf, cache, tables, ctx, H, KVH, hd, 0, 1 / math.sqrt(hd))
     err = (out.double().cpu() - want.reshape(n, -1)).abs().max().item()
-    ops_tc.PROMPT_KERNEL[0] = "tcgen05"
     assert err < 2.5e-2, err
     assert ops_tc.device_error() == 0
 
@@ -563,3 +552,31 @@ def test_attention_decode_fused(H, KVH, hd, window, rotate, kernel):
     decode(out2, q_only, cos if rotate else None, sin if rotate else None, cache, tab, ctx, H, KVH,
            hd, window, 1 / math.sqrt(hd), False)
     assert torch.equal(out2[:B], out[:B])
+
+
+def test_gemm_wait_that_runs_out_returns_and_reports():
+    """A wait inside the tensor-core product that nothing ends: with the epilogues told to withhold
+    their accumulators and a limit of 2 ms, the waits for each CTA's third tile run out; the
+    kernel must come back by itself, report the wait's code through oe_gemm_tc_error(), leave the
+    tensor memory free, and the next ordinary product must be right."""
+    import time
+    from oracle_engine_b200.csrc import ops_tc
+    M, N, K = 300, 2048, 256
+    a, w = _rand(M, K, dtype=torch.bfloat16, scale=0.5, seed=1), _rand(N, K, dtype=torch.bfloat16, scale=0.5, seed=2)
+    want = a.double() @ w.double().T
+    out = torch.zeros(M, N, device=DEV)
+    assert ops_tc.device_error() == 0
+    with ops_tc.knobs(sm_count=4, gemm_waits=(2_000_000, 1)):          # 24 tiles on 4 CTAs: 6 each
+        t0 = time.time()
+        ops_tc.gemm(out, a, w, kernel="tcgen05", split_k=False)
+        torch.cuda.synchronize()
+        took = time.time() - t0
+    assert took < 1.0, f"the kernel took {took:.2f} s to give up"
+    # the MMA role's wait for an accumulator (4) or the epilogue's wait for the next sums (3), whichever ran out first
+    assert ops_tc.device_error() in (3, 4)
+    assert ops_tc.device_error() == 0                                   # reading the flag clears it
+    for _ in range(2):                                                  # tensor memory and barriers are as new
+        good = torch.zeros(M, N, device=DEV)
+        ops_tc.gemm(good, a, w, kernel="tcgen05", split_k=False)
+        assert (good.double() - want).abs().max() < 2e-6 * K + 1e-5
+    assert ops_tc.device_error() == 0

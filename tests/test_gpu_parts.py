@@ -104,7 +104,7 @@ def test_attention_mixer_alone(dtype, window, rotary):
                                          "position": rope if rotary else None, "window": window}, "m.", rt)
     w = _weights(mixer, 5)
     need = mixer.cache_need()
-    assert need.kind == ("window" if window else "full") and need.kv_heads == KVH and need.head_dim == hd
+    assert need.kind == ("window" if window else "full") and need.tensors == (("kv", (2, KVH, hd)),)
     cache = KVCache([need], 512, 256, dtype, DEV)
     lens = [70, 9]
     g = torch.Generator().manual_seed(6)
@@ -280,7 +280,8 @@ def test_toy_architecture_with_state_window_repeat_and_shared_cache(toy_register
     # entries 1 (state only) and 4 (reads entry 0) own none
     assert [g.entries for g in eng.cache.groups] == [[0, 3], [2]]
     assert [g.need.kind for g in eng.cache.groups] == ["full", "window"]
-    assert not eng.stepper.use_graphs                       # the toy mixer is not graph safe
+    # the toy mixer is not graph safe: the stages before and after it are captured, it runs between them
+    assert eng.stepper.use_graphs and eng.model.stages() == [(True, 0, 2), (False, 2, 3), (True, 3, 7)]
     w = pl.read_safetensors(tmp_path / "toy" / "model.safetensors")
     requests = [helpers.random_tokens(n, cfg.vocab_size, 70 + i) for i, n in enumerate([1, 30, 150, 65, 90])]
     runs = {"whole": helpers.whole_steps(requests), "tail": helpers.tail_steps(requests, 32),
@@ -291,6 +292,8 @@ def test_toy_architecture_with_state_window_repeat_and_shared_cache(toy_register
         got[name] = helpers.collect(steps, out, requests)
         eng.cache.check()
         assert eng.cache.slots.n_free == eng.cache.n_slots
+    captured = [g.graph for g in eng.stepper._graphs.values() if g.graph is not None]
+    assert captured and all([piece[0] is not None for piece in pieces] == [True, False, True] for pieces in captured)
     tol = 2e-4 if dtype == "float32" else 6e-2
     for i, toks in enumerate(requests):
         want = _toy_plain(w, cfg, toks).numpy()

@@ -81,6 +81,36 @@ def test_llama3_scaling_regions():
     assert torch.equal(pl.rope_inv_freq(32, 500000.0, {"rope_type": "default"}), base)
 
 
+def test_llama3_scaling_pinned_by_literals_and_continuity():
+    """The llama3 frequency scaling, which the reference does not have, pinned by things that are not
+    the formula typed again: values worked out apart (40-digit decimal arithmetic) for the benchmark
+    model's constants, continuity at both boundaries, and monotony.  The plain function and the
+    product's (parts/positions.py) must both give them.
+
+    By hand for i = 32: f = 500000^(-1/2) = 1/707.10678 = 1.41421356e-3, wavelength 2 pi / f = 4442.88,
+    between 8192/4 and 8192/1, so s = (8192 / 4442.88 - 1) / 3 = 0.281283 and
+    f' = f ((1 - s) / 32 + s) = 1.41421356e-3 x 0.3037428 = 4.295568e-4."""
+    from oracle_engine_b200.parts.positions import rotary_inv_freq
+    sc = {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+          "original_max_position_embeddings": 8192}
+    table = {0: 1.0, 28: 3.211445994753e-3, 29: 2.118406996780e-3, 32: 4.295567965594e-4,
+             34: 9.708287802628e-5, 35: 2.389053088491e-5, 63: 7.672314972286e-8}
+    for fn in (pl.rope_inv_freq, rotary_inv_freq):
+        got = fn(128, 500000.0, sc)
+        for i, want in table.items():
+            assert abs(float(got[i]) / want - 1.0) < 1e-11, (fn.__module__, i, float(got[i]), want)
+        assert all(float(got[i]) > float(got[i + 1]) for i in range(63))                # strictly falling
+        # Continuity: a frequency whose wavelength is exactly orig / high keeps its value from both
+        # sides, one at orig / low is divided by the factor from both sides.  theta and head_dim are
+        # chosen so that f_1 = theta^(-1/2) has exactly that wavelength (up to rounding).
+        for bound, ratio in ((8192.0 / 4.0, 1.0), (8192.0 / 1.0, 1.0 / 32.0)):
+            f_edge = 2.0 * math.pi / bound
+            for nudge in (1.0 - 1e-9, 1.0 + 1e-9):
+                theta = (1.0 / (f_edge * nudge)) ** 2                                   # head_dim 4: f_1 = theta^(-2/4)
+                got2 = fn(4, theta, sc)
+                assert abs(float(got2[1]) / (f_edge * nudge * ratio) - 1.0) < 1e-7, (bound, nudge)
+
+
 def test_attention_is_causal_grouped_and_windowed():
     torch.manual_seed(0)
     n, H, KVH, hd = 9, 6, 2, 4
@@ -145,3 +175,25 @@ def test_generate_stops_without_emitting(plain_models):
     out = pl.generate(m, [3, 4, 5], 5)
     assert len(out) == 5
     assert pl.generate(m, [3, 4, 5], 5, stop_ids=(out[2],)) == out[:out.index(out[2])]
+
+
+def fnv1a(tokens) -> int:
+    """The checksum the reference's bench prints for its greedy tokens (benchmark/bench_engine.cpp:233-242)."""
+    h = 1469598103934665603
+    for t in tokens:
+        h ^= int(t) & 0xFFFFFFFF
+        h = (h * 1099511628211) & ((1 << 64) - 1)
+    return h
+
+
+def test_greedy_tokens_hash_to_the_checksum_of_the_references_own_bench(tmp_path):
+    """tests/golden/bench_checksum_B0.json holds the checksum that the reference's unmodified benchmark
+    program printed for 64 greedy tokens after its 128-token prompt, on this model (made by
+    tests/golden/make_bench_checksum.py); the plain model's greedy generation gives the same tokens."""
+    import json
+    from oracle_engine_b200 import LlamaConfig, write_model_folder
+    g = json.loads((GOLDEN / "bench_checksum_B0.json").read_text())
+    write_model_folder(tmp_path / "m", LlamaConfig.from_dict(g["config"]), seed=g["seed"], std=g["std"])
+    toks = pl.generate(pl.PlainLlama(tmp_path / "m"), g["prompt"], g["gen_tokens"])
+    assert len(set(toks)) > 20
+    assert f"{fnv1a(toks):016x}" == g["gen_checksum"]

@@ -399,7 +399,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // the first stages' weight tiles are requested before pdl_wait(), the activation
         // tiles after it.
         if (lane == 0) {
-            int it = 0;                                         // k-blocks issued so far, over all work items
+            int s = 0;                                          // the ring's next stage, over all work items
+            uint32_t phase = 0;                                 // and how often the ring has wrapped (mod 2)
             bool waited = false, ok = true;
             ItemIter iter = make_iter(g);
             Item item;
@@ -425,18 +426,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             else tma_load_2d(a_dst + h * A_TILE_BYTES, &map_a, &ctl->full[j], (kb0 + j) * kb_elems + h * BLOCK_K, tile_a * BLOCK_M);
                         }
                     }
-                    it = first;
+                    s = first == g.stages ? 0 : first;          // the ring's next stage and its phase
+                    phase = first == g.stages ? 1u : 0u;
                 }
-                for (; i < n_kb; i++, it++) {
-                    const int s = it % g.stages;
-                    const uint32_t phase = (uint32_t)(it / g.stages) & 1u;
+                // The loop of one k-block is short on purpose (no division, addresses carried along):
+                // the thread that runs it is one of two whose rate bounds what a CTA streams.
+                const int row_a = tile_a * BLOCK_M, row_b = tile_b * g.n_tile;
+                int col = (kb0 + i) * kb_elems;
+                for (; i < n_kb; i++, col += kb_elems) {
                     if (!mbar_wait(&ctl->empty[s], phase ^ 1u, ctl, 1)) { ok = false; break; }
                     uint8_t* a_dst = smem + (size_t)s * stage_bytes;
                     mbar_expect_tx(&ctl->full[s], stage_tx);
-                    for (int h = 0; h < g.atoms; h++) {
-                        tma_load_2d(a_dst + h * A_TILE_BYTES, &map_a, &ctl->full[s], (kb0 + i) * kb_elems + h * BLOCK_K, tile_a * BLOCK_M);
-                        tma_load_2d(a_dst + b_off + h * b_atom_bytes, &map_b, &ctl->full[s], (kb0 + i) * kb_elems + h * BLOCK_K, tile_b * g.n_tile);
+                    tma_load_2d(a_dst, &map_a, &ctl->full[s], col, row_a);
+                    tma_load_2d(a_dst + b_off, &map_b, &ctl->full[s], col, row_b);
+                    if (g.atoms == 2) {
+                        tma_load_2d(a_dst + A_TILE_BYTES, &map_a, &ctl->full[s], col + BLOCK_K, row_a);
+                        tma_load_2d(a_dst + b_off + b_atom_bytes, &map_b, &ctl->full[s], col + BLOCK_K, row_b);
                     }
+                    if (++s == g.stages) { s = 0; phase ^= 1u; }
                 }
             }
         }
@@ -444,7 +451,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ---------------- MMA issue ----------------
         if (lane == 0) {
             const uint32_t idesc = umma_idesc(BLOCK_M, g.n_tile);
-            int it = 0, lt = 0;
+            int lt = 0;
+            int s = 0;                                          // the ring's next stage and its phase, over all work items
+            uint32_t phase = 0;
+            // Operand descriptors differ from stage to stage and from one 16-deep step to the next only
+            // in their address field (bytes / 16): they are carried along by additions.
+            const uint64_t desc0 = umma_desc(smem_u32(smem));
+            const uint64_t stage_step = (uint64_t)(stage_bytes >> 4), b_step = (uint64_t)(b_off >> 4);
+            const uint64_t a_atom = (uint64_t)(A_TILE_BYTES >> 4), b_atom = (uint64_t)(b_atom_bytes >> 4);
             bool ok = true;
             ItemIter iter = make_iter(g);
             Item item;
@@ -455,21 +469,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (!mbar_wait(&ctl->tmem_empty[buf], ((uint32_t)(lt >> 1) & 1u) ^ 1u, ctl, 4)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmem_d = tmem_base + (uint32_t)(buf * g.n_tile);
-                for (int i = 0; i < n_kb; i++, it++) {
-                    const int s = it % g.stages;
-                    const uint32_t phase = (uint32_t)(it / g.stages) & 1u;
+                for (int i = 0; i < n_kb; i++) {
                     if (!mbar_wait(&ctl->full[s], phase, ctl, 2)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    for (int h = 0; h < g.atoms; h++) {
-                        const uint32_t a_addr = smem_u32(smem + (size_t)s * stage_bytes) + (uint32_t)(h * A_TILE_BYTES);
-                        const uint32_t b_addr = smem_u32(smem + (size_t)s * stage_bytes) + (uint32_t)(b_off + h * b_atom_bytes);
+                    const uint64_t a_desc = desc0 + (uint64_t)s * stage_step, b_desc = a_desc + b_step;
+                    umma_bf16(tmem_d, a_desc, b_desc, idesc, i > 0 ? 1u : 0u);
 #pragma unroll
-                        for (int k = 0; k < BLOCK_K / UMMA_K; k++) {
-                            umma_bf16(tmem_d, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc,
-                                      (i > 0 || h > 0 || k > 0) ? 1u : 0u);
-                        }
+                    for (int k = 1; k < BLOCK_K / UMMA_K; k++)
+                        umma_bf16(tmem_d, a_desc + (uint64_t)(k * UMMA_K * 2 >> 4), b_desc + (uint64_t)(k * UMMA_K * 2 >> 4), idesc, 1u);
+                    if (g.atoms == 2) {
+#pragma unroll
+                        for (int k = 0; k < BLOCK_K / UMMA_K; k++)
+                            umma_bf16(tmem_d, a_desc + a_atom + (uint64_t)(k * UMMA_K * 2 >> 4),
+                                      b_desc + b_atom + (uint64_t)(k * UMMA_K * 2 >> 4), idesc, 1u);
                     }
                     umma_commit(&ctl->empty[s]);          // frees the stage when these MMAs have read it
+                    if (++s == g.stages) { s = 0; phase ^= 1u; }
                 }
                 umma_commit(&ctl->tmem_full[buf]);        // this accumulator is complete
             }
@@ -726,7 +741,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // host side
 // ---------------------------------------------------------------------------------------
 PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
-inline long long kb_ns(int n_tile) { return n_tile <= 128 ? 280 : n_tile <= 192 ? 417 : 482; }   // measured, one k-block
+// One k-block of a 128 x n_tile tile, measured with all SMs busy (2,048 x 16384 x 3072: 222, 170, 149 us at
+// 128, 192, 256 columns): the wide tile is bounded by the tensor cores at the clock the power limit
+// leaves, the narrow one by what the L2 delivers (32 KB per k-block and SM).
+inline long long kb_ns(int n_tile) { return n_tile <= 128 ? 330 : n_tile <= 192 ? 353 : 444; }
 int g_force_tile = 0;       // measurements only: tile width and schedule for many tokens (0, -1: chosen here)
 int g_force_streamk = -1;
 int g_force_narrow = -1;      // 48..128 tokens: 1 narrow tiles, 0 swap-AB with split K, -1 by the shape
@@ -883,10 +901,9 @@ int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, 
         if (N < 256) {
             g.n_tile = ((N + 15) / 16) * 16;
         } else {
-            // The tile width with the shortest rounds of CTAs (one CTA per SM).  A k-block takes
-            // about 280, 417 and 482 ns at 128, 192 and 256 columns (measured; a wide instruction
-            // costs little more than a narrow one); over 13 token counts from 256 to 8,192 and this
-            // model's four shapes that choice was within 1% of the best of the three.
+            // The tile width with the shortest rounds of CTAs (one CTA per SM) at the measured time of
+            // a k-block (kb_ns); at 2,048 and 8,192 tokens and this model's four shapes that choice is
+            // the best of the three or within 1 % of it.
             const int tiles_m = (M + BLOCK_M - 1) / BLOCK_M;
             long long best = -1;
             for (int nt = 256; nt >= 128; nt -= 64) {
@@ -910,7 +927,7 @@ int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, 
             2LL * sm_count * 256 * BLOCK_M * 4 <= ws_bytes) {
             const long long tiles_now = (long long)g.tiles_a * ((N + g.n_tile - 1) / g.n_tile);
             const double whole = (double)((tiles_now + sm_count - 1) / sm_count) * (double)kb_ns(g.n_tile);
-            const double shared_k = (double)tiles256 / (double)sm_count * 482.0;
+            const double shared_k = (double)tiles256 / (double)sm_count * (double)kb_ns(256);
             const long long rounds = tiles256 / sm_count, rest = tiles256 % sm_count;
             if (sk == 1 ? rest > 0 : (rounds >= 1 && rest > 0 && shared_k < 0.9 * whole)) {
                 // the shared part: the remainder, plus one full round if the remainder alone would
@@ -919,7 +936,7 @@ int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, 
                 if (rounds >= 2 && rest * 4 < sm_count) shared += sm_count;
                 const long long run = shared * n_kb / sm_count;
                 const long long pieces = run > 0 ? (n_kb + run - 1) / run + 1 : 1000;
-                if (sk == 1 ? run >= 1 : (run >= 8 && (double)pieces * 10000.0 <= (double)n_kb * 482.0)) {
+                if (sk == 1 ? run >= 1 : (run >= 8 && (double)pieces * 10000.0 <= (double)n_kb * (double)kb_ns(256))) {
                     g.streamk = 1;
                     g.sk_tiles = (int)shared;
                     g.n_tile = 256;

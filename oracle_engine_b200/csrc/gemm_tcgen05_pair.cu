@@ -250,21 +250,22 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // ---------------- TMA producer (both CTAs) ----------------
         if (lane == 0) {
             pdl_wait();                                    // the activations come from the kernel before
-            int it = 0;
+            int s = 0;                                     // the ring's next stage and its phase, over all tiles
+            uint32_t phase = 0;
             bool ok = true;
             for (int w = cluster_id; w < n_work && ok; w += n_clusters) {
                 const int tile_n = w / g.tiles_m, tile_m = w % g.tiles_m;
                 const int a_row = tile_m * (2 * BLOCK_M) + (int)rank * BLOCK_M;
                 const int b_row = tile_n * g.n_tile + (int)rank * b_half_rows;
-                for (int i = 0; i < n_kb; i++, it++) {
-                    const int s = it % g.stages;
-                    const uint32_t phase = (uint32_t)(it / g.stages) & 1u;
+                // a short loop per k-block (no division, addresses carried along): see gemm_tcgen05.cu
+                for (int i = 0, col = 0; i < n_kb; i++, col += BLOCK_K) {
                     if (!mbar_wait(&ctl->empty[s], phase ^ 1u, ctl, 1)) { ok = false; break; }
                     uint8_t* a_dst = smem + (size_t)s * stage_bytes;
                     if (leader) mbar_expect_tx(&ctl->full[s], (uint32_t)(2 * (A_TILE_BYTES + b_bytes)));
                     const uint32_t bar = in_leader(&ctl->full[s]);
-                    tma_load_pair(a_dst, &map_a, bar, i * BLOCK_K, a_row);
-                    tma_load_pair(a_dst + A_TILE_BYTES, &map_b, bar, i * BLOCK_K, b_row);
+                    tma_load_pair(a_dst, &map_a, bar, col, a_row);
+                    tma_load_pair(a_dst + A_TILE_BYTES, &map_b, bar, col, b_row);
+                    if (++s == g.stages) { s = 0; phase ^= 1u; }
                 }
             }
         }
@@ -272,7 +273,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // ---------------- MMA issue (leader only) ----------------
         if (lane == 0 && leader) {
             const uint32_t idesc = umma_idesc(2 * BLOCK_M, g.n_tile);
-            int it = 0, lt = 0;
+            int lt = 0;
+            int s = 0;
+            uint32_t phase = 0;
+            // descriptors differ between stages and 16-deep steps only in their address field (bytes / 16)
+            const uint64_t desc0 = umma_desc(smem_u32(smem));
+            const uint64_t stage_step = (uint64_t)(stage_bytes >> 4), b_step = (uint64_t)(A_TILE_BYTES >> 4);
             bool ok = true;
             for (int w = cluster_id; w < n_work && ok; w += n_clusters, lt++) {
                 const int buf = lt & 1;
@@ -280,17 +286,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (!mbar_wait(&ctl->tmem_empty[buf], ((uint32_t)(lt >> 1) & 1u) ^ 1u, ctl, 4)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmem_d = tmem_base + (uint32_t)(buf * g.n_tile);
-                for (int i = 0; i < n_kb; i++, it++) {
-                    const int s = it % g.stages;
-                    const uint32_t phase = (uint32_t)(it / g.stages) & 1u;
+                for (int i = 0; i < n_kb; i++) {
                     if (!mbar_wait(&ctl->full[s], phase, ctl, 2)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a_addr = smem_u32(smem + (size_t)s * stage_bytes);
-                    const uint32_t b_addr = a_addr + A_TILE_BYTES;
+                    const uint64_t a_desc = desc0 + (uint64_t)s * stage_step, b_desc = a_desc + b_step;
+                    umma_pair(tmem_d, a_desc, b_desc, idesc, i > 0 ? 1u : 0u);
 #pragma unroll
-                    for (int k = 0; k < BLOCK_K / UMMA_K; k++)
-                        umma_pair(tmem_d, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 1; k < BLOCK_K / UMMA_K; k++)
+                        umma_pair(tmem_d, a_desc + (uint64_t)(k * UMMA_K * 2 >> 4), b_desc + (uint64_t)(k * UMMA_K * 2 >> 4), idesc, 1u);
                     umma_commit_both(&ctl->empty[s]);       // frees the stage in both CTAs
+                    if (++s == g.stages) { s = 0; phase ^= 1u; }
                 }
                 if (ok) umma_commit_both(&ctl->tmem_full[buf]);
             }

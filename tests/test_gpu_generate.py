@@ -349,3 +349,25 @@ def test_greedy_checksum_of_the_references_own_bench(tmp_path, dtype):
         lg = plain_llama.PlainLlama(tmp_path / "m").logits(g["prompt"] + want[:k])[-1]
         assert float(lg[want[k]] - lg[toks[k]]) < 0.1, f"token {k}: {toks[k]} vs {want[k]}"
         assert k > 8
+
+
+def test_bench_checksum_is_the_same_on_every_run(model_dirs):
+    """The bench's end-to-end arm hashes its greedy tokens (FNV-1a, as the reference's bench does,
+    benchmark/bench_engine.cpp:233-242): two runs give the same checksum, and so does a run that does
+    not queue a step ahead of the host; unequal prompts as in the quoted workloads."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench", helpers.ROOT / "bench.py")
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    assert bench.fnv1a([]) == 1469598103934665603 and bench.fnv1a([1]) != bench.fnv1a([2])     # the reference's offset
+    eng = _engine(model_dirs, "E", "bfloat16", max_tokens=4096)
+    lengths = [40, 7, 130, 64, 1]
+    runs = [bench.time_e2e(eng, lengths, steps=12, warmup=3, vocab=389, lookahead=ahead) for ahead in (True, True, False)]
+    assert runs[0]["tokens"] == len(lengths) * 16
+    assert runs[0]["checksum"] == runs[1]["checksum"] == runs[2]["checksum"]
+    assert runs[0]["h2d_bytes_per_step"] > 0 and runs[0]["d2h_bytes_per_step"] == 4 * len(lengths)
+    dec = bench.time_decode(eng, lengths, steps=6, warmup=3, vocab=389, regions=3)
+    assert dec["regions"] == 3 and dec["ms_min"] <= dec["ms_per_step"] <= dec["ms_max"] and dec["launches"] > 0
+    weights = eng.model.step_bytes([])
+    assert dec["step_bytes"] > weights > 0
+    eng.cache.check()

@@ -212,7 +212,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     Ctl* ctl = (Ctl*)(v_s + STAGES * KV_TILE);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.z, kvh = blockIdx.y;
+    // grid (KV heads, sequences, tiles): CTAs start in that order, so the heaviest tiles (the late rows
+    // of a causal prompt) of every head and sequence start first and the light ones fill the gaps
+    const int b = blockIdx.y, kvh = blockIdx.x;
     if (threadIdx.x == 0) {
         mbar_init(&ctl->q_full, 1);
         for (int s = 0; s < STAGES; s++) {
@@ -242,7 +244,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     // heavy tiles (late rows of a causal prompt) first
     const int qlen = a.seq_qlen[b];
     const int tpt = a.tokens_per_tile;
-    const int q_tile = (int)gridDim.x - 1 - (int)blockIdx.x;
+    const int q_tile = (int)gridDim.z - 1 - (int)blockIdx.z;
     const bool active = qlen > 0 && q_tile * tpt < qlen;
     int n_blocks = 0, j_lo = 0, t0 = 0, nt = 0, start = 0;
     long long packed0 = 0;
@@ -287,15 +289,20 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             const uint32_t idesc_s = umma_idesc(BM, BN, false);
             const uint32_t idesc_o = umma_idesc(BM, HD, true);
             bool ok = mbar_wait(&ctl->q_full, 0, ctl, 2);
+            // Operand descriptors differ from stage to stage and from one 16-deep step to the next only in
+            // their address field (bytes / 16): built once, carried along by additions (this thread's loop
+            // bounds how fast a CTA can issue, see gemm_tcgen05.cu).
+            const uint64_t q_desc = umma_desc(smem_u32(q_s), 16, 1024), k_desc = umma_desc(smem_u32(k_s), 16, 1024);
+            const uint64_t v_desc = umma_desc(smem_u32(v_s), BN * 128, 1024);
             auto issue_s = [&](int i) {                       // S_i = Q K_i^T into S buffer i & 1
                 const int s = i % STAGES;
-                const uint32_t k_addr = smem_u32(k_s + (size_t)s * KV_TILE);
-                const uint32_t q_addr = smem_u32(q_s);
+                const uint64_t kd = k_desc + (uint64_t)(s * (KV_TILE >> 4));
+                const uint32_t s_tmem = tmem_base + S_COL + (uint32_t)((i & 1) * BN);
 #pragma unroll
                 for (int k = 0; k < HD / 16; k++) {
                     const uint32_t sb = k / 4, kk = k % 4;
-                    umma(tmem_base + S_COL + (uint32_t)((i & 1) * BN), umma_desc(q_addr + sb * (BM * 128) + kk * 32, 16, 1024),
-                         umma_desc(k_addr + sb * (BN * 128) + kk * 32, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
+                    umma(s_tmem, q_desc + (uint64_t)((sb * (BM * 128) + kk * 32) >> 4),
+                         kd + (uint64_t)((sb * (BN * 128) + kk * 32) >> 4), idesc_s, k > 0 ? 1u : 0u);
                 }
                 umma_commit(&ctl->s_full[i & 1]);
                 umma_commit(&ctl->k_empty[s]);               // K_i is no longer needed
@@ -321,13 +328,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 ok = mbar_wait(&ctl->v_full[s], (uint32_t)(i / STAGES) & 1u, ctl, 5);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t v_addr = smem_u32(v_s + (size_t)s * KV_TILE);
+                const uint64_t vd = v_desc + (uint64_t)(s * (KV_TILE >> 4));
                 // P_i sits in the first 32 columns of S buffer i & 1: 16 keys = 8 columns per instruction
                 const uint32_t p_tmem = tmem_base + S_COL + (uint32_t)((i & 1) * BN);
 #pragma unroll
                 for (int k = 0; k < BN / 16; k++) {
-                    umma_ts(tmem_base + O_COL, p_tmem + (uint32_t)(k * 8),
-                            umma_desc(v_addr + k * (16 * 128), BN * 128, 1024), idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+                    umma_ts(tmem_base + O_COL, p_tmem + (uint32_t)(k * 8), vd + (uint64_t)((k * (16 * 128)) >> 4), idesc_o,
+                            (i > 0 || k > 0) ? 1u : 0u);
                 }
                 umma_commit(&ctl->pv_done);
                 umma_commit(&ctl->v_empty[s]);               // V_i is no longer needed
@@ -514,6 +521,7 @@ int oe_attn_tc_bf16(bf16* out, const bf16* q, long long q_stride, const bf16* ca
         if (r != CUDA_SUCCESS) return 2000 + (int)r;
     }
     const int tiles = (max_qlen + a.tokens_per_tile - 1) / a.tokens_per_tile;
+    if (tiles > 65535) return OE_ERR_UNSUPPORTED;
     // two CTAs an SM; the kernel checks that its tiles fit behind the 1024-byte boundary it needs
     const size_t smem = (size_t)SMEM_NEEDED + 1024;
     static bool attr_set = false;
@@ -524,7 +532,7 @@ int oe_attn_tc_bf16(bf16* out, const bf16* q, long long q_stride, const bf16* ca
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
-    return oe_launch(attn_tc_kernel, dim3(tiles, KVH, n_seqs), dim3(THREADS), smem, st, map_q, map_kv, a);
+    return oe_launch(attn_tc_kernel, dim3(KVH, n_seqs, tiles), dim3(THREADS), smem, st, map_q, map_kv, a);
 }
 
 int oe_attn_tc_error() {

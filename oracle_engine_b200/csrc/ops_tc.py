@@ -107,8 +107,20 @@ def gemm_supported(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.stride(1) == 1)
 
 
-SKINNY_MAX_TOKENS = 16      # up to here the weight-streaming kernel (gemm_skinny.cu) is used (measured: 58 vs 65 us
-                            # for a layer's four products at 16 tokens; from 24 tokens on tcgen05 wins)
+SKINNY_MAX_TOKENS = 16      # the most tokens the weight-streaming kernel (gemm_skinny.cu) takes
+SKINNY_FULL_TOKENS = 8      # up to here it is used for every product; from 9 to 16 tokens only for weights of up to
+SKINNY_SMALL_BYTES = 24 << 20   # this size and for the logits.  Measured (us; 3072->16384 with SwiGLU, 8192->3072,
+                            # 3072->5120, 3072->3072; weight-streaming / tcgen05): 8 tokens 18.4 12.8 8.5 7.2 / 20.0 14.2
+                            # 11.2 9.9; 12 tokens 23.8 15.1 12.0 7.1 / 20.4 14.4 11.4 9.9; 16 tokens 23.8 15.0 11.9 7.1 /
+                            # 20.7 14.5 11.2 10.2
+
+
+def uses_skinny(M: int, N: int, K: int, kind: int) -> bool:
+    """Whether a product of M tokens with an [N, K] weight goes to the weight-streaming kernel
+    (kind: the epilogue, 1 = float32 store, the logits)."""
+    if M <= SKINNY_FULL_TOKENS:
+        return True
+    return M <= SKINNY_MAX_TOKENS and (kind == 1 or N * K * 2 <= SKINNY_SMALL_BYTES)
 PAIR_MIN_TOKENS = 256       # from here on the two-SM kernel (gemm_tcgen05_pair.cu) for stores; measured the
                             # same speed as the one-SM kernel or a little faster, except with the accumulate epilogue
 
@@ -142,7 +154,7 @@ def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool =
 
     swiglu: w's rows alternate gate and up rows (g0, u0, g1, u1, ...) and out [M, N/2]
     bfloat16 receives silu(gate) * up, computed in float32 in the epilogue.
-    kernel: "auto" (weight-streaming kernel up to SKINNY_MAX_TOKENS rows, the two-SM tcgen05
+    kernel: "auto" (weight-streaming kernel for a handful of rows, see uses_skinny, the two-SM tcgen05
     kernel from PAIR_MIN_TOKENS rows unless it accumulates, the one-SM tcgen05 kernel otherwise),
     "tcgen05", "pair" or "skinny".
     early (weight-streaming kernel only): bit 0, it may start while the kernel before it drains;
@@ -167,7 +179,7 @@ def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool =
         kind = 1
     else:
         raise KernelError("gemm: output must be bfloat16 or float32")
-    if kernel == "skinny" or (kernel == "auto" and M <= SKINNY_MAX_TOKENS):
+    if kernel == "skinny" or (kernel == "auto" and uses_skinny(M, N, K, kind)):
         code = _skinny().oe_gemm_skinny_bf16(out.data_ptr(), a.data_ptr(), w.data_ptr(), M, N, K, a.stride(0),
                                              out.stride(0), kind, int(early), ops._stream())
         ops._check(code, "gemm_skinny", (M, N, K))

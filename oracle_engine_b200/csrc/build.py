@@ -114,8 +114,9 @@ def build(name: str, verbose: bool = True, defines=None) -> Path:
     tmp = out.with_suffix(f".tmp{os.getpid()}.so")
     cmd[cmd.index(None)] = str(tmp)
     t0 = time.time()
+    what = src + (f" ({', '.join(dflags)})" if dflags else "")
     if verbose:
-        log.info("build", f"compiling {src}{tag} for sm_100a ...")
+        log.info("build", f"compiling {what} for sm_100a ...")
     env = dict(os.environ)
     env.setdefault("TMPDIR", tempfile.gettempdir())
     proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env)
@@ -125,7 +126,7 @@ def build(name: str, verbose: bool = True, defines=None) -> Path:
             break
         except subprocess.TimeoutExpired:
             if verbose:
-                log.info("build", f"... still compiling {src}{tag} ({time.time() - t0:.0f} s)")
+                log.info("build", f"... still compiling {what} ({time.time() - t0:.0f} s)")
     if proc.returncode != 0:
         tmp.unlink(missing_ok=True)
         raise BuildError(f"nvcc failed on {src} (exit {proc.returncode}):\n{' '.join(cmd)}\n{output}")

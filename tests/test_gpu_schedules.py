@@ -203,29 +203,33 @@ def test_sixty_four_sequences_across_the_first_boundary(real_heads, tmp_path):
     eng.cache.check()
 
 
-def test_real_widths_against_plain(tmp_path):
-    """Two layers with the widths of the benchmark model (hidden 3072, 24 / 8 heads of 128, FFN 8192)
-    and a small vocabulary, against the plain model: a prompt step of 64 unequal prompts (the
-    tensor-core products at thousands of rows), decode steps of 64 sequences (swap-AB products whose K
-    splits add up in a cluster, narrow gate/up tiles), of 24 and of 8 (the weight-streaming kernel)."""
+@pytest.mark.parametrize("hidden,heads,kv_heads,head_dim,ffn,factor", [(3072, 24, 8, 128, 8192, 32.0),      # Llama 3.2 3B
+                                                                       (2048, 32, 8, 64, 8192, 32.0),       # 3.2 1B
+                                                                       (4096, 32, 8, 128, 14336, 8.0)])     # 3.1 8B
+def test_real_widths_against_plain(tmp_path, hidden, heads, kv_heads, head_dim, ffn, factor):
+    """Two layers with the widths of the benchmark models and a small vocabulary, against the plain
+    model: a prompt step of 64 unequal prompts (the tensor-core products at thousands of rows), decode
+    steps of 64 sequences (swap-AB products whose K splits add up in a cluster, narrow gate/up tiles),
+    of 24 (tcgen05 products and the weight-streaming kernel side by side) and of 8."""
     import plain_llama
     from oracle_engine_b200 import LlamaConfig, write_model_folder
     from oracle_engine_b200.engine.engine import Engine
-    raw = dict(architectures=["LlamaForCausalLM"], vocab_size=2048, hidden_size=3072, intermediate_size=8192,
-               num_hidden_layers=2, num_attention_heads=24, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-5,
-               rope_theta=500000.0, rope_scaling={"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
-                                                  "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+    raw = dict(architectures=["LlamaForCausalLM"], vocab_size=2048, hidden_size=hidden, intermediate_size=ffn,
+               num_hidden_layers=2, num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=head_dim,
+               rms_norm_eps=1e-5, rope_theta=500000.0,
+               rope_scaling={"rope_type": "llama3", "factor": factor, "low_freq_factor": 1.0,
+                             "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
                max_position_embeddings=4096, tie_word_embeddings=False, eos_token_id=1)
     folder = tmp_path / "wide"
     write_model_folder(folder, LlamaConfig.from_dict(raw), seed=3, device="cuda")
     plain = plain_llama.PlainLlama(folder, device="cuda")
     n = 64
-    # 64 sequences decode 3 tokens, then 24 of them 2 more, then 8 of them 2 more
-    decoded = [7 if i < 8 else 5 if i < 24 else 3 for i in range(n)]
+    # 64 sequences decode 3 tokens, then 24 of them 2 more, then 12 of them 2 more, then 8 of them 2 more
+    decoded = [9 if i < 8 else 7 if i < 12 else 5 if i < 24 else 3 for i in range(n)]
     prompt_lens = [20 + (i * 7) % 64 for i in range(n)]
     requests = [helpers.random_tokens(p + d, 2048, 600 + i) for i, (p, d) in enumerate(zip(prompt_lens, decoded))]
     steps = helpers.batched_steps(requests, prompt_lens, n)
-    assert [len(s["entries"]) for s in steps] == [64, 64, 64, 64, 24, 24, 8, 8]
+    assert [len(s["entries"]) for s in steps] == [64, 64, 64, 64, 24, 24, 12, 12, 8, 8]
     eng = Engine.from_pretrained(str(folder), dtype="bfloat16", max_tokens=n * 128)
     out = helpers.TraceRunner(eng, tmp_path / "wide_out").run(steps)
     eng.check_device_errors()

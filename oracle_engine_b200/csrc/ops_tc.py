@@ -121,8 +121,9 @@ def uses_skinny(M: int, N: int, K: int, kind: int) -> bool:
     if M <= SKINNY_FULL_TOKENS:
         return True
     return M <= SKINNY_MAX_TOKENS and (kind == 1 or N * K * 2 <= SKINNY_SMALL_BYTES)
-PAIR_MIN_TOKENS = 256       # from here on the two-SM kernel (gemm_tcgen05_pair.cu) for stores; measured the
-                            # same speed as the one-SM kernel or a little faster, except with the accumulate epilogue
+PAIR_MIN_TOKENS = 256       # from here on the two-SM kernel (gemm_tcgen05_pair.cu); measured against the one-SM kernel
+                            # at 2,048 / 4,096 tokens (us): 3072->16384 SwiGLU 134 / 150; 3072->3072 accumulate 39.2 /
+                            # 40.9 and 64.5 / 72.5; 8192->3072 accumulate 90.2 / 95.5 and 165 / 183
 
 
 def _pair():
@@ -155,7 +156,7 @@ def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool =
     swiglu: w's rows alternate gate and up rows (g0, u0, g1, u1, ...) and out [M, N/2]
     bfloat16 receives silu(gate) * up, computed in float32 in the epilogue.
     kernel: "auto" (weight-streaming kernel for a handful of rows, see uses_skinny, the two-SM tcgen05
-    kernel from PAIR_MIN_TOKENS rows unless it accumulates, the one-SM tcgen05 kernel otherwise),
+    kernel from PAIR_MIN_TOKENS rows, the one-SM tcgen05 kernel otherwise),
     "tcgen05", "pair" or "skinny".
     early (weight-streaming kernel only): bit 0, it may start while the kernel before it drains;
     bit 1, the kernel after it is released only when its CTAs have streamed their weights."""
@@ -184,7 +185,7 @@ def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool =
                                              out.stride(0), kind, int(early), ops._stream())
         ops._check(code, "gemm_skinny", (M, N, K))
         return
-    if kernel == "pair" or (kernel == "auto" and M >= PAIR_MIN_TOKENS and N >= 32 and not accumulate):
+    if kernel == "pair" or (kernel == "auto" and M >= PAIR_MIN_TOKENS and N >= 32):
         code = _pair().oe_gemm_pair_bf16(out.data_ptr(), a.data_ptr(), w.data_ptr(), M, N, K, a.stride(0), out.stride(0),
                                          kind, int(KNOBS.pair_max_tile), ops._stream())
         ops._check(code, "gemm_pair", (M, N, K))

@@ -316,9 +316,9 @@ def test_generate_raises_when_a_kernel_reports_an_error(model_dirs):
     from oracle_engine_b200 import GenParams
     from oracle_engine_b200.csrc import ops_tc
     eng = _engine(model_dirs, "E", "bfloat16", max_tokens=2048)
-    prompts = [helpers.random_tokens(600, 389, 5)]
+    prompts = [helpers.random_tokens(200, 389, 5)]                      # fewer than 256 tokens: the one-SM tcgen05 products
     good = eng.generate(prompts, GenParams.greedy(3, ignore_eos=True))
-    with ops_tc.knobs(sm_count=1, gemm_waits=(2_000_000, 1)):           # five row tiles of the prompt on one CTA
+    with ops_tc.knobs(sm_count=1, gemm_waits=(2_000_000, 1)):           # six and eight tiles of the prompt's products on one CTA
         with pytest.raises(RuntimeError, match="bounded wait"):
             eng.generate(prompts, GenParams.greedy(3, ignore_eos=True))
     assert eng.cache.slots.n_free == eng.cache.n_slots                  # the slots came back

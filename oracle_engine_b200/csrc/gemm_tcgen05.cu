@@ -159,6 +159,7 @@ struct GemmArgs {
     int rows_a, rows_b, K;      // valid rows of the A (128-row) and B (n_tile-row) operands
     int n_tile;                 // rows of the B tile, multiple of 16, <= 256
     int atoms;                  // 64-deep swizzle atoms per k-block and pipeline stage (1 or 2)
+    int n_kb_total, kb_per;     // k-blocks of the whole K, and of one split (worked out on the host: no division per thread)
     int stages;
     int swap;                   // 1: C[b_row, a_row] (A = weights); 0: C[a_row, b_row] (A = activations)
     int out_kind;               // 0 bf16 store, 1 float32 store, 2 float32 accumulate, 3 bf16 silu(gate)*up
@@ -333,13 +334,16 @@ struct ItemIter {
 __device__ __forceinline__ ItemIter make_iter(const GemmArgs& g) {
     ItemIter t;
     t.streamk = g.streamk; t.cluster = g.cluster; t.tiles_a = g.tiles_a; t.tiles_b = g.tiles_b; t.splits = g.splits;
-    t.n_kb_total = (g.K + BLOCK_K * g.atoms - 1) / (BLOCK_K * g.atoms);
-    t.kb_per = (t.n_kb_total + g.splits - 1) / g.splits;
+    t.n_kb_total = g.n_kb_total;
+    t.kb_per = g.kb_per;
     t.w = blockIdx.x; t.step = gridDim.x; t.n_work = g.tiles_a * g.tiles_b * g.splits;
     t.G = gridDim.x;
-    t.T = (long long)g.sk_tiles * t.n_kb_total;
-    t.n_tiles = (long long)g.tiles_a * g.tiles_b; t.dp = (long long)g.sk_tiles + blockIdx.x;
-    t.u0 = t.start_of(blockIdx.x); t.u1 = t.start_of(blockIdx.x + 1); t.u = t.u0;
+    t.T = 0; t.n_tiles = 0; t.dp = 0; t.u0 = t.u1 = t.u = 0;
+    if (g.streamk) {           // 64-bit divisions: only where the schedule needs them
+        t.T = (long long)g.sk_tiles * t.n_kb_total;
+        t.n_tiles = (long long)g.tiles_a * g.tiles_b; t.dp = (long long)g.sk_tiles + blockIdx.x;
+        t.u0 = t.start_of(blockIdx.x); t.u1 = t.start_of(blockIdx.x + 1); t.u = t.u0;
+    }
     return t;
 }
 // Where piece p of the item's tile lies in the workspace (floats), for row 0 and column 0.
@@ -373,6 +377,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint32_t tmem_cols = 32;
     while ((int)tmem_cols < 2 * g.n_tile) tmem_cols <<= 1;          // two accumulators
 
+    if (threadIdx.x == 32) {    // the copies' descriptors are on their way while the barriers are set up
+        asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_b) : "memory");
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < g.stages; s++) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
         for (int b = 0; b < 2; b++) { mbar_init(&ctl->tmem_full[b], 1); mbar_init(&ctl->tmem_empty[b], 4); }
@@ -949,6 +957,8 @@ int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, 
     }
     const long long n_work = (long long)g.tiles_a * g.tiles_b * g.splits;
     if (n_work > 2147483647LL) return OE_ERR_UNSUPPORTED;
+    g.n_kb_total = (K + BLOCK_K * g.atoms - 1) / (BLOCK_K * g.atoms);
+    g.kb_per = (g.n_kb_total + g.splits - 1) / g.splits;
     grid = dim3((unsigned)((n_work < sm_count && !g.streamk) ? n_work : sm_count));
     const int b_tile_bytes = g.n_tile * BLOCK_K * 2;
     const int stage_bytes = g.atoms * (A_TILE_BYTES + ((b_tile_bytes + 1023) & ~1023));

@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Compiles the reference engine's own benchmark program, unmodified, into baseline/_ref/.
 
-    python baseline/build_reference.py [/path/to/oracle-engine]      (default: /root/reference)
+    python baseline/build_reference.py /path/to/oracle-engine        (or the path in $ORACLE_REFERENCE_SRC)
 
 The reference is a C++17 CPU program without a Python package, so there is nothing for pip
 to install; its Makefile builds `oracle_bench` from benchmark/bench_engine.cpp and the
@@ -46,5 +46,8 @@ def build(source: Path) -> Path:
 
 
 if __name__ == "__main__":
-    src = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
-    print(build(src))
+    import os
+    where = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("ORACLE_REFERENCE_SRC")
+    if not where:
+        sys.exit(__doc__)
+    print(build(Path(where)))

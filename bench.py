@@ -317,8 +317,10 @@ def reference_arm(args) -> int:
     why = None
     exe = os.path.join(ROOT, "baseline", "_ref", "oracle_bench")
     if not os.path.isfile(exe):
-        src = os.environ.get("ORACLE_REFERENCE_SRC", "/root/reference")
+        src = os.environ.get("ORACLE_REFERENCE_SRC")
         try:
+            if not src:
+                raise RuntimeError("set ORACLE_REFERENCE_SRC to the reference's source tree")
             sys.path.insert(0, os.path.join(ROOT, "baseline"))
             import build_reference
             from pathlib import Path

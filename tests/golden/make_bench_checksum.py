@@ -37,7 +37,9 @@ def reference_sentence(ref: Path) -> str:
 
 
 def main():
-    ref = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit(__doc__)
+    ref = Path(sys.argv[1])
     import torch
     import gguf_export
     from conftest import TINY_B

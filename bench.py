@@ -298,9 +298,12 @@ def profile_decode(engine, lengths, vocab, file):
             per_launch = max(0.0, inside - plain_us) / max(1, len(prof.graph_events))
             print(f"decode step at batch {batch}: {plain_us:.1f} us plain, {inside:.1f} us with an event after every "
                   f"launch ({per_launch:.2f} us per launch, taken off in the last column)", file=file)
+            if per_launch > 8.0:
+                print("  (the events cost this step more than a launch usually does: its kernels normally start while their "
+                      "predecessors drain; read the first column as upper bounds and the last as a rough share)", file=file)
             totals = prof.graph_totals()
             for kind, (n, us) in sorted(totals.items(), key=lambda kv: -kv[1][1]):
-                net = us / n - per_launch
+                net = max(0.0, us / n - per_launch)
                 print(f"  {kind:<40s} {n:5d} x {us / n:8.1f} us  -> {net:8.1f} us  {100 * net * n / plain_us:5.1f} %", file=file)
         finally:
             for s in slots:

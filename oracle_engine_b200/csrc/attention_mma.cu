@@ -420,7 +420,6 @@ attn_mma_kernel(const AttnArgs a) {
 constexpr int TB = 32;                          // keys per tile of a warp
 constexpr int TB_BYTES = TB * ROW_BYTES;
 constexpr int WARP_STAGE_BYTES = 2 * TB_BYTES;  // K and V
-constexpr int WARP_BYTES = 2 * WARP_STAGE_BYTES;
 
 __device__ __forceinline__ void load_half_page(uint8_t* ks, uint8_t* vs, const bf16* cache, int page, int half, int kvh, int KVH, int lane) {
     const bf16* kg = cache + (((size_t)page * 2 + 0) * KVH + kvh) * (size_t)(BN * HD) + (size_t)half * TB * HD;
@@ -435,9 +434,15 @@ __device__ __forceinline__ void load_half_page(uint8_t* ks, uint8_t* vs, const b
     }
 }
 
-template <int NW>
+// NW warps, each with a ring of ST tiles: ST - 1 tiles of every warp are on their way from memory
+// while one is multiplied.  What a kernel like this streams is (bytes in flight) / (memory
+// latency), so the ring is as deep as shared memory allows: few warps with deep rings where many
+// CTAs share an SM (a large batch), many warps where a CTA has an SM to itself.
+template <int NW, int ST>
 __global__ void __launch_bounds__(NW * 32, 1)
 attn_decode_warps_kernel(const AttnArgs a) {
+    constexpr int WARP_BYTES = ST * WARP_STAGE_BYTES;
+    static_assert(ST >= 2 && 16 * (HD + 2) * 4 <= WARP_BYTES, "the merge scratch shares the staging buffers");
     extern __shared__ __align__(16) uint8_t smem[];
     pdl_launch_dependents();
     // A layer that reads another layer's cache finds the new token's key there, written by an
@@ -459,11 +464,15 @@ attn_decode_warps_kernel(const AttnArgs a) {
 
     // this warp's first tiles are requested before anything else
     const int n_my = hp_lo + warp <= hp_hi ? (hp_hi - hp_lo - warp) / NW + 1 : 0;
-    if (n_my > 0) {
-        const int hp = hp_lo + warp;
-        load_half_page(mine, mine + TB_BYTES, a.cache, trow[hp >> 1], hp & 1, kvh, a.KVH, lane);
+#pragma unroll
+    for (int pre = 0; pre < ST - 1; pre++) {
+        if (pre < n_my) {
+            const int hp = hp_lo + warp + pre * NW;
+            uint8_t* st = mine + (size_t)pre * WARP_STAGE_BYTES;
+            load_half_page(st, st + TB_BYTES, a.cache, trow[hp >> 1], hp & 1, kvh, a.KVH, lane);
+        }
+        cp_async_commit();
     }
-    cp_async_commit();
     // Up to here only the step's tables and keys and values of earlier steps were read, which no
     // kernel of this step writes (the stale row of the new token is replaced below): those loads
     // overlap the end of the kernel before this one.  The new token's q, k and v come from that kernel.
@@ -516,17 +525,21 @@ attn_decode_warps_kernel(const AttnArgs a) {
     for (int n = 0; n < HD / 8; n++) { oacc[n][0] = oacc[n][1] = oacc[n][2] = oacc[n][3] = 0.f; }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
+    int stage = 0;                                          // it % ST
     for (int it = 0; it < n_my; it++) {
         const int hp = hp_lo + warp + it * NW;
-        uint8_t* ks_cur = mine + (size_t)(it & 1) * WARP_STAGE_BYTES;
+        uint8_t* ks_cur = mine + (size_t)stage * WARP_STAGE_BYTES;
         uint8_t* vs_cur = ks_cur + TB_BYTES;
-        if (it + 1 < n_my) {
-            uint8_t* nxt = mine + (size_t)((it + 1) & 1) * WARP_STAGE_BYTES;
-            const int hn = hp + NW;
+        if (it + ST - 1 < n_my) {
+            // into the stage that the iteration before this one has read
+            const int fill = stage == 0 ? ST - 1 : stage - 1;
+            uint8_t* nxt = mine + (size_t)fill * WARP_STAGE_BYTES;
+            const int hn = hp + (ST - 1) * NW;
             load_half_page(nxt, nxt + TB_BYTES, a.cache, trow[hn >> 1], hn & 1, kvh, a.KVH, lane);
         }
         cp_async_commit();
-        cp_async_wait<1>();
+        cp_async_wait<ST - 1>();
+        stage = stage + 1 == ST ? 0 : stage + 1;
         __syncwarp();
         if (hp == hp_hi && a.cache_w != nullptr) {
             // this warp holds the tile of the new token: rotate its key, store key and value in the
@@ -636,7 +649,7 @@ attn_decode_warps_kernel(const AttnArgs a) {
                 mma_bf16(oacc[2 * dp + 1], pa, vb[dp & 1][2], vb[dp & 1][3]);
             }
         }
-        __syncwarp();                                       // the stage is refilled two tiles from now
+        __syncwarp();                                       // the next iteration refills this stage
     }
     cp_async_wait<0>();
 #pragma unroll
@@ -827,11 +840,14 @@ int oe_attn_decode_fused_bf16(bf16* out, const bf16* qkv, long long qkv_stride, 
 }
 
 // The same decode step with the warps of a CTA splitting the keys (attn_decode_warps_kernel):
-// one launch, no scratch.  Needs G = H/KVH <= 16.
+// one launch, no scratch.  Needs G = H/KVH <= 16.  shape = warps * 16 + ring depth; the forms
+// built here: 6 x 2 (a CTA fills an SM: up to about two CTAs for every SM), 4 x 3 (the same with
+// a deeper ring), 2 x 3 (two CTAs an SM) and 1 x 3 (four CTAs an SM: large batches).  0: 6 x 2.
+// Returns OE_ERR_UNSUPPORTED for a form that is not built or does not fit an SM at this head size.
 int oe_attn_decode_warps_bf16(bf16* out, const bf16* qkv, long long qkv_stride, const float* cos_tab,
                               const float* sin_tab, bf16* cache, int has_kv, const int* tables, int max_pages,
                               const int* cu_q, const int* seq_start, const int* seq_qlen, int n_seqs, int H, int KVH,
-                              int window, float scale, cudaStream_t st) {
+                              int window, float scale, int shape, cudaStream_t st) {
     if (n_seqs <= 0) return 0;
     if (H % KVH || ((uintptr_t)qkv & 3) || (qkv_stride & 1) || (HD % 32)) return OE_ERR_UNSUPPORTED;
     const int G = H / KVH;
@@ -842,17 +858,32 @@ int oe_attn_decode_warps_bf16(bf16* out, const bf16* qkv, long long qkv_stride, 
     a.scale_log2 = scale * 1.4426950408889634f;
     a.partial = nullptr; a.fused = 1; a.cos_tab = cos_tab; a.sin_tab = sin_tab; a.cache_w = has_kv ? cache : nullptr;
     a.counters = nullptr; a.tokens_per_tile = 1; a.n_splits = 1; a.stages = 2;
-    constexpr int NW = (6 * WARP_BYTES <= 220 * 1024) ? 6 : 3;
-    static_assert(NW * 16 * (HD + 2) * 4 <= NW * WARP_BYTES, "the merge scratch shares the staging buffers");
-    const size_t smem = (size_t)NW * WARP_BYTES;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_warps_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        attr_set = true;
+    if (shape == 0) shape = 6 * 16 + 2;
+    if (shape == 6 * 16 + 2 && 6 * 2 * WARP_STAGE_BYTES > 220 * 1024) shape = 3 * 16 + 2;    // large heads
+#define OE_WARPS_LAUNCH(NW, ST)                                                                                    \
+    if (shape == NW * 16 + ST) {                                                                                  \
+        constexpr size_t smem = (size_t)NW * ST * WARP_STAGE_BYTES;                                               \
+        if (smem > 220 * 1024) return OE_ERR_UNSUPPORTED;                                                         \
+        static bool attr_set = false;                                                                             \
+        if (!attr_set) {                                                                                          \
+            cudaError_t e = cudaFuncSetAttribute(attn_decode_warps_kernel<NW, ST>,                                \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
+            if (e != cudaSuccess) return (int)e;                                                                  \
+            attr_set = true;                                                                                      \
+        }                                                                                                         \
+        return oe_launch(attn_decode_warps_kernel<NW, ST>, dim3(1, KVH, n_seqs), dim3(NW * 32), smem, st, a);     \
     }
-    return oe_launch(attn_decode_warps_kernel<NW>, dim3(1, KVH, n_seqs), dim3(NW * 32), smem, st, a);
+    OE_WARPS_LAUNCH(6, 2)
+    OE_WARPS_LAUNCH(3, 2)
+    OE_WARPS_LAUNCH(4, 3)
+    OE_WARPS_LAUNCH(2, 3)
+    OE_WARPS_LAUNCH(1, 3)
+#undef OE_WARPS_LAUNCH
+    return OE_ERR_UNSUPPORTED;
 }
+
+// Bytes of shared memory one CTA of a form takes (how many share an SM follows from it).
+int oe_attn_decode_warps_smem(int shape) { return (shape / 16) * (shape % 16) * WARP_STAGE_BYTES; }
 
 }  // extern "C"
 

@@ -25,6 +25,7 @@ class _Knobs:
     prompt_kernel = "tcgen05"      # "tcgen05" or "mma": the prompt attention kernel for head sizes 64 / 128
     decode_kernel = "auto"         # "auto", "warps", "split": the decode attention kernel
     decode_splits = 0              # > 0: this many CTAs per (sequence, KV head) instead of the rule's
+    decode_warps_shape = None      # (warps, ring depth) of the kernel whose warps split the keys, instead of the rule's
     pair_max_tile = 0              # > 0: an upper limit for the two-SM product's tile width
     sm_count = 0                   # > 0: the products plan their grids for this many SMs
     gemm_schedule = (0, -1, -1, -1, -1)     # one-SM tcgen05 product: tile width, stream-K, cluster, narrow, atoms (see knobs)
@@ -242,7 +243,7 @@ def _attn_lib(head_dim: int):
         lib.oe_attn_decode_fused_bf16.restype = c_int
         lib.oe_attn_decode_warps_bf16.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
                                                   c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                                  c_int, c_float, c_void_p]
+                                                  c_int, c_float, c_int, c_void_p]
         lib.oe_attn_decode_warps_bf16.restype = c_int
         lib.oe_attn_mma_partial_floats.argtypes = [c_int, c_int, c_int]
         lib.oe_attn_mma_partial_floats.restype = c_longlong
@@ -356,8 +357,8 @@ def decode_fused_supported(head_dim: int, n_heads: int, n_kv_heads: int) -> bool
 
 DECODE_WARPS_FULL_CTAS = 48  # (sequence, KV head) pairs from which contexts of class 1 stay on the warps kernel too
 DECODE_WARPS_LONG_CTAS = 96  # ... and contexts of class 2
-DECODE_WARPS_MAX_CTAS = 300  # short contexts with more pairs than this: the one-warp kernel, several CTAs an SM
-DECODE_WARPS_MIN_FILL = 0.75 # long contexts, more pairs than SMs: the share of the last round of CTAs that must be full
+DECODE_WARPS_FORMS = ((6, 2), (2, 3), (1, 3))    # (warps, tiles in a warp's ring) the rule picks from (csrc/attention_mma.cu)
+SM_SHARED_BYTES = 227 * 1024   # what the CTAs resident on an SM share, each with 1 KB of the system's on top
 
 
 def decode_warps_supported(head_dim: int, n_heads: int, n_kv_heads: int) -> bool:
@@ -367,27 +368,70 @@ def decode_warps_supported(head_dim: int, n_heads: int, n_kv_heads: int) -> bool
 def decode_uses_warps(n_seqs: int, context_class: int, head_dim: int, n_heads: int, n_kv_heads: int,
                       sm_count: int | None = None) -> bool:
     """Whether a decode step goes to the kernel whose warps split the keys (one launch, no
-    scratch) rather than to CTAs that split the keys plus a merge, or to the one-warp kernel.
-    Depends on the batch size and the step's context class (engine/batch.py) only; a captured
-    graph is kept per class.  Measured (us, 24 heads over 8 KV heads of 128; warps / split / one-warp):
-    class 0 (640 keys): 8 sequences 10.6 / 10.8+rotation / 28, 64 sequences 43 / 38+rotation / 40;
-    class 1 (2,048): 1 sequence 20 / 12 / 28, 8: 21 / 22 / 43, 64: 93 / 105 / 108;
-    class 2 (8,000): 1: 63 / 18 / 33, 8: 66 / 56 / 109, 16: 90 / 90, 24: 150 / 130, 32: 159 / 246,
-    64: 316 / 390 / 391."""
+    scratch) rather than to CTAs that split the keys plus a merge.  Depends on the batch size and
+    the step's context class (engine/batch.py) only; a captured graph is kept per class.
+    With up to one (sequence, KV head) pair per SM, measured (us, 24 heads over 8 KV heads of
+    128; warps / split): class 0 (640 keys): 8 sequences 9.1 / 10.8+rotation; class 1 (2,048):
+    1 sequence 20 / 12, 8: 21 / 22; class 2 (8,000): 1: 63 / 18, 8: 66 / 56, 16: 90 / 90.
+    With more pairs than SMs the warps kernel in the form `decode_warps_shape` picks wins
+    everywhere (see there)."""
     if KNOBS.decode_kernel == "split" or not decode_warps_supported(head_dim, n_heads, n_kv_heads):
         return False
     if KNOBS.decode_kernel == "warps":
         return True
     pairs = n_seqs * n_kv_heads
-    if context_class <= 0:
-        return pairs <= DECODE_WARPS_MAX_CTAS     # beyond: every SM has several one-warp CTAs, measured faster
+    if context_class <= 0 or pairs > (sm_count or _sm_count()):
+        return True
+    # with few sequences more CTAs per sequence win
+    return pairs >= (DECODE_WARPS_FULL_CTAS if context_class == 1 else DECODE_WARPS_LONG_CTAS)
+
+
+def decode_warps_per_sm(shape: tuple, head_dim: int) -> int:
+    """How many CTAs of a form of the warps kernel an SM holds (0: the form does not fit)."""
+    smem = shape[0] * shape[1] * 2 * 32 * (head_dim * 2 + 16)      # K and V tiles of 32 padded rows
+    return 0 if smem > 220 * 1024 else SM_SHARED_BYTES // (smem + 1024)
+
+
+def decode_warps_shape(n_seqs: int, context_class: int, head_dim: int, n_kv_heads: int,
+                       sm_count: int | None = None) -> tuple:
+    """(warps, tiles in each warp's ring) for the kernel whose warps split the keys.
+
+    What an SM streams is its bytes in flight over the memory latency, and a CTA's start and
+    merge hide only behind another CTA of the same SM.  So: the form with the most warps whose
+    CTAs are all resident at once (at head size 128 one CTA an SM for up to 148 pairs, then two,
+    then four); with more pairs than that, short contexts take the smallest CTAs.  Long contexts
+    leave the one-warp form out (a lone warp's arithmetic shows there) and, past one round, take
+    the form whose last round of CTAs is fullest.  Measured (us; 24 heads over 8 KV heads of 128; 6x2 / 2x3 /
+    1x3 / the one-warp kernel with one staged page):
+    600 keys:   16 sequences 10.5 / 14.0 / 20.6 / -,  24: 19.2 / 15.0 / 22.8 / -,  32: 21.2 / 16.1 / 24.2 / -,
+                48: 31.5 / 31.4 / 24.9 / 35.2,  64: 41.9 / 33.1 / 31.3 / 37.8,  128: 74.1 / 64.1 / 55.3 / 74.2
+    2,100 keys: 24: 46.0 / 40.0 / 67.3,  32: 48.3 / 49.0 / 70.5,  48: 71.9 / 83.8 / 73.9,  64: 95.1 / 87.2 / 96.4,
+                96: 139 / 132 / 155,  128: 182 / 174 / 169;   8,000 keys, 64: 314 / 309 / 349."""
+    if KNOBS.decode_warps_shape is not None:
+        return tuple(KNOBS.decode_warps_shape)
     sms = sm_count or _sm_count()
-    if pairs <= sms:                              # with few sequences more CTAs per sequence win
-        return pairs >= (DECODE_WARPS_FULL_CTAS if context_class == 1 else DECODE_WARPS_LONG_CTAS)
-    # One CTA of this kernel fills an SM's shared memory, and one SM streams about 40 GB/s: a last
-    # round with few CTAs is a slow tail (192 pairs at 8,000 keys: 150 us against 130 split; 256: 159 / 246).
-    rounds = (pairs + sms - 1) // sms
-    return pairs >= DECODE_WARPS_MIN_FILL * rounds * sms
+    pairs = max(1, n_seqs * n_kv_heads)
+    forms, seen = [], set()
+    for shape in DECODE_WARPS_FORMS:                # most warps first; one form for each number of CTAs an SM holds
+        per_sm = decode_warps_per_sm(shape, head_dim)
+        if per_sm > 0 and per_sm not in seen:
+            seen.add(per_sm)
+            forms.append((shape, per_sm * sms))
+    if not forms:
+        raise KernelError(f"attention_decode_warps: no form of the kernel fits an SM at head size {head_dim}")
+    if context_class > 0 and len(forms) > 1:
+        forms = forms[:-1]
+    for shape, slots in forms:
+        if pairs <= slots:
+            return shape
+    if context_class <= 0:
+        return forms[-1][0]
+    best, best_fill = forms[0][0], 0.0
+    for shape, slots in forms:
+        fill = pairs / (-(-pairs // slots) * slots)
+        if fill >= best_fill - 1e-9:                 # equal fill: the smaller CTAs, whose tail is shorter
+            best, best_fill = shape, fill
+    return best
 
 
 def _sm_count() -> int:
@@ -397,10 +441,10 @@ def _sm_count() -> int:
 
 
 def attention_decode_warps(out, qkv, cos, sin, cache, tables, ctx, n_heads: int, n_kv_heads: int, head_dim: int,
-                           window: int, scale: float, has_kv: bool) -> None:
+                           window: int, scale: float, has_kv: bool, shape: tuple | None = None) -> None:
     """The decode step's mixer core (rotation, cache write, attention) in one launch: one CTA per
     (sequence, KV head), whose warps split the keys (csrc/attention_mma.cu).  Same arguments as
-    attention_decode_fused."""
+    attention_decode_fused; shape = (warps, tiles in each warp's ring), None: `decode_warps_shape`."""
     if out.dtype != torch.bfloat16 or qkv.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
         raise KernelError("attention_decode_warps: bfloat16 tensors expected")
     width = (n_heads + (2 * n_kv_heads if has_kv else 0)) * head_dim
@@ -409,12 +453,14 @@ def attention_decode_warps(out, qkv, cos, sin, cache, tables, ctx, n_heads: int,
     if tuple(cache.shape[1:]) != (2, n_kv_heads, ops.PAGE, head_dim):
         raise KernelError("attention_decode_warps: cache entry must be [pages, 2, KVH, PAGE, head_dim]")
     lib = _attn_lib(head_dim)
+    if shape is None:
+        shape = decode_warps_shape(ctx.n_seqs, getattr(ctx, "context_class", 0), head_dim, n_kv_heads)
     code = lib.oe_attn_decode_warps_bf16(
         out.data_ptr(), qkv.data_ptr(), qkv.stride(0), None if cos is None else cos.data_ptr(),
         None if sin is None else sin.data_ptr(), cache.data_ptr(), int(has_kv), tables.data_ptr(), tables.shape[1],
         ctx.cu_q.data_ptr(), ctx.seq_start.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.n_seqs, n_heads, n_kv_heads,
-        int(window), float(scale), ops._stream())
-    ops._check(code, "attention_decode_warps")
+        int(window), float(scale), shape[0] * 16 + shape[1], ops._stream())
+    ops._check(code, "attention_decode_warps", {"warps": shape[0], "ring": shape[1]})
 
 
 def _attn_counters(device):

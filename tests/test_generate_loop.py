@@ -223,10 +223,20 @@ def test_decode_kernel_rules_depend_on_sizes_only():
     from oracle_engine_b200.engine import batch
     assert [batch.context_class(n) for n in (1, 1536, 1537, 4096, 4097, 100000)] == [0, 0, 1, 1, 2, 2]
     uses = lambda n_seqs, cls: ops_tc.decode_uses_warps(n_seqs, cls, 128, 24, 8, sm_count=148)
-    assert [uses(b, 0) for b in (1, 8, 37, 38, 64)] == [True, True, True, False, False]      # 300 pairs at most
-    assert [uses(b, 1) for b in (1, 5, 6, 18, 19, 24, 28, 32, 64)] == \
-        [False, False, True, True, False, False, True, True, True]     # 48..148 pairs, then rounds three quarters full
-    assert [uses(b, 2) for b in (8, 11, 12, 18, 24, 32, 40, 64)] == [False, False, True, True, False, True, False, True]
+    assert [uses(b, 0) for b in (1, 8, 37, 38, 64, 500)] == [True] * 6                       # short contexts: always
+    assert [uses(b, 1) for b in (1, 5, 6, 18, 19, 24, 64)] == [False, False, True, True, True, True, True]   # from 48 pairs
+    assert [uses(b, 2) for b in (8, 11, 12, 18, 24, 40, 64)] == [False, False, True, True, True, True, True]  # from 96 pairs
+    # its form, (warps, tiles in a warp's ring): the most warps whose CTAs are all resident at once (1, 2 or 4 an SM)
+    shape = lambda n_seqs, cls, hd=128, kvh=8: ops_tc.decode_warps_shape(n_seqs, cls, hd, kvh, sm_count=148)
+    assert [shape(b, 0) for b in (1, 18, 19, 37, 38, 64, 74, 75, 128)] == \
+        [(6, 2), (6, 2), (2, 3), (2, 3), (1, 3), (1, 3), (1, 3), (1, 3), (1, 3)]
+    # long contexts: no one-warp form; past one round of CTAs the fullest last round, equal ones to the smaller CTAs
+    assert [shape(b, 1) for b in (18, 19, 37, 38, 48, 64, 96, 128)] == \
+        [(6, 2), (2, 3), (2, 3), (6, 2), (6, 2), (2, 3), (2, 3), (6, 2)]
+    assert shape(4, 0, hd=256, kvh=2) == (2, 3) and shape(100, 1, hd=256, kvh=2) == (2, 3)     # 6 x 2 does not fit an SM there
+    assert shape(30, 0, hd=64, kvh=8) == (6, 2) and shape(40, 0, hd=64, kvh=8) == (2, 3)       # two CTAs of 6 x 2 an SM
+    with ops_tc.knobs(decode_warps_shape=(4, 3)):
+        assert shape(64, 0) == (4, 3)
     assert not ops_tc.decode_uses_warps(8, 0, 128, 64, 2, sm_count=148)                      # 32 heads per KV head
     splits = lambda n_seqs, cls, pages=128: ops_tc.decode_splits(n_seqs, 8, 148, pages, cls, 3)
     assert [splits(b, 0) for b in (1, 8, 24, 64)] == [32, 5, 2, 1]                            # about two CTAs an SM

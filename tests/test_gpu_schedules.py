@@ -168,13 +168,14 @@ def test_one_sequence_across_both_context_class_boundaries(real_heads, tmp_path)
 
 def test_sixty_four_sequences_across_the_first_boundary(real_heads, tmp_path):
     """64 sequences of 1,460 to 1,523 tokens decode 90 tokens each, across 1,536: 512 (sequence, KV
-    head) pairs go to the one-warp fused kernel in class 0 and to the warps kernel in class 1.  CUDA
+    head) pairs go to one-warp CTAs with rings of three tiles in class 0 (four CTAs an SM) and to
+    two-warp CTAs in class 1.  CUDA
     graphs on, as in serving; every decoded position against the plain model."""
     from oracle_engine_b200.csrc import ops_tc
     from oracle_engine_b200.engine.engine import Engine
     folder, plain = real_heads
     n = 64
-    assert not ops_tc.decode_uses_warps(n, 0, 128, 24, 8) and ops_tc.decode_uses_warps(n, 1, 128, 24, 8)
+    assert ops_tc.decode_warps_shape(n, 0, 128, 8) == (1, 3) and ops_tc.decode_warps_shape(n, 1, 128, 8) == (2, 3)
     lens = [1460 + i + 90 for i in range(n)]
     requests = [helpers.random_tokens(m, 512, 900 + i) for i, m in enumerate(lens)]
     steps = helpers.batched_steps(requests, [1460 + i for i in range(n)], n)

@@ -188,6 +188,13 @@ __device__ __forceinline__ void tmem_st16_u32(uint32_t taddr, const uint32_t* v)
         : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// True in exactly one lane of a converged warp.  The warp stays converged around the
+// instructions that lane issues, so their operands can stay in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -285,30 +292,38 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
     } else if (warp == 1) {
         // ---------------- MMA issue ----------------
-        if (lane == 0 && active) {
+        // The whole warp runs the loop and waits; one elected lane issues.  (With the role inside
+        // `if (lane == 0)` every operand of every instruction went through that one lane's registers.)
+        if (active) {
             const uint32_t idesc_s = umma_idesc(BM, BN, false);
             const uint32_t idesc_o = umma_idesc(BM, HD, true);
-            bool ok = mbar_wait(&ctl->q_full, 0, ctl, 2);
+            // every lane waits, and all take the same decision
+            auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) -> bool {
+                return __all_sync(0xffffffffu, mbar_wait(bar, parity, ctl, code));
+            };
+            bool ok = wait_all(&ctl->q_full, 0, 2);
             // Operand descriptors differ from stage to stage and from one 16-deep step to the next only in
-            // their address field (bytes / 16): built once, carried along by additions (this thread's loop
-            // bounds how fast a CTA can issue, see gemm_tcgen05.cu).
+            // their address field (bytes / 16): built once, carried along by additions.
             const uint64_t q_desc = umma_desc(smem_u32(q_s), 16, 1024), k_desc = umma_desc(smem_u32(k_s), 16, 1024);
             const uint64_t v_desc = umma_desc(smem_u32(v_s), BN * 128, 1024);
             auto issue_s = [&](int i) {                       // S_i = Q K_i^T into S buffer i & 1
                 const int s = i % STAGES;
                 const uint64_t kd = k_desc + (uint64_t)(s * (KV_TILE >> 4));
                 const uint32_t s_tmem = tmem_base + S_COL + (uint32_t)((i & 1) * BN);
+                if (elect_one()) {
 #pragma unroll
-                for (int k = 0; k < HD / 16; k++) {
-                    const uint32_t sb = k / 4, kk = k % 4;
-                    umma(s_tmem, q_desc + (uint64_t)((sb * (BM * 128) + kk * 32) >> 4),
-                         kd + (uint64_t)((sb * (BN * 128) + kk * 32) >> 4), idesc_s, k > 0 ? 1u : 0u);
+                    for (int k = 0; k < HD / 16; k++) {
+                        const uint32_t sb = k / 4, kk = k % 4;
+                        umma(s_tmem, q_desc + (uint64_t)((sb * (BM * 128) + kk * 32) >> 4),
+                             kd + (uint64_t)((sb * (BN * 128) + kk * 32) >> 4), idesc_s, k > 0 ? 1u : 0u);
+                    }
+                    umma_commit(&ctl->s_full[i & 1]);
+                    umma_commit(&ctl->k_empty[s]);           // K_i is no longer needed
                 }
-                umma_commit(&ctl->s_full[i & 1]);
-                umma_commit(&ctl->k_empty[s]);               // K_i is no longer needed
+                __syncwarp();
             };
             if (ok && n_blocks > 0) {
-                ok = mbar_wait(&ctl->k_full[0], 0, ctl, 3);
+                ok = wait_all(&ctl->k_full[0], 0, 3);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 if (ok) issue_s(0);
             }
@@ -316,29 +331,32 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 if (i + 1 < n_blocks) {
                     // S buffer (i + 1) & 1 held block i - 1, read before P_{i-1} was signalled
                     const int s1 = (i + 1) % STAGES;
-                    ok = mbar_wait(&ctl->k_full[s1], (uint32_t)((i + 1) / STAGES) & 1u, ctl, 3);
+                    ok = wait_all(&ctl->k_full[s1], (uint32_t)((i + 1) / STAGES) & 1u, 3);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     issue_s(i + 1);
                 }
-                // P_i is in shared memory, S_i has been read, O has been rescaled if it had to be
-                ok = mbar_wait(&ctl->p_ready[i & 1], (uint32_t)(i >> 1) & 1u, ctl, 4);
+                // P_i is in tensor memory, S_i has been read, O has been rescaled if it had to be
+                ok = wait_all(&ctl->p_ready[i & 1], (uint32_t)(i >> 1) & 1u, 4);
                 if (!ok) break;
                 const int s = i % STAGES;
-                ok = mbar_wait(&ctl->v_full[s], (uint32_t)(i / STAGES) & 1u, ctl, 5);
+                ok = wait_all(&ctl->v_full[s], (uint32_t)(i / STAGES) & 1u, 5);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint64_t vd = v_desc + (uint64_t)(s * (KV_TILE >> 4));
                 // P_i sits in the first 32 columns of S buffer i & 1: 16 keys = 8 columns per instruction
                 const uint32_t p_tmem = tmem_base + S_COL + (uint32_t)((i & 1) * BN);
+                if (elect_one()) {
 #pragma unroll
-                for (int k = 0; k < BN / 16; k++) {
-                    umma_ts(tmem_base + O_COL, p_tmem + (uint32_t)(k * 8), vd + (uint64_t)((k * (16 * 128)) >> 4), idesc_o,
-                            (i > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BN / 16; k++) {
+                        umma_ts(tmem_base + O_COL, p_tmem + (uint32_t)(k * 8), vd + (uint64_t)((k * (16 * 128)) >> 4), idesc_o,
+                                (i > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&ctl->pv_done);
+                    umma_commit(&ctl->v_empty[s]);           // V_i is no longer needed
+                    if (i == n_blocks - 1) umma_commit(&ctl->o_done);   // O is complete
                 }
-                umma_commit(&ctl->pv_done);
-                umma_commit(&ctl->v_empty[s]);               // V_i is no longer needed
-                if (i == n_blocks - 1) umma_commit(&ctl->o_done);   // O is complete
+                __syncwarp();
             }
         }
     } else {
@@ -361,16 +379,24 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             tmem_ld_wait();
             const int key0 = (j_lo + i) * BN;
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-            // a block that lies wholly before this row's position and inside its window needs no mask
-            const bool whole = valid && key0 + BN - 1 <= pos && (a.window <= 0 || key0 > pos - a.window);
-            if (whole) {
+            // A block that lies wholly before a row's position and inside its window needs no mask.  The
+            // decision is the warp's: rows past the tile's tokens (a tile of 128 rows holds 126 rows of
+            // 42 tokens x 3 heads, and a prompt's last tile fewer) take the unmasked path with whatever
+            // their scores are, since every row's maximum, sum and output are that row's own and those
+            // rows are never stored; left to each row, one such row made its warp run both paths.
+            const bool needs_mask = valid && !(key0 + BN - 1 <= pos && (a.window <= 0 || key0 > pos - a.window));
+            if (!__any_sync(0xffffffffu, needs_mask)) {
 #pragma unroll
                 for (int c = 0; c < BN; c++) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
             } else {
+                // keys key0 + c with lo <= c <= hi stay (one unsigned comparison per score)
+                const int hi = valid ? min(pos - key0, BN - 1) : -1;
+                const int lo = a.window > 0 ? max(pos - a.window + 1 - key0, 0) : 0;
+                const unsigned span = hi >= lo ? (unsigned)(hi - lo) : 0u;
+                const bool any = hi >= lo;
 #pragma unroll
                 for (int c = 0; c < BN; c++) {
-                    const int key = key0 + c;
-                    const bool keep = valid && key <= pos && (a.window <= 0 || key > pos - a.window);
+                    const bool keep = any && (unsigned)(c - lo) <= span;
                     s[c] = keep ? s[c] : -INFINITY;
                     mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
                 }

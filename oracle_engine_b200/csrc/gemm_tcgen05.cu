@@ -49,6 +49,15 @@ struct SharedCtl {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
+// True in exactly one lane of a converged warp.  The TMA and MMA roles are run by whole warps
+// that stay converged, and this lane issues: inside `if (lane == 0)` every operand of every
+// copy and instruction (descriptors, coordinates, barrier addresses) went through that one
+// lane's registers, which cost more per k-block than the tensor cores needed.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -406,7 +415,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // The weight operand (A when swapped, else B) does not depend on earlier kernels:
         // the first stages' weight tiles are requested before pdl_wait(), the activation
         // tiles after it.
-        if (lane == 0) {
+        {
             int s = 0;                                          // the ring's next stage, over all work items
             uint32_t phase = 0;                                 // and how often the ring has wrapped (mod 2)
             bool waited = false, ok = true;
@@ -417,47 +426,57 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 int i = 0;
                 if (!waited) {
                     const int first = min(n_kb, g.stages);
-                    for (; i < first; i++) {
-                        uint8_t* a_dst = smem + (size_t)i * stage_bytes;
-                        mbar_expect_tx(&ctl->full[i], stage_tx);
-                        for (int h = 0; h < g.atoms; h++) {
-                            if (g.swap) tma_load_2d(a_dst + h * A_TILE_BYTES, &map_a, &ctl->full[i], (kb0 + i) * kb_elems + h * BLOCK_K, tile_a * BLOCK_M);
-                            else tma_load_2d(a_dst + b_off + h * b_atom_bytes, &map_b, &ctl->full[i], (kb0 + i) * kb_elems + h * BLOCK_K, tile_b * g.n_tile);
+                    if (elect_one()) {
+                        for (int j = 0; j < first; j++) {
+                            uint8_t* a_dst = smem + (size_t)j * stage_bytes;
+                            mbar_expect_tx(&ctl->full[j], stage_tx);
+                            for (int h = 0; h < g.atoms; h++) {
+                                if (g.swap) tma_load_2d(a_dst + h * A_TILE_BYTES, &map_a, &ctl->full[j], (kb0 + j) * kb_elems + h * BLOCK_K, tile_a * BLOCK_M);
+                                else tma_load_2d(a_dst + b_off + h * b_atom_bytes, &map_b, &ctl->full[j], (kb0 + j) * kb_elems + h * BLOCK_K, tile_b * g.n_tile);
+                            }
                         }
                     }
+                    __syncwarp();
                     pdl_wait();
                     waited = true;
-                    for (int j = 0; j < first; j++) {
-                        uint8_t* a_dst = smem + (size_t)j * stage_bytes;
-                        for (int h = 0; h < g.atoms; h++) {
-                            if (g.swap) tma_load_2d(a_dst + b_off + h * b_atom_bytes, &map_b, &ctl->full[j], (kb0 + j) * kb_elems + h * BLOCK_K, tile_b * g.n_tile);
-                            else tma_load_2d(a_dst + h * A_TILE_BYTES, &map_a, &ctl->full[j], (kb0 + j) * kb_elems + h * BLOCK_K, tile_a * BLOCK_M);
+                    if (elect_one()) {
+                        for (int j = 0; j < first; j++) {
+                            uint8_t* a_dst = smem + (size_t)j * stage_bytes;
+                            for (int h = 0; h < g.atoms; h++) {
+                                if (g.swap) tma_load_2d(a_dst + b_off + h * b_atom_bytes, &map_b, &ctl->full[j], (kb0 + j) * kb_elems + h * BLOCK_K, tile_b * g.n_tile);
+                                else tma_load_2d(a_dst + h * A_TILE_BYTES, &map_a, &ctl->full[j], (kb0 + j) * kb_elems + h * BLOCK_K, tile_a * BLOCK_M);
+                            }
                         }
                     }
+                    __syncwarp();
+                    i = first;
                     s = first == g.stages ? 0 : first;          // the ring's next stage and its phase
                     phase = first == g.stages ? 1u : 0u;
                 }
                 // The loop of one k-block is short on purpose (no division, addresses carried along):
-                // the thread that runs it is one of two whose rate bounds what a CTA streams.
+                // the warp that runs it is one of two whose rate bounds what a CTA streams.
                 const int row_a = tile_a * BLOCK_M, row_b = tile_b * g.n_tile;
                 int col = (kb0 + i) * kb_elems;
                 for (; i < n_kb; i++, col += kb_elems) {
-                    if (!mbar_wait(&ctl->empty[s], phase ^ 1u, ctl, 1)) { ok = false; break; }
-                    uint8_t* a_dst = smem + (size_t)s * stage_bytes;
-                    mbar_expect_tx(&ctl->full[s], stage_tx);
-                    tma_load_2d(a_dst, &map_a, &ctl->full[s], col, row_a);
-                    tma_load_2d(a_dst + b_off, &map_b, &ctl->full[s], col, row_b);
-                    if (g.atoms == 2) {
-                        tma_load_2d(a_dst + A_TILE_BYTES, &map_a, &ctl->full[s], col + BLOCK_K, row_a);
-                        tma_load_2d(a_dst + b_off + b_atom_bytes, &map_b, &ctl->full[s], col + BLOCK_K, row_b);
+                    if (!__all_sync(0xffffffffu, mbar_wait(&ctl->empty[s], phase ^ 1u, ctl, 1))) { ok = false; break; }
+                    if (elect_one()) {
+                        uint8_t* a_dst = smem + (size_t)s * stage_bytes;
+                        mbar_expect_tx(&ctl->full[s], stage_tx);
+                        tma_load_2d(a_dst, &map_a, &ctl->full[s], col, row_a);
+                        tma_load_2d(a_dst + b_off, &map_b, &ctl->full[s], col, row_b);
+                        if (g.atoms == 2) {
+                            tma_load_2d(a_dst + A_TILE_BYTES, &map_a, &ctl->full[s], col + BLOCK_K, row_a);
+                            tma_load_2d(a_dst + b_off + b_atom_bytes, &map_b, &ctl->full[s], col + BLOCK_K, row_b);
+                        }
                     }
+                    __syncwarp();
                     if (++s == g.stages) { s = 0; phase ^= 1u; }
                 }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issue ----------------
-        if (lane == 0) {
+        {
             const uint32_t idesc = umma_idesc(BLOCK_M, g.n_tile);
             int lt = 0;
             int s = 0;                                          // the ring's next stage and its phase, over all work items
@@ -474,27 +493,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int n_kb = item.n_kb;
                 const int buf = lt & 1;
                 // the epilogue must have read this accumulator (two work items ago)
-                if (!mbar_wait(&ctl->tmem_empty[buf], ((uint32_t)(lt >> 1) & 1u) ^ 1u, ctl, 4)) break;
+                if (!__all_sync(0xffffffffu, mbar_wait(&ctl->tmem_empty[buf], ((uint32_t)(lt >> 1) & 1u) ^ 1u, ctl, 4))) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmem_d = tmem_base + (uint32_t)(buf * g.n_tile);
                 for (int i = 0; i < n_kb; i++) {
-                    if (!mbar_wait(&ctl->full[s], phase, ctl, 2)) { ok = false; break; }
+                    if (!__all_sync(0xffffffffu, mbar_wait(&ctl->full[s], phase, ctl, 2))) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint64_t a_desc = desc0 + (uint64_t)s * stage_step, b_desc = a_desc + b_step;
-                    umma_bf16(tmem_d, a_desc, b_desc, idesc, i > 0 ? 1u : 0u);
+                    if (elect_one()) {
+                        const uint64_t a_desc = desc0 + (uint64_t)s * stage_step, b_desc = a_desc + b_step;
+                        umma_bf16(tmem_d, a_desc, b_desc, idesc, i > 0 ? 1u : 0u);
 #pragma unroll
-                    for (int k = 1; k < BLOCK_K / UMMA_K; k++)
-                        umma_bf16(tmem_d, a_desc + (uint64_t)(k * UMMA_K * 2 >> 4), b_desc + (uint64_t)(k * UMMA_K * 2 >> 4), idesc, 1u);
-                    if (g.atoms == 2) {
+                        for (int k = 1; k < BLOCK_K / UMMA_K; k++)
+                            umma_bf16(tmem_d, a_desc + (uint64_t)(k * UMMA_K * 2 >> 4), b_desc + (uint64_t)(k * UMMA_K * 2 >> 4), idesc, 1u);
+                        if (g.atoms == 2) {
 #pragma unroll
-                        for (int k = 0; k < BLOCK_K / UMMA_K; k++)
-                            umma_bf16(tmem_d, a_desc + a_atom + (uint64_t)(k * UMMA_K * 2 >> 4),
-                                      b_desc + b_atom + (uint64_t)(k * UMMA_K * 2 >> 4), idesc, 1u);
+                            for (int k = 0; k < BLOCK_K / UMMA_K; k++)
+                                umma_bf16(tmem_d, a_desc + a_atom + (uint64_t)(k * UMMA_K * 2 >> 4),
+                                          b_desc + b_atom + (uint64_t)(k * UMMA_K * 2 >> 4), idesc, 1u);
+                        }
+                        umma_commit(&ctl->empty[s]);      // frees the stage when these MMAs have read it
                     }
-                    umma_commit(&ctl->empty[s]);          // frees the stage when these MMAs have read it
+                    __syncwarp();
                     if (++s == g.stages) { s = 0; phase ^= 1u; }
                 }
-                umma_commit(&ctl->tmem_full[buf]);        // this accumulator is complete
+                if (ok) {
+                    if (elect_one()) umma_commit(&ctl->tmem_full[buf]);   // this accumulator is complete
+                    __syncwarp();
+                }
             }
         }
     } else {

@@ -152,6 +152,14 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
         : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// True in exactly one lane of a converged warp.  The warp stays converged around the
+// instructions that lane issues, so their operands (descriptors, coordinates, barrier
+// addresses) can stay in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
 
 __device__ __forceinline__ float silu_mul(float gate, float up) { return (gate / (1.f + expf(-gate))) * up; }
 __device__ __forceinline__ void red_add(float* p, float v) { asm volatile("red.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory"); }
@@ -248,30 +256,33 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     pdl_launch_dependents();
     if (warp == 0) {
         // ---------------- TMA producer (both CTAs) ----------------
-        if (lane == 0) {
-            pdl_wait();                                    // the activations come from the kernel before
-            int s = 0;                                     // the ring's next stage and its phase, over all tiles
-            uint32_t phase = 0;
-            bool ok = true;
-            for (int w = cluster_id; w < n_work && ok; w += n_clusters) {
-                const int tile_n = w / g.tiles_m, tile_m = w % g.tiles_m;
-                const int a_row = tile_m * (2 * BLOCK_M) + (int)rank * BLOCK_M;
-                const int b_row = tile_n * g.n_tile + (int)rank * b_half_rows;
-                // a short loop per k-block (no division, addresses carried along): see gemm_tcgen05.cu
-                for (int i = 0, col = 0; i < n_kb; i++, col += BLOCK_K) {
-                    if (!mbar_wait(&ctl->empty[s], phase ^ 1u, ctl, 1)) { ok = false; break; }
+        // The whole warp runs the loop and waits; one elected lane issues the copies.
+        pdl_wait();                                        // the activations come from the kernel before
+        int s = 0;                                         // the ring's next stage and its phase, over all tiles
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int w = cluster_id; w < n_work && ok; w += n_clusters) {
+            const int tile_n = w / g.tiles_m, tile_m = w % g.tiles_m;
+            const int a_row = tile_m * (2 * BLOCK_M) + (int)rank * BLOCK_M;
+            const int b_row = tile_n * g.n_tile + (int)rank * b_half_rows;
+            // a short loop per k-block (no division, addresses carried along): see gemm_tcgen05.cu
+            for (int i = 0, col = 0; i < n_kb; i++, col += BLOCK_K) {
+                if (!__all_sync(0xffffffffu, mbar_wait(&ctl->empty[s], phase ^ 1u, ctl, 1))) { ok = false; break; }
+                if (elect_one()) {
                     uint8_t* a_dst = smem + (size_t)s * stage_bytes;
                     if (leader) mbar_expect_tx(&ctl->full[s], (uint32_t)(2 * (A_TILE_BYTES + b_bytes)));
                     const uint32_t bar = in_leader(&ctl->full[s]);
                     tma_load_pair(a_dst, &map_a, bar, col, a_row);
                     tma_load_pair(a_dst + A_TILE_BYTES, &map_b, bar, col, b_row);
-                    if (++s == g.stages) { s = 0; phase ^= 1u; }
                 }
+                __syncwarp();
+                if (++s == g.stages) { s = 0; phase ^= 1u; }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issue (leader only) ----------------
-        if (lane == 0 && leader) {
+        // The whole warp runs the loop and waits; one elected lane issues the instructions.
+        if (leader) {
             const uint32_t idesc = umma_idesc(2 * BLOCK_M, g.n_tile);
             int lt = 0;
             int s = 0;
@@ -283,21 +294,27 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             for (int w = cluster_id; w < n_work && ok; w += n_clusters, lt++) {
                 const int buf = lt & 1;
                 // both CTAs' epilogues have read this accumulator (two tiles ago)
-                if (!mbar_wait(&ctl->tmem_empty[buf], ((uint32_t)(lt >> 1) & 1u) ^ 1u, ctl, 4)) break;
+                if (!__all_sync(0xffffffffu, mbar_wait(&ctl->tmem_empty[buf], ((uint32_t)(lt >> 1) & 1u) ^ 1u, ctl, 4))) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmem_d = tmem_base + (uint32_t)(buf * g.n_tile);
                 for (int i = 0; i < n_kb; i++) {
-                    if (!mbar_wait(&ctl->full[s], phase, ctl, 2)) { ok = false; break; }
+                    if (!__all_sync(0xffffffffu, mbar_wait(&ctl->full[s], phase, ctl, 2))) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint64_t a_desc = desc0 + (uint64_t)s * stage_step, b_desc = a_desc + b_step;
-                    umma_pair(tmem_d, a_desc, b_desc, idesc, i > 0 ? 1u : 0u);
+                    if (elect_one()) {
+                        const uint64_t a_desc = desc0 + (uint64_t)s * stage_step, b_desc = a_desc + b_step;
+                        umma_pair(tmem_d, a_desc, b_desc, idesc, i > 0 ? 1u : 0u);
 #pragma unroll
-                    for (int k = 1; k < BLOCK_K / UMMA_K; k++)
-                        umma_pair(tmem_d, a_desc + (uint64_t)(k * UMMA_K * 2 >> 4), b_desc + (uint64_t)(k * UMMA_K * 2 >> 4), idesc, 1u);
-                    umma_commit_both(&ctl->empty[s]);       // frees the stage in both CTAs
+                        for (int k = 1; k < BLOCK_K / UMMA_K; k++)
+                            umma_pair(tmem_d, a_desc + (uint64_t)(k * UMMA_K * 2 >> 4), b_desc + (uint64_t)(k * UMMA_K * 2 >> 4), idesc, 1u);
+                        umma_commit_both(&ctl->empty[s]);   // frees the stage in both CTAs
+                    }
+                    __syncwarp();
                     if (++s == g.stages) { s = 0; phase ^= 1u; }
                 }
-                if (ok) umma_commit_both(&ctl->tmem_full[buf]);
+                if (ok) {
+                    if (elect_one()) umma_commit_both(&ctl->tmem_full[buf]);
+                    __syncwarp();
+                }
             }
         }
     } else {

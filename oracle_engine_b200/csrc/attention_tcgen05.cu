@@ -404,7 +404,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             const float m_new = fmaxf(m_run, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2);
             if (i == 0) {
                 m_run = m_new;
-            } else if (__any_sync(0xffffffffu, m_new > m_run + RESCALE_STEP)) {
+            } else if (__any_sync(0xffffffffu, valid && m_new > m_run + RESCALE_STEP)) {
+                // (only the tile's own rows vote: the scores of the rows past them are whatever shared memory held)
                 // P_{i-1} V_{i-1} must have been added to O before O is rescaled.  S_i is complete, so
                 // P_{i-2} V_{i-2} (issued before it) is too: the parity cannot be that of an earlier block
                 ok = mbar_wait(&ctl->pv_done, (uint32_t)(i - 1) & 1u, ctl, 7);

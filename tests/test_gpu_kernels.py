@@ -32,10 +32,12 @@ def test_embed_rmsnorm_swiglu_gather(dtype):
     ops.embed_gather(xb, table, bad, err)
     assert err.item() == 1 and torch.equal(xb[1], torch.zeros(D, device=DEV)) and torch.equal(xb[0], table.float()[3])
 
-    for D2, eps in ((200, 1e-5), (3, 1e-6), (1031, 1e-2)):
-        xr = _rand(5, D2, scale=3.0, seed=1)
+    # few rows: a block per row; from 1,024 rows of up to 4,096 columns (a prompt step) bfloat16 takes a warp per row
+    for rows, D2, eps in ((5, 200, 1e-5), (5, 3, 1e-6), (5, 1031, 1e-2), (1024, 200, 1e-5), (1031, 3076, 1e-6),
+                          (1100, 4096, 1e-5), (1025, 2052, 1e-5), (1024, 4100, 1e-5), (1030, 1031, 1e-5)):
+        xr = _rand(rows, D2, scale=3.0, seed=1)
         w = _rand(D2, seed=2)
-        y = torch.empty(5, D2, dtype=dtype, device=DEV)
+        y = torch.empty(rows, D2, dtype=dtype, device=DEV)
         ops.rmsnorm(y, xr, w, eps)
         want = pl.rms_norm(xr.double().cpu(), w.double().cpu(), eps)
         tol = 1e-5 if dtype == torch.float32 else 2e-2

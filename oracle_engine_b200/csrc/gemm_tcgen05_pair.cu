@@ -51,7 +51,8 @@ struct PairArgs {
     void* C;
     long long ldc;
     int M, N, K;
-    int n_tile;                    // columns of the pair's tile, multiple of 32, <= 256
+    int n_tile;                    // columns of the pair's tile, multiple of 16, <= 256
+    int acc_cols;                  // tensor-memory columns between the two accumulators (n_tile rounded up to 32)
     int stages;
     int out_kind;                  // 0 bf16 store, 1 float32 store, 2 float32 accumulate, 3 bf16 silu(gate)*up
     int tiles_m, tiles_n;          // tiles of 256 rows and of n_tile columns
@@ -234,7 +235,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int n_work = g.tiles_m * g.tiles_n;
     const int n_kb = (g.K + BLOCK_K - 1) / BLOCK_K;
     uint32_t tmem_cols = 32;
-    while ((int)tmem_cols < 2 * g.n_tile) tmem_cols <<= 1;          // two accumulators
+    while ((int)tmem_cols < 2 * g.acc_cols) tmem_cols <<= 1;        // two accumulators
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < g.stages; s++) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
@@ -296,7 +297,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 // both CTAs' epilogues have read this accumulator (two tiles ago)
                 if (!__all_sync(0xffffffffu, mbar_wait(&ctl->tmem_empty[buf], ((uint32_t)(lt >> 1) & 1u) ^ 1u, ctl, 4))) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * g.n_tile);
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * g.acc_cols);
                 for (int i = 0; i < n_kb; i++) {
                     if (!__all_sync(0xffffffffu, mbar_wait(&ctl->full[s], phase, ctl, 2))) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -330,14 +331,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             if (!mbar_wait(&ctl->tmem_full[buf], (uint32_t)(lt >> 1) & 1u, ctl, 3)) break;
             if (first) { pdl_wait(); first = false; }     // before the first access to C
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * g.n_tile);
-            for (int c0 = 0; c0 < g.n_tile; c0 += 32) {    // n_tile is a multiple of 32
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * g.acc_cols);
+            for (int c0 = 0; c0 < g.n_tile; c0 += 32) {    // n_tile is a multiple of 16: the last group may be half
                 uint32_t r[2][16];
+                const bool two = c0 + 16 < g.n_tile;
                 tmem_ld16(taddr + (uint32_t)c0, r[0]);
-                tmem_ld16(taddr + (uint32_t)(c0 + 16), r[1]);
+                if (two) tmem_ld16(taddr + (uint32_t)(c0 + 16), r[1]);
                 tmem_ld_wait();
 #pragma unroll
                 for (int h = 0; h < 2; h++) {
+                    if (h == 1 && !two) break;
                     float v[16];
 #pragma unroll
                     for (int j = 0; j < 16; j++) v[j] = __uint_as_float(r[h][j]);
@@ -431,21 +434,25 @@ int oe_gemm_pair_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K
     PairArgs g;
     g.C = C; g.ldc = ldc; g.M = M; g.N = N; g.K = K; g.out_kind = out_kind;
     g.tiles_m = (M + 2 * BLOCK_M - 1) / (2 * BLOCK_M);
-    // The tile width with the shortest rounds of clusters.  A k-block of a pair takes about 414,
-    // 420, 433, 450 and 475 ns at 128, 160, 192, 224 and 256 columns (measured: the width hardly
-    // matters, the number of rounds does).
+    // The tile width (a multiple of 16) with the shortest rounds of clusters at the measured time of a
+    // pair's k-block: 230, 249, 284, 310 and 365 ns from 128, 160, 192, 224 and 256 columns on, and a
+    // width between two of these costs what the one below it costs (4096^3 with every width forced,
+    // the roles as converged warps).  So 176 columns are the cheapest per column after 224..256, and
+    // 8192 -> 3072 at 2,048 tokens takes 18 x 8 tiles of 176 (1.95 rounds of 74 clusters) rather than
+    // 16 x 8 of 192 (1.73 rounds).
     int limit = 256;
-    if (max_tile >= 32 && max_tile < limit) limit = max_tile / 32 * 32;
+    if (max_tile >= 32 && max_tile < limit) limit = max_tile / 16 * 16;
     long long best = -1;
     g.n_tile = limit;
-    for (int nt = limit; nt >= 128 && nt >= 32; nt -= 32) {
+    for (int nt = limit; nt >= 128 && nt >= 32; nt -= 16) {
         const long long tiles = (long long)g.tiles_m * ((N + nt - 1) / nt);
-        const long long kb_ns = nt <= 128 ? 414 : nt <= 160 ? 420 : nt <= 192 ? 433 : nt <= 224 ? 450 : 475;
-        const long long cost = ((tiles + g_clusters - 1) / g_clusters) * kb_ns;
+        static const int kb_ns[9] = {230, 230, 230, 230, 230, 249, 284, 310, 365};
+        const long long cost = ((tiles + g_clusters - 1) / g_clusters) * kb_ns[nt / 32];
         if (best < 0 || cost < best) { best = cost; g.n_tile = nt; }
     }
-    if (max_tile <= -32 && max_tile >= -256 && max_tile % 32 == 0) g.n_tile = -max_tile;     // measurements: this width
-    if (N < g.n_tile) g.n_tile = (N + 31) / 32 * 32;
+    if (max_tile <= -32 && max_tile >= -256 && max_tile % 16 == 0) g.n_tile = -max_tile;     // measurements: this width
+    if (N < g.n_tile) g.n_tile = (N + 15) / 16 * 16;
+    g.acc_cols = (g.n_tile + 31) / 32 * 32;
     g.tiles_n = (N + g.n_tile - 1) / g.n_tile;
     const long long n_work = (long long)g.tiles_m * g.tiles_n;
     if (n_work > 2147483647LL) return OE_ERR_UNSUPPORTED;

@@ -154,9 +154,11 @@ def test_gemm_tcgen05(M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K,max_tile", [(300, 1000, 520, 128), (256, 256, 64, 128), (1000, 264, 72, 0), (513, 3072, 1024, 0),
-                                            (2048, 640, 200, 0), (129, 40, 8, 0)])
+                                            (2048, 640, 200, 0), (129, 40, 8, 0), (600, 3000, 320, -176),
+                                            (300, 520, 136, -240), (512, 300, 64, -144), (2048, 3072, 256, 0)])
 def test_gemm_pair(M, N, K, max_tile):
-    """The two-SM kernel: row and column edges, both halves of the weight tile, all epilogues."""
+    """The two-SM kernel: row and column edges, both halves of the weight tile, all epilogues; tile widths
+    that are odd multiples of 16 (max_tile < 0 forces a width), whose last group of columns is half."""
     from oracle_engine_b200.csrc import ops_tc
     with ops_tc.knobs(pair_max_tile=max_tile):
         a, w = _rand(M, K, dtype=torch.bfloat16, scale=0.5, seed=1), _rand(N, K, dtype=torch.bfloat16, scale=0.5, seed=2)

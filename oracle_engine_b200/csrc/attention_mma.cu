@@ -464,8 +464,9 @@ attn_decode_warps_kernel(const AttnArgs a) {
 
     // this warp's first tiles are requested before anything else
     const int n_my = hp_lo + warp <= hp_hi ? (hp_hi - hp_lo - warp) / NW + 1 : 0;
+    // (the whole ring: nothing is being multiplied yet)
 #pragma unroll
-    for (int pre = 0; pre < ST - 1; pre++) {
+    for (int pre = 0; pre < ST; pre++) {
         if (pre < n_my) {
             const int hp = hp_lo + warp + pre * NW;
             uint8_t* st = mine + (size_t)pre * WARP_STAGE_BYTES;
@@ -477,6 +478,44 @@ attn_decode_warps_kernel(const AttnArgs a) {
     // kernel of this step writes (the stale row of the new token is replaced below): those loads
     // overlap the end of the kernel before this one.  The new token's q, k and v come from that kernel.
     if (own_kv) pdl_wait();
+
+    // The warp that will meet the new token's tile asks for that token's k and v now, with q, rotates
+    // the key and stores both in the cache; the values wait in registers for the tile.
+    constexpr int NEW_IT = (HD / 2 + 31) / 32;
+    const bool owner = a.cache_w != nullptr && n_my > 0 && (hp_hi - hp_lo - warp) % NW == 0;
+    bf16 new_k0[NEW_IT], new_k1[NEW_IT], new_v0[NEW_IT], new_v1[NEW_IT];
+    if (owner) {
+        const bf16* krow = a.q + packed0 * a.q_stride + (size_t)(a.H + kvh) * HD;
+        const bf16* vrow = krow + (size_t)a.KVH * HD;
+        float kf0[NEW_IT], kf1[NEW_IT], cs[NEW_IT], sn[NEW_IT];
+#pragma unroll
+        for (int u = 0; u < NEW_IT; u++) {
+            const int d = lane + u * 32;
+            if (d < HD / 2) {
+                kf0[u] = __bfloat162float(krow[d]); kf1[u] = __bfloat162float(krow[d + HD / 2]);
+                new_v0[u] = vrow[d]; new_v1[u] = vrow[d + HD / 2];
+                cs[u] = a.cos_tab != nullptr ? a.cos_tab[(size_t)pos * (HD / 2) + d] : 1.f;
+                sn[u] = a.cos_tab != nullptr ? a.sin_tab[(size_t)pos * (HD / 2) + d] : 0.f;
+            }
+        }
+        const size_t page = (size_t)trow[pos / BN];
+        bf16* kc = a.cache_w + ((page * 2 + 0) * a.KVH + kvh) * (size_t)(BN * HD) + (size_t)(pos % BN) * HD;
+        bf16* vc = a.cache_w + ((page * 2 + 1) * a.KVH + kvh) * (size_t)(BN * HD) + (size_t)(pos % BN) * HD;
+#pragma unroll
+        for (int u = 0; u < NEW_IT; u++) {
+            const int d = lane + u * 32;
+            if (d < HD / 2) {
+                float k0 = kf0[u], k1 = kf1[u];
+                if (a.cos_tab != nullptr) {
+                    const float r0 = k0 * cs[u] - k1 * sn[u], r1 = k0 * sn[u] + k1 * cs[u];
+                    k0 = r0; k1 = r1;
+                }
+                new_k0[u] = __float2bfloat16_rn(k0); new_k1[u] = __float2bfloat16_rn(k1);
+                kc[d] = new_k0[u]; kc[d + HD / 2] = new_k1[u];
+                vc[d] = new_v0[u]; vc[d + HD / 2] = new_v1[u];
+            }
+        }
+    }
 
     bool valid[2];
     int head[2];
@@ -530,39 +569,20 @@ attn_decode_warps_kernel(const AttnArgs a) {
         const int hp = hp_lo + warp + it * NW;
         uint8_t* ks_cur = mine + (size_t)stage * WARP_STAGE_BYTES;
         uint8_t* vs_cur = ks_cur + TB_BYTES;
-        if (it + ST - 1 < n_my) {
-            // into the stage that the iteration before this one has read
-            const int fill = stage == 0 ? ST - 1 : stage - 1;
-            uint8_t* nxt = mine + (size_t)fill * WARP_STAGE_BYTES;
-            const int hn = hp + (ST - 1) * NW;
-            load_half_page(nxt, nxt + TB_BYTES, a.cache, trow[hn >> 1], hn & 1, kvh, a.KVH, lane);
-        }
-        cp_async_commit();
         cp_async_wait<ST - 1>();
-        stage = stage + 1 == ST ? 0 : stage + 1;
         __syncwarp();
         if (hp == hp_hi && a.cache_w != nullptr) {
-            // this warp holds the tile of the new token: rotate its key, store key and value in the
-            // cache, and put them into the staged tile as well
+            // the tile of the new token: its row in the cache was stale when the tile was requested
             const int r = pos % TB;
-            const bf16* krow = a.q + packed0 * a.q_stride + (size_t)(a.H + kvh) * HD;
-            const bf16* vrow = krow + (size_t)a.KVH * HD;
-            const size_t page = (size_t)trow[pos / BN];
-            bf16* kc = a.cache_w + ((page * 2 + 0) * a.KVH + kvh) * (size_t)(BN * HD) + (size_t)(pos % BN) * HD;
-            bf16* vc = a.cache_w + ((page * 2 + 1) * a.KVH + kvh) * (size_t)(BN * HD) + (size_t)(pos % BN) * HD;
             bf16* ksm = (bf16*)(ks_cur + r * ROW_BYTES);
             bf16* vsm = (bf16*)(vs_cur + r * ROW_BYTES);
-            for (int d = lane; d < HD / 2; d += 32) {
-                float k0 = __bfloat162float(krow[d]), k1 = __bfloat162float(krow[d + HD / 2]);
-                if (a.cos_tab != nullptr) {
-                    const float c = a.cos_tab[(size_t)pos * (HD / 2) + d], sn = a.sin_tab[(size_t)pos * (HD / 2) + d];
-                    const float r0 = k0 * c - k1 * sn, r1 = k0 * sn + k1 * c;
-                    k0 = r0; k1 = r1;
+#pragma unroll
+            for (int u = 0; u < NEW_IT; u++) {
+                const int d = lane + u * 32;
+                if (d < HD / 2) {
+                    ksm[d] = new_k0[u]; ksm[d + HD / 2] = new_k1[u];
+                    vsm[d] = new_v0[u]; vsm[d + HD / 2] = new_v1[u];
                 }
-                const bf16 b0 = __float2bfloat16_rn(k0), b1 = __float2bfloat16_rn(k1);
-                const bf16 v0 = vrow[d], v1 = vrow[d + HD / 2];
-                kc[d] = b0; kc[d + HD / 2] = b1; ksm[d] = b0; ksm[d + HD / 2] = b1;
-                vc[d] = v0; vc[d + HD / 2] = v1; vsm[d] = v0; vsm[d + HD / 2] = v1;
             }
             __syncwarp();
         }
@@ -649,7 +669,13 @@ attn_decode_warps_kernel(const AttnArgs a) {
                 mma_bf16(oacc[2 * dp + 1], pa, vb[dp & 1][2], vb[dp & 1][3]);
             }
         }
-        __syncwarp();                                       // the next iteration refills this stage
+        __syncwarp();                                       // every lane has read the stage: refill it
+        if (it + ST < n_my) {
+            const int hn = hp + ST * NW;
+            load_half_page(ks_cur, vs_cur, a.cache, trow[hn >> 1], hn & 1, kvh, a.KVH, lane);
+        }
+        cp_async_commit();
+        stage = stage + 1 == ST ? 0 : stage + 1;
     }
     cp_async_wait<0>();
 #pragma unroll

@@ -137,12 +137,16 @@ class StepBuffers:
         self.sizes = sizes
         self._copied = torch.cuda.Event() if torch.cuda.is_available() else None
         self._pending = False
+        # the sections as numpy views of the staging buffer and as device views, made once
+        self._host_views = [self.host[o: o + n].numpy() for o, n in zip(self.offsets, sizes)]
+        self._dev_views = [self.dev[o: o + n] for o, n in zip(self.offsets, sizes)]
+        self._dev_tables = [self._dev_views[8 + j].view(*shape) for j, shape in enumerate(self.table_shapes)]
 
     def _host_view(self, i):
-        return self.host[self.offsets[i]: self.offsets[i] + self.sizes[i]].numpy()
+        return self._host_views[i]
 
     def _dev_view(self, i):
-        return self.dev[self.offsets[i]: self.offsets[i] + self.sizes[i]]
+        return self._dev_views[i]
 
     def upload(self, plan: StepPlan, tables: list) -> StepContext:
         """Fills the staging buffer from the plan and copies it to the device (one
@@ -182,8 +186,8 @@ class StepBuffers:
         return self.total * 4
 
     def context(self, plan: StepPlan) -> StepContext:
-        v = [self._dev_view(i) for i in range(8)]
-        tabs = [self._dev_view(8 + j).view(*self.table_shapes[j]) for j in range(len(self.table_shapes))]
+        v = self._dev_views
+        tabs = list(self._dev_tables)
         return StepContext(
             n_tokens=self.n_tokens, n_seqs=self.n_seqs, n_want=self.n_want, token_ids=v[0], tok_seq=v[1],
             tok_pos=v[2], seq_slot=v[3], seq_start=v[4], seq_qlen=v[5], cu_q=v[6], want_rows=v[7], tables=tabs,

@@ -152,7 +152,7 @@ def workload(shape: str, kind: str, batch: int, steps: int):
     return [PROMPT_LEN] * batch, steps, context
 
 
-def time_decode(engine, lengths, steps, warmup, vocab, regions=5):
+def time_decode(engine, lengths, steps, warmup, vocab, regions=5, settle_ms=0):
     """Device time of exactly `steps` decode steps (step function + greedy token choice on the
     device) after `warmup` untimed ones, for a batch whose prompts have the given lengths.  The
     whole thing (fresh slots, the prompts in one step, warm-up, the timed steps) is done `regions`
@@ -173,6 +173,9 @@ def time_decode(engine, lengths, steps, warmup, vocab, regions=5):
         row_slot = torch.tensor(slots, dtype=torch.int32, device=engine.device)
         try:
             engine.step([SequenceStep(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+            if settle_ms > 0:
+                torch.cuda.synchronize()
+                time.sleep(settle_ms / 1e3)
 
             def one(i):
                 logits = engine.step([SequenceStep(s, [feed[b][i]], [0]) for b, s in enumerate(slots)])
@@ -413,6 +416,8 @@ def main():
                     help="fixed: --batch prompts of 512 tokens; baseline: the workload the shape is quoted with "
                          "(1b: 16 prompts of 64..2,048 tokens, 128 steps; 8b: 32 prompts of 128..4,096 tokens, 256 steps)")
     ap.add_argument("--regions", type=int, default=5, help="timed regions of --steps steps; the median is reported")
+    ap.add_argument("--settle-ms", type=int, default=100,
+                    help="idle time between a region's prompt step and its warm-up steps (see time_decode; 0: none)")
     ap.add_argument("--profile", action="store_true",
                     help="print device time per kind of kernel of a prompt step and a decode step on standard error, "
                          "and nothing else")
@@ -448,14 +453,14 @@ def main():
         return 0
 
     with ClockSampler() as clocks:
-        dec = time_decode(engine, lengths, steps, args.warmup, cfg.vocab_size, max(1, args.regions))
+        dec = time_decode(engine, lengths, steps, args.warmup, cfg.vocab_size, max(1, args.regions), args.settle_ms)
     clock_info = clocks.summary()
     e2e = time_e2e(engine, lengths, steps, args.warmup, cfg.vocab_size)
     points = {}
     if points_wanted:
         for b in (1, 64):
             points[f"decode_b{b}"] = round(time_decode(engine, [PROMPT_LEN] * b, min(steps, 128), args.warmup,
-                                                       cfg.vocab_size, 3)["tok_s"], 1)
+                                                       cfg.vocab_size, 3, args.settle_ms)["tok_s"], 1)
     prefill = None
     if not args.no_prefill:
         pre_lengths = lengths if baseline_load else [PREFILL_TOKENS]
@@ -483,7 +488,7 @@ def main():
                    "tied_head": cfg.tie_word_embeddings,
                    "rope": "llama3 factor %g" % cfg.rope_scaling.factor,
                    "l2": "inputs larger than L2 (weights %.1f GB per step)" % (engine.model.step_bytes([]) / 1e9),
-                   "peaks": pk["source"], "workload": args.workload},
+                   "peaks": pk["source"], "workload": args.workload, "settle_ms_after_prompt": args.settle_ms},
         "regions": {"n": dec["regions"], "ms_per_step_min": round(dec["ms_min"], 4),
                     "ms_per_step_max": round(dec["ms_max"], 4), "reported": "median"},
         "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tokens/s", "ms_per_step": round(e2e["ms_per_step"], 4),

@@ -153,7 +153,10 @@ int oe_gemm_skinny_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int
     // gate/up or down starting early behind kernels that trigger at their top cost 20-50 %
     // (their very many CTAs sit on the SMs while the kernel before still needs them); with o,
     // gate/up and down starting early AND triggering late, qkv starting early and triggering at
-    // its top (the attention kernel asks for its keys meanwhile): 1.736 ms.  The caller decides.
+    // its top (the attention kernel asks for its keys meanwhile): 1.736 ms.  Varied one at a time
+    // from there (timed steps of 1.714 ms, the device idle before them): only down triggering at its
+    // top is as fast or faster (1 sequence 1.606 -> 1.577 ms); o starting early and triggering at its
+    // top: 2.44 ms.  The caller decides.
     // Warps and loads in flight per shape, from a sweep on B200 at 8 tokens: matrices with
     // very many rows do best with small CTAs, long rows with more loads in flight.
 #define OE_SKINNY_LAUNCH(NT, WARPS, UNROLL)                                                                        \

@@ -57,4 +57,6 @@ class SwiGLU(Part):
             gu = self.rt.empty(T, 2 * self.FF)
             matmul_nt(self.rt, gu, h, self.w_gu)
             ops.swiglu(a, gu)
-        matmul_nt(self.rt, residual, a, self.w_down, accumulate=True, early=START_EARLY | TRIGGER_LATE)
+        # what follows the down product is a norm (few small CTAs): it may be scheduled from the product's
+        # top (measured inside the 28-layer step, 1 / 2 / 4 / 8 sequences: 1.8 / 0.8 / 1.0 / 0 % faster)
+        matmul_nt(self.rt, residual, a, self.w_down, accumulate=True, early=START_EARLY)

@@ -255,11 +255,18 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, int row_stride,
         Vec16<T>::load(src + i, x0);
         Vec16<T>::load(src + i + half, x1);
         if (rotate) {
+            // i is a multiple of V and the table's rows are hd/2 floats: 16-byte loads
+            float c[V], s[V];
+#pragma unroll
+            for (int j = 0; j < V; j += 4) {
+                const float4 c4 = *(const float4*)(cs + i + j), s4 = *(const float4*)(sn + i + j);
+                c[j] = c4.x; c[j + 1] = c4.y; c[j + 2] = c4.z; c[j + 3] = c4.w;
+                s[j] = s4.x; s[j + 1] = s4.y; s[j + 2] = s4.z; s[j + 3] = s4.w;
+            }
 #pragma unroll
             for (int j = 0; j < V; j++) {
-                const float c = cs[i + j], s = sn[i + j];
-                y0[j] = x0[j] * c - x1[j] * s;
-                y1[j] = x0[j] * s + x1[j] * c;
+                y0[j] = x0[j] * c[j] - x1[j] * s[j];
+                y1[j] = x0[j] * s[j] + x1[j] * c[j];
             }
         } else {
 #pragma unroll
@@ -357,7 +364,7 @@ int oe_rope_kv_write_f32(float* qkv, int row_stride, const float* cos_tab, const
                          cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (hd % 2) return OE_ERR_UNSUPPORTED;
-    if ((hd / 2) % 4 == 0 && row_stride % 4 == 0 && !(((uintptr_t)qkv | (uintptr_t)cache) & 15))
+    if ((hd / 2) % 4 == 0 && row_stride % 4 == 0 && !(((uintptr_t)qkv | (uintptr_t)cache | (uintptr_t)cos_tab | (uintptr_t)sin_tab) & 15))
         return oe_launch(rope_kv_write_vec_kernel<float>, dim3(n_tokens), dim3(256), 0, st, qkv, row_stride, cos_tab, sin_tab,
                          cache, tables, max_pages, tok_seq, tok_pos, H, KVH, hd, has_kv, rotate);
     const int launch_rc = oe_launch(rope_kv_write_kernel<float>, dim3(n_tokens), dim3(256), 0, st, qkv, row_stride, cos_tab, sin_tab, cache, tables,
@@ -370,7 +377,7 @@ int oe_rope_kv_write_bf16(bf16* qkv, int row_stride, const float* cos_tab, const
                           cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (hd % 2) return OE_ERR_UNSUPPORTED;
-    if ((hd / 2) % 8 == 0 && row_stride % 8 == 0 && !(((uintptr_t)qkv | (uintptr_t)cache) & 15))
+    if ((hd / 2) % 8 == 0 && row_stride % 8 == 0 && !(((uintptr_t)qkv | (uintptr_t)cache | (uintptr_t)cos_tab | (uintptr_t)sin_tab) & 15))
         return oe_launch(rope_kv_write_vec_kernel<bf16>, dim3(n_tokens), dim3(256), 0, st, qkv, row_stride, cos_tab, sin_tab,
                          cache, tables, max_pages, tok_seq, tok_pos, H, KVH, hd, has_kv, rotate);
     const int launch_rc = oe_launch(rope_kv_write_kernel<bf16>, dim3(n_tokens), dim3(256), 0, st, qkv, row_stride, cos_tab, sin_tab, cache, tables,

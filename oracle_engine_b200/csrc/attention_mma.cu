@@ -53,6 +53,7 @@ struct AttnArgs {
     bf16* cache_w;             // the cache entry, writable, when this call stores the new k, v; else null
     int* counters;             // [B * KVH] zeros (n_splits > 1)
     int stages;                // K/V tiles staged ahead: 2 (double buffer) or 1
+    int cluster;               // warps kernel: CTAs (a thread-block cluster) that share one (sequence, KV head)
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -104,14 +105,23 @@ attn_mma_kernel(const AttnArgs a) {
     if (!own_kv) pdl_wait();
     const int b = blockIdx.z, kvh = blockIdx.y;
     const int qlen = a.seq_qlen[b];
-    if (qlen <= 0) return;
+    if (qlen <= 0) {
+        // a padding sequence: like every CTA of this kernel it leaves only after the kernel before has
+        // finished (CTAs that left at once made the decode step of 5 to 7 sequences, padded to 8, 15 %
+        // slower than that of 8)
+        if (own_kv) pdl_wait();
+        return;
+    }
     const int start = a.seq_start[b];
     const int G = a.H / a.KVH;
     const int tpt = a.tokens_per_tile;
     const int n_q_tiles = (qlen + tpt - 1) / tpt;
     const int q_tile = a.n_splits > 1 ? 0 : blockIdx.x;
     const int split = a.n_splits > 1 ? blockIdx.x : 0;
-    if (q_tile >= n_q_tiles) return;
+    if (q_tile >= n_q_tiles) {
+        if (own_kv) pdl_wait();                  // as above
+        return;
+    }
     const int t0 = q_tile * tpt;
     const int nt = min(tpt, qlen - t0);
     const int pos_lo = start + t0, pos_hi = start + t0 + nt - 1;
@@ -438,11 +448,30 @@ __device__ __forceinline__ void load_half_page(uint8_t* ks, uint8_t* vs, const b
 // while one is multiplied.  What a kernel like this streams is (bytes in flight) / (memory
 // latency), so the ring is as deep as shared memory allows: few warps with deep rings where many
 // CTAs share an SM (a large batch), many warps where a CTA has an SM to itself.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Every thread of every CTA of the cluster calls it.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+// A float at this CTA's shared-memory address `p`, read from the CTA of rank `rank` of the cluster.
+__device__ __forceinline__ float ld_peer_f32(const float* p, uint32_t rank) {
+    uint32_t addr;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"((uint32_t)__cvta_generic_to_shared(p)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
+
 template <int NW, int ST>
 __global__ void __launch_bounds__(NW * 32, 1)
 attn_decode_warps_kernel(const AttnArgs a) {
     constexpr int WARP_BYTES = ST * WARP_STAGE_BYTES;
-    static_assert(ST >= 2 && 16 * (HD + 2) * 4 <= WARP_BYTES, "the merge scratch shares the staging buffers");
+    static_assert(ST >= 2 && (NW + 1) * 16 * (HD + 2) * 4 <= NW * WARP_BYTES, "the merge scratch shares the staging buffers");
     extern __shared__ __align__(16) uint8_t smem[];
     pdl_launch_dependents();
     // A layer that reads another layer's cache finds the new token's key there, written by an
@@ -455,20 +484,31 @@ attn_decode_warps_kernel(const AttnArgs a) {
     const int G = a.H / a.KVH;
     const int qlen = a.seq_qlen[b];
     const long long packed0 = a.cu_q[b];
-    if (qlen <= 0) return;                                   // a padding sequence: its row is never read
+    if (qlen <= 0) {
+        // A padding sequence: its row is never read.  Like every CTA of this kernel it leaves only after
+        // the kernel before has finished: with padding CTAs that left at once the decode step of 5 to 7
+        // sequences (padded to 8) took 1.98-2.04 ms against 1.72 ms for 8; with the wait 1.69-1.70 ms.
+        if (own_kv) pdl_wait();
+        return;
+    }
     const int pos = a.seq_start[b];                          // the new token's position
     const int key_lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
     const int hp_lo = key_lo / TB, hp_hi = pos / TB;
     const int* trow = a.tables + (size_t)b * a.max_pages;
     uint8_t* mine = smem + (size_t)warp * WARP_BYTES;
+    // Few sequences with long contexts: the CTAs of a thread-block cluster (gridDim.x of them) share the
+    // pair's tiles, warp gw of NW x CR taking every (NW x CR)-th, and rank 0 adds up through the
+    // cluster's shared memory: twice or four times the SMs stream one sequence's keys.
+    const int CR = a.cluster, rank = CR > 1 ? (int)cluster_ctarank() : 0;
+    const int gw = rank * NW + warp, stride = NW * CR;
 
     // this warp's first tiles are requested before anything else
-    const int n_my = hp_lo + warp <= hp_hi ? (hp_hi - hp_lo - warp) / NW + 1 : 0;
+    const int n_my = hp_lo + gw <= hp_hi ? (hp_hi - hp_lo - gw) / stride + 1 : 0;
     // (the whole ring: nothing is being multiplied yet)
 #pragma unroll
     for (int pre = 0; pre < ST; pre++) {
         if (pre < n_my) {
-            const int hp = hp_lo + warp + pre * NW;
+            const int hp = hp_lo + gw + pre * stride;
             uint8_t* st = mine + (size_t)pre * WARP_STAGE_BYTES;
             load_half_page(st, st + TB_BYTES, a.cache, trow[hp >> 1], hp & 1, kvh, a.KVH, lane);
         }
@@ -482,7 +522,7 @@ attn_decode_warps_kernel(const AttnArgs a) {
     // The warp that will meet the new token's tile asks for that token's k and v now, with q, rotates
     // the key and stores both in the cache; the values wait in registers for the tile.
     constexpr int NEW_IT = (HD / 2 + 31) / 32;
-    const bool owner = a.cache_w != nullptr && n_my > 0 && (hp_hi - hp_lo - warp) % NW == 0;
+    const bool owner = a.cache_w != nullptr && n_my > 0 && (hp_hi - hp_lo - gw) % stride == 0;
     bf16 new_k0[NEW_IT], new_k1[NEW_IT], new_v0[NEW_IT], new_v1[NEW_IT];
     if (owner) {
         const bf16* krow = a.q + packed0 * a.q_stride + (size_t)(a.H + kvh) * HD;
@@ -566,7 +606,7 @@ attn_decode_warps_kernel(const AttnArgs a) {
 
     int stage = 0;                                          // it % ST
     for (int it = 0; it < n_my; it++) {
-        const int hp = hp_lo + warp + it * NW;
+        const int hp = hp_lo + gw + it * stride;
         uint8_t* ks_cur = mine + (size_t)stage * WARP_STAGE_BYTES;
         uint8_t* vs_cur = ks_cur + TB_BYTES;
         cp_async_wait<ST - 1>();
@@ -671,7 +711,7 @@ attn_decode_warps_kernel(const AttnArgs a) {
         }
         __syncwarp();                                       // every lane has read the stage: refill it
         if (it + ST < n_my) {
-            const int hn = hp + ST * NW;
+            const int hn = hp + ST * stride;
             load_half_page(ks_cur, vs_cur, a.cache, trow[hn >> 1], hn & 1, kvh, a.KVH, lane);
         }
         cp_async_commit();
@@ -699,6 +739,7 @@ attn_decode_warps_kernel(const AttnArgs a) {
     }
     __syncthreads();
     bf16* obase = a.out + packed0 * (long long)(a.H * HD) + (size_t)kvh * G * HD;
+    float* cpart = part + (size_t)NW * G * (HD + 2);       // [G][HD + 2]: this CTA's sum, for the cluster
     for (int idx = threadIdx.x; idx < G * HD; idx += NW * 32) {
         const int gh = idx / HD, d = idx % HD;
         float m = -INFINITY;
@@ -714,7 +755,43 @@ attn_decode_warps_kernel(const AttnArgs a) {
                 o += p[d] * wgt;
             }
         }
-        obase[idx] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+        if (CR == 1) {
+            obase[idx] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+        } else {
+            cpart[(size_t)gh * (HD + 2) + d] = o;
+            if (d == 0) { cpart[(size_t)gh * (HD + 2) + HD] = m; cpart[(size_t)gh * (HD + 2) + HD + 1] = l; }
+        }
+    }
+    if (CR > 1) {
+        cluster_sync_all();                                 // every CTA's sum is in its shared memory
+        if (rank == 0) {
+            for (int idx = threadIdx.x; idx < G * HD; idx += NW * 32) {
+                const int gh = idx / HD, d = idx % HD;
+                const float* row = cpart + (size_t)gh * (HD + 2);
+                float mr[8], lr[8], orr[8];
+                float m = -INFINITY;
+#pragma unroll
+                for (int r = 0; r < 8; r++) {
+                    if (r >= CR) break;
+                    mr[r] = ld_peer_f32(row + HD, (uint32_t)r);
+                    lr[r] = ld_peer_f32(row + HD + 1, (uint32_t)r);
+                    orr[r] = ld_peer_f32(row + d, (uint32_t)r);
+                    m = fmaxf(m, mr[r]);
+                }
+                float l = 0.f, o = 0.f;
+#pragma unroll
+                for (int r = 0; r < 8; r++) {              // in rank order
+                    if (r >= CR) break;
+                    if (mr[r] != -INFINITY) {
+                        const float wgt = exp2f(mr[r] - m);
+                        l += lr[r] * wgt;
+                        o += orr[r] * wgt;
+                    }
+                }
+                obase[idx] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+            }
+        }
+        cluster_sync_all();                                 // nobody leaves while its shared memory is read
     }
 }
 
@@ -813,7 +890,7 @@ int oe_attn_mma_bf16(bf16* out, const bf16* q, long long q_stride, const bf16* c
     a.scale_log2 = scale * 1.4426950408889634f;
     a.partial = partial;
     a.fused = 0; a.cos_tab = nullptr; a.sin_tab = nullptr; a.cache_w = nullptr; a.counters = nullptr;
-    a.stages = 2;
+    a.stages = 2; a.cluster = 1;
     // rows per sequence tile: 16 per warp; few rows (decode) use fewer warps
     const long long rows_needed = (long long)max_qlen * G;
     int nwarps = rows_needed <= 16 ? 1 : (rows_needed <= 32 ? 2 : 4);
@@ -859,7 +936,7 @@ int oe_attn_decode_fused_bf16(bf16* out, const bf16* qkv, long long qkv_stride, 
     int nwarps = G <= 16 ? 1 : (G <= 32 ? 2 : 4);
     a.tokens_per_tile = (nwarps * 16) / G;
     a.n_splits = n_splits < 1 ? 1 : n_splits;
-    a.stages = nwarps == 1 ? decode_stages(a.n_splits) : 2;
+    a.stages = nwarps == 1 ? decode_stages(a.n_splits) : 2; a.cluster = 1;
     if (nwarps == 1) return launch<1>(a, n_seqs, a.n_splits, st);
     if (nwarps == 2) return launch<2>(a, n_seqs, a.n_splits, st);
     return launch<4>(a, n_seqs, a.n_splits, st);
@@ -869,11 +946,12 @@ int oe_attn_decode_fused_bf16(bf16* out, const bf16* qkv, long long qkv_stride, 
 // one launch, no scratch.  Needs G = H/KVH <= 16.  shape = warps * 16 + ring depth; the forms
 // built here: 6 x 2 (a CTA fills an SM: up to about two CTAs for every SM), 4 x 3 (the same with
 // a deeper ring), 2 x 3 (two CTAs an SM) and 1 x 3 (four CTAs an SM: large batches).  0: 6 x 2.
+// cluster: 1, or how many CTAs (a thread-block cluster, up to 8) share one (sequence, KV head).
 // Returns OE_ERR_UNSUPPORTED for a form that is not built or does not fit an SM at this head size.
 int oe_attn_decode_warps_bf16(bf16* out, const bf16* qkv, long long qkv_stride, const float* cos_tab,
                               const float* sin_tab, bf16* cache, int has_kv, const int* tables, int max_pages,
                               const int* cu_q, const int* seq_start, const int* seq_qlen, int n_seqs, int H, int KVH,
-                              int window, float scale, int shape, cudaStream_t st) {
+                              int window, float scale, int shape, int cluster, cudaStream_t st) {
     if (n_seqs <= 0) return 0;
     if (H % KVH || ((uintptr_t)qkv & 3) || (qkv_stride & 1) || (HD % 32)) return OE_ERR_UNSUPPORTED;
     const int G = H / KVH;
@@ -884,6 +962,8 @@ int oe_attn_decode_warps_bf16(bf16* out, const bf16* qkv, long long qkv_stride, 
     a.scale_log2 = scale * 1.4426950408889634f;
     a.partial = nullptr; a.fused = 1; a.cos_tab = cos_tab; a.sin_tab = sin_tab; a.cache_w = has_kv ? cache : nullptr;
     a.counters = nullptr; a.tokens_per_tile = 1; a.n_splits = 1; a.stages = 2;
+    if (cluster < 1 || cluster > 8) return OE_ERR_UNSUPPORTED;
+    a.cluster = cluster;
     if (shape == 0) shape = 6 * 16 + 2;
     if (shape == 6 * 16 + 2 && 6 * 2 * WARP_STAGE_BYTES > 220 * 1024) shape = 3 * 16 + 2;    // large heads
 #define OE_WARPS_LAUNCH(NW, ST)                                                                                    \
@@ -897,6 +977,9 @@ int oe_attn_decode_warps_bf16(bf16* out, const bf16* qkv, long long qkv_stride, 
             if (e != cudaSuccess) return (int)e;                                                                  \
             attr_set = true;                                                                                      \
         }                                                                                                         \
+        if (cluster > 1)                                                                                          \
+            return oe_launch_cluster(attn_decode_warps_kernel<NW, ST>, (unsigned)cluster, dim3(cluster, KVH, n_seqs), \
+                                     dim3(NW * 32), smem, st, a);                                                  \
         return oe_launch(attn_decode_warps_kernel<NW, ST>, dim3(1, KVH, n_seqs), dim3(NW * 32), smem, st, a);     \
     }
     OE_WARPS_LAUNCH(6, 2)

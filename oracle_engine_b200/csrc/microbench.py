@@ -98,7 +98,7 @@ def run_gemm(a):
 
 def run_attention(a):
     shape = tuple(int(v) for v in a.warps.split("x")) if a.warps else None
-    with ops_tc.knobs(decode_splits=a.splits, decode_warps_shape=shape):
+    with ops_tc.knobs(decode_splits=a.splits, decode_warps_shape=shape, decode_warps_cluster=a.cluster):
         _run_attention(a)
 
 
@@ -187,6 +187,7 @@ def main(argv=None):
     at.add_argument("--kv-heads", type=int, default=8)
     at.add_argument("--head-dim", type=int, default=128)
     at.add_argument("--splits", type=int, default=0, help="split kernel: CTAs per (sequence, KV head) (0: the rule's)")
+    at.add_argument("--cluster", type=int, default=0, help="warps kernel: CTAs that share a (sequence, KV head) (0: the rule's)")
     at.add_argument("--warps", default="", help="warps kernel: WARPSxRING, e.g. 1x3 (default: the rule's)")
     at.add_argument("--decode", default="split", choices=["split", "warps", "fused"],
                     help="decode kernel: keys split over CTAs plus a merge (after a separate rotation kernel, not timed "

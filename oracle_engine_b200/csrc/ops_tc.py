@@ -26,6 +26,7 @@ class _Knobs:
     decode_kernel = "auto"         # "auto", "warps", "split": the decode attention kernel
     decode_splits = 0              # > 0: this many CTAs per (sequence, KV head) instead of the rule's
     decode_warps_shape = None      # (warps, ring depth) of the kernel whose warps split the keys, instead of the rule's
+    decode_warps_cluster = 0       # > 0: this many CTAs of that kernel share a (sequence, KV head), instead of the rule's
     pair_max_tile = 0              # > 0: an upper limit for the two-SM product's tile width
     sm_count = 0                   # > 0: the products plan their grids for this many SMs
     gemm_schedule = (0, -1, -1, -1, -1)     # one-SM tcgen05 product: tile width, stream-K, cluster, narrow, atoms (see knobs)
@@ -243,7 +244,7 @@ def _attn_lib(head_dim: int):
         lib.oe_attn_decode_fused_bf16.restype = c_int
         lib.oe_attn_decode_warps_bf16.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
                                                   c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                                  c_int, c_float, c_int, c_void_p]
+                                                  c_int, c_float, c_int, c_int, c_void_p]
         lib.oe_attn_decode_warps_bf16.restype = c_int
         lib.oe_attn_mma_partial_floats.argtypes = [c_int, c_int, c_int]
         lib.oe_attn_mma_partial_floats.restype = c_longlong
@@ -355,8 +356,6 @@ def decode_fused_supported(head_dim: int, n_heads: int, n_kv_heads: int) -> bool
     return attention_supported(head_dim, n_heads, n_kv_heads) and head_dim % 32 == 0
 
 
-DECODE_WARPS_FULL_CTAS = 48  # (sequence, KV head) pairs from which contexts of class 1 stay on the warps kernel too
-DECODE_WARPS_LONG_CTAS = 96  # ... and contexts of class 2
 DECODE_WARPS_FORMS = ((6, 2), (2, 3), (1, 3))    # (warps, tiles in a warp's ring) the rule picks from (csrc/attention_mma.cu)
 SM_SHARED_BYTES = 227 * 1024   # what the CTAs resident on an SM share, each with 1 KB of the system's on top
 
@@ -370,20 +369,16 @@ def decode_uses_warps(n_seqs: int, context_class: int, head_dim: int, n_heads: i
     """Whether a decode step goes to the kernel whose warps split the keys (one launch, no
     scratch) rather than to CTAs that split the keys plus a merge.  Depends on the batch size and
     the step's context class (engine/batch.py) only; a captured graph is kept per class.
-    With up to one (sequence, KV head) pair per SM, measured (us, 24 heads over 8 KV heads of
-    128; warps / split): class 0 (640 keys): 8 sequences 9.1 / 10.8+rotation; class 1 (2,048):
-    1 sequence 20 / 12, 8: 21 / 22; class 2 (8,000): 1: 63 / 18, 8: 66 / 56, 16: 90 / 90.
-    With more pairs than SMs the warps kernel in the form `decode_warps_shape` picks wins
-    everywhere (see there)."""
+    It is used wherever it can be (groups of up to 16 heads, head sizes that are multiples of 32).
+    Alone, the split kernels are faster for few long sequences (us, 24 heads over 8 KV heads of 128;
+    warps / split: 2,048 keys, 1 sequence 20 / 12; 8,000 keys, 1: 63 / 18, 8: 66 / 56), but inside the
+    decode step their three launches cost the overlap with the products around them (ms a step of the
+    28-layer model, split / warps: 2,048-token contexts, 1 sequence 2.50 / 1.93, 8: 3.17 / 2.05; 6,000
+    tokens, 1: 2.60 / 2.74, 16: 4.40 / 4.03), and with a cluster per pair (`decode_warps_cluster`) the
+    warps kernel wins there too (1 sequence at 6,000 tokens: 1.80)."""
     if KNOBS.decode_kernel == "split" or not decode_warps_supported(head_dim, n_heads, n_kv_heads):
         return False
-    if KNOBS.decode_kernel == "warps":
-        return True
-    pairs = n_seqs * n_kv_heads
-    if context_class <= 0 or pairs > (sm_count or _sm_count()):
-        return True
-    # with few sequences more CTAs per sequence win
-    return pairs >= (DECODE_WARPS_FULL_CTAS if context_class == 1 else DECODE_WARPS_LONG_CTAS)
+    return True
 
 
 def decode_warps_per_sm(shape: tuple, head_dim: int) -> int:
@@ -434,6 +429,33 @@ def decode_warps_shape(n_seqs: int, context_class: int, head_dim: int, n_kv_head
     return best
 
 
+def decode_warps_cluster(n_seqs: int, context_class: int, n_kv_heads: int, sm_count: int | None = None) -> int:
+    """How many CTAs (a thread-block cluster) of the warps kernel share one (sequence, KV head).
+
+    One where the context is short or the pairs alone fill the SMs.  Past 1,536 keys, few sequences are
+    streamed by 2 or 4 CTAs each (8 for a single sequence past 4,096 keys), which add up through the
+    cluster's shared memory, as long as all clusters are resident at once.  Measured alone (us; 24 heads over
+    8 KV heads of 128, six warps x two tiles; 1 / 2 / 4 / 8 CTAs, and the split kernels + merge):
+    2,100 keys: 1 sequence 18.4 / 12.5 / 8.8 / 9.6 (12), 4: 19.0 / 13.3 / 12.3 / 29 , 8: 19.5 / 16.1 / 23.8 / 51 (22);
+    8,000 keys: 1: 61 / 34 / 21 / 15.6 (18), 2: 62 / 35 / 21.5 / 30, 4: 63 / 36 / 27.5 / 46, 8: 64 / 44.8 / 52 / 80 (56),
+    16: 88 / 85 / 101 / 149 (90).  530 keys, 8 sequences: 7.0 / 9.0 / 15.4 / 41."""
+    if KNOBS.decode_warps_cluster > 0:
+        return int(KNOBS.decode_warps_cluster)
+    if context_class <= 0:
+        return 1
+    # Inside the decode step the attention's CTAs (a whole SM's shared memory and two thirds of its
+    # registers each) must leave SMs to the products before and after it, which overlap it: with more than
+    # about 64 of them on 148 SMs the step loses more than the attention gains (ms a step of the 28-layer
+    # model, 1 / 2 / 4 CTAs per pair; 2,048-token contexts: 1 sequence 1.93 / 1.76 / 1.69, 4: 1.98 / 1.85 /
+    # 2.62, 8: 2.05 / 2.93 / 3.13; 6,000 tokens: 2: 2.77 / 2.20 / 1.95, 4: 2.82 / 2.27 / 2.93, 8: 2.88 / 3.49 / 3.68).
+    budget = (sm_count or _sm_count()) * 7 // 16
+    pairs = max(1, n_seqs * n_kv_heads)
+    for cr in ((8, 4, 2) if context_class >= 2 else (4, 2)):
+        if pairs * cr <= budget:
+            return cr
+    return 1
+
+
 def _sm_count() -> int:
     if "sms" not in _state:
         _state["sms"] = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
@@ -441,10 +463,12 @@ def _sm_count() -> int:
 
 
 def attention_decode_warps(out, qkv, cos, sin, cache, tables, ctx, n_heads: int, n_kv_heads: int, head_dim: int,
-                           window: int, scale: float, has_kv: bool, shape: tuple | None = None) -> None:
+                           window: int, scale: float, has_kv: bool, shape: tuple | None = None,
+                           cluster: int | None = None) -> None:
     """The decode step's mixer core (rotation, cache write, attention) in one launch: one CTA per
     (sequence, KV head), whose warps split the keys (csrc/attention_mma.cu).  Same arguments as
-    attention_decode_fused; shape = (warps, tiles in each warp's ring), None: `decode_warps_shape`."""
+    attention_decode_fused; shape = (warps, tiles in each warp's ring), None: `decode_warps_shape`;
+    cluster = CTAs that share one (sequence, KV head), None: `decode_warps_cluster`."""
     if out.dtype != torch.bfloat16 or qkv.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
         raise KernelError("attention_decode_warps: bfloat16 tensors expected")
     width = (n_heads + (2 * n_kv_heads if has_kv else 0)) * head_dim
@@ -455,12 +479,14 @@ def attention_decode_warps(out, qkv, cos, sin, cache, tables, ctx, n_heads: int,
     lib = _attn_lib(head_dim)
     if shape is None:
         shape = decode_warps_shape(ctx.n_seqs, getattr(ctx, "context_class", 0), head_dim, n_kv_heads)
+    if cluster is None:
+        cluster = decode_warps_cluster(ctx.n_seqs, getattr(ctx, "context_class", 0), n_kv_heads)
     code = lib.oe_attn_decode_warps_bf16(
         out.data_ptr(), qkv.data_ptr(), qkv.stride(0), None if cos is None else cos.data_ptr(),
         None if sin is None else sin.data_ptr(), cache.data_ptr(), int(has_kv), tables.data_ptr(), tables.shape[1],
         ctx.cu_q.data_ptr(), ctx.seq_start.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.n_seqs, n_heads, n_kv_heads,
-        int(window), float(scale), shape[0] * 16 + shape[1], ops._stream())
-    ops._check(code, "attention_decode_warps", {"warps": shape[0], "ring": shape[1]})
+        int(window), float(scale), shape[0] * 16 + shape[1], int(cluster), ops._stream())
+    ops._check(code, "attention_decode_warps", {"warps": shape[0], "ring": shape[1], "cluster": int(cluster)})
 
 
 def _attn_counters(device):

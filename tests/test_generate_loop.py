@@ -223,9 +223,14 @@ def test_decode_kernel_rules_depend_on_sizes_only():
     from oracle_engine_b200.engine import batch
     assert [batch.context_class(n) for n in (1, 1536, 1537, 4096, 4097, 100000)] == [0, 0, 1, 1, 2, 2]
     uses = lambda n_seqs, cls: ops_tc.decode_uses_warps(n_seqs, cls, 128, 24, 8, sm_count=148)
-    assert [uses(b, 0) for b in (1, 8, 37, 38, 64, 500)] == [True] * 6                       # short contexts: always
-    assert [uses(b, 1) for b in (1, 5, 6, 18, 19, 24, 64)] == [False, False, True, True, True, True, True]   # from 48 pairs
-    assert [uses(b, 2) for b in (8, 11, 12, 18, 24, 40, 64)] == [False, False, True, True, True, True, True]  # from 96 pairs
+    assert [uses(b, c) for c in (0, 1, 2) for b in (1, 8, 64, 500)] == [True] * 12          # wherever it can be used
+    # few sequences with long contexts: 2, 4 or 8 CTAs (a cluster) per (sequence, KV head), at most about 64 CTAs in all
+    cluster = lambda n_seqs, cls: ops_tc.decode_warps_cluster(n_seqs, cls, 8, sm_count=148)
+    assert [cluster(b, 0) for b in (1, 4, 8, 64)] == [1, 1, 1, 1]
+    assert [cluster(b, 1) for b in (1, 2, 3, 4, 5, 8, 64)] == [4, 4, 2, 2, 1, 1, 1]
+    assert [cluster(b, 2) for b in (1, 2, 3, 4, 5, 8, 64)] == [8, 4, 2, 2, 1, 1, 1]
+    with ops_tc.knobs(decode_warps_cluster=2):
+        assert cluster(64, 0) == 2
     # its form, (warps, tiles in a warp's ring): the most warps whose CTAs are all resident at once (1, 2 or 4 an SM)
     shape = lambda n_seqs, cls, hd=128, kvh=8: ops_tc.decode_warps_shape(n_seqs, cls, hd, kvh, sm_count=148)
     assert [shape(b, 0) for b in (1, 18, 19, 37, 38, 64, 74, 75, 128)] == \

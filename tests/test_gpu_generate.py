@@ -188,9 +188,9 @@ def test_decoding_across_the_context_classes(model_dirs, plain_models, tmp_path,
 
 def test_many_sequences_decoding_across_the_context_classes(model_dirs, plain_models, tmp_path, monkeypatch):
     """50 sequences (100 (sequence, KV head) pairs) that grow across both class boundaries while
-    they decode: in the longer classes such a batch goes to the kernel whose warps split the keys,
-    where two sequences went to the split kernel; the logits are those of the plain model at
-    every position, and shorter sequences leave the batch on the way."""
+    they decode: in every class such a batch goes to the kernel whose warps split the keys, one CTA
+    per pair; the logits are those of the plain model at every position, and shorter sequences leave
+    the batch on the way."""
     from oracle_engine_b200.csrc import ops_tc
     from oracle_engine_b200.engine import batch
     from oracle_engine_b200.engine.engine import Engine
@@ -199,12 +199,41 @@ def test_many_sequences_decoding_across_the_context_classes(model_dirs, plain_mo
     kvh, heads, hd = plain.cfg["num_key_value_heads"], plain.cfg["num_attention_heads"], plain.cfg["head_dim"]
     n = 50
     assert ops_tc.decode_uses_warps(n, 1, hd, heads, kvh) and ops_tc.decode_uses_warps(n, 2, hd, heads, kvh)
-    assert not ops_tc.decode_uses_warps(2, 1, hd, heads, kvh)
+    assert ops_tc.decode_warps_cluster(n, 1, kvh) == 1 and ops_tc.decode_warps_cluster(n, 2, kvh) == 1
     eng = Engine.from_pretrained(model_dirs["E"], dtype="bfloat16", max_tokens=n * 256)
     lens = [200 if i % 5 else 120 + i for i in range(n)]
     requests = [helpers.random_tokens(m, plain.cfg["vocab_size"], 300 + i) for i, m in enumerate(lens)]
     steps = helpers.batched_steps(requests, [60 + (i % 7) for i in range(n)], n)
     out = helpers.TraceRunner(eng, tmp_path / "many").run(steps)
+    got = helpers.collect(steps, out, requests)
+    for i, toks in enumerate(requests):
+        want = plain.logits(toks).numpy()
+        err = np.abs(got[i] - want).max(axis=1)
+        assert err.max() < TOL["bfloat16"], f"request {i}: first bad position {int((err >= TOL['bfloat16']).argmax())}"
+    classes = {key[1] for key, g in eng.stepper._graphs.items() if g.graph is not None}
+    assert classes == {0, 1, 2}
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("n", [1, 3, 6])
+def test_few_sequences_decoding_across_the_context_classes(n, model_dirs, plain_models, tmp_path, monkeypatch):
+    """Few sequences that grow across both class boundaries while they decode: in the longer classes
+    2, 4 or 8 CTAs (a thread-block cluster) share each (sequence, KV head) and add up through the
+    cluster's shared memory; the new token's tile may lie in any of them.  Every decoded position
+    against the plain model."""
+    from oracle_engine_b200.csrc import ops_tc
+    from oracle_engine_b200.engine import batch
+    from oracle_engine_b200.engine.engine import Engine
+    monkeypatch.setattr(batch, "CONTEXT_CLASS_TOKENS", [96, 170])
+    plain = plain_models["E"]
+    kvh = plain.cfg["num_key_value_heads"]
+    sizes = [ops_tc.decode_warps_cluster(n, c, kvh) for c in (0, 1, 2)]
+    assert sizes[0] == 1 and sizes[1] > 1 and sizes[2] >= sizes[1]
+    eng = Engine.from_pretrained(model_dirs["E"], dtype="bfloat16", max_tokens=n * 256)
+    lens = [230 - 7 * i for i in range(n)]
+    requests = [helpers.random_tokens(m, plain.cfg["vocab_size"], 700 + i) for i, m in enumerate(lens)]
+    steps = helpers.batched_steps(requests, [50 + 3 * i for i in range(n)], n)
+    out = helpers.TraceRunner(eng, tmp_path / "few").run(steps)
     got = helpers.collect(steps, out, requests)
     for i, toks in enumerate(requests):
         want = plain.logits(toks).numpy()

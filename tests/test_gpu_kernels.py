@@ -501,19 +501,22 @@ def test_argmax_and_sampling():
         assert counters[5].item() == (3 if c["temperature"] > 0 else 0) and hist_count[5].item() == 10
 
 
-@pytest.mark.parametrize("kernel", ["fused", "warps", "warps 4x3", "warps 2x3", "warps 1x3", "warps 3x2"])
+@pytest.mark.parametrize("kernel", ["fused", "warps", "warps 4x3", "warps 2x3", "warps 1x3", "warps 3x2",
+                                    "warps 6x2x2", "warps 6x2x4", "warps 2x3x2", "warps 1x3x8"])
 @pytest.mark.parametrize("H,KVH,hd,window,rotate", [(24, 8, 128, 0, True), (6, 2, 32, 0, True), (8, 8, 64, 100, False),
                                                      (4, 1, 32, 0, True), (16, 1, 64, 300, True)])
 def test_attention_decode_fused(H, KVH, hd, window, rotate, kernel):
     """One kernel for rotation, cache write, attention and merge (the keys split over CTAs, or over
-    the warps of one CTA, in every form of that kernel: warps x tiles in a warp's ring), against
+    the warps of one CTA, in every form of that kernel: warps x tiles in a warp's ring, alone or
+    several CTAs of a cluster sharing the keys), against
     the plain parts."""
     import functools
     from types import SimpleNamespace
     from oracle_engine_b200.csrc import ops_tc
     decode = ops_tc.attention_decode_fused if kernel == "fused" else ops_tc.attention_decode_warps
-    if " " in kernel:
-        decode = functools.partial(decode, shape=tuple(int(v) for v in kernel.split()[1].split("x")))
+    if " " in kernel:                      # warps x ring [x CTAs of a cluster that share a (sequence, KV head)]
+        form = tuple(int(v) for v in kernel.split()[1].split("x"))
+        decode = functools.partial(decode, shape=form[:2], cluster=form[2] if len(form) > 2 else 1)
     lens = [1, 64, 65, 200, 130, 17, 128, 33, 600, 2100]       # length including the new token
     B = len(lens)
     g = torch.Generator().manual_seed(hd + H)

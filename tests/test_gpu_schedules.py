@@ -125,14 +125,14 @@ class _Seen:
         self.log.append((what, detail))
 
     def attention(self):
-        return [(w, (d or {}).get("splits")) for w, d in self.log if w.startswith("attention")]
+        return [(w, (d or {}).get("splits") or (d or {}).get("cluster")) for w, d in self.log if w.startswith("attention")]
 
 
 def test_one_sequence_across_both_context_class_boundaries(real_heads, tmp_path):
     """4,300 tokens: a prompt, decoding across 1,536 tokens, a prompt piece of 2,450 tokens over the
     cached prefix, decoding across 4,096 tokens; with the class boundaries where serving has them.
     Every decoded position and the rows of the prompt pieces are compared with the plain model, and
-    each class must have used the decode kernel and split count its rule names."""
+    each class must have used the decode kernel and the number of CTAs per pair its rule names."""
     from oracle_engine_b200.csrc import ops, ops_tc
     from oracle_engine_b200.engine import batch
     from oracle_engine_b200.engine.engine import Engine
@@ -154,15 +154,12 @@ def test_one_sequence_across_both_context_class_boundaries(real_heads, tmp_path)
     tol = _tolerance(want)
     assert err.max() < tol, f"first bad position {int((err >= tol).argmax())}: {err.max()} (tolerance {tol})"
     eng.check_device_errors()
-    # which decode kernel ran in each class: 8 (sequence, KV head) pairs are few, so only class 0 stays
-    # on the one-CTA-per-pair kernel; the longer classes split the keys over CTAs, class 2 over more
+    # which decode kernel ran in each class: the one whose warps split the keys, with one CTA per
+    # (sequence, KV head) in class 0 and, 8 pairs being few, clusters of 4 and of 8 CTAs in the longer classes
     kinds = set(seen.attention())
-    assert ("attention_decode_warps", None) in kinds
-    splits = sorted({s for w, s in kinds if w == "attention_mma" and s and s > 1})
-    sms = torch.cuda.get_device_properties(0).multi_processor_count
-    pages = eng.cache.max_pages_per_seq
-    per_sm = ops_tc._decode_ctas_per_sm(128)
-    assert splits == sorted({ops_tc.decode_splits(1, 8, sms, pages, 1, per_sm), ops_tc.decode_splits(1, 8, sms, pages, 2, per_sm)})
+    clusters = sorted(c for w, c in kinds if w == "attention_decode_warps")
+    assert clusters == [ops_tc.decode_warps_cluster(1, c, 8) for c in (0, 1, 2)] == [1, 4, 8]
+    assert not any(w == "attention_mma" for w, _ in kinds)
     assert ("attention_tcgen05", None) in kinds            # the prompt pieces
 
 

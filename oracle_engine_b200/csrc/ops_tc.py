@@ -109,23 +109,21 @@ def gemm_supported(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.stride(1) == 1)
 
 
-SKINNY_MAX_TOKENS = 16      # the most tokens the weight-streaming kernel (gemm_skinny.cu) takes
-SKINNY_FULL_TOKENS = 8      # up to here it is used for every product; from 9 to 16 tokens only for weights of up to
-SKINNY_SMALL_BYTES = 24 << 20   # this size, for weights with fewer than
-SKINNY_NARROW = 3072        # this many rows or columns, and for the logits.  Measured alone (us; 3072->16384 with SwiGLU,
-                            # 8192->3072, 3072->5120, 3072->3072; weight-streaming / tcgen05): 8 tokens 18.4 12.8 8.5 7.2 /
-                            # 20.0 14.2 11.2 9.9; 12 tokens 23.8 15.1 12.0 7.1 / 20.4 14.4 11.4 9.9; 16 tokens 23.8 15.0 11.9
-                            # 7.1 / 20.7 14.5 11.2 10.2.  Inside a model (ms a decode step, all products weight-streaming /
-                            # this rule): 3B shape, 12 sequences 2.51 / 2.45, 16 sequences 2.62 / 2.50; the 1B shape (K = 2048
-                            # or 2048 rows) at 16 sequences lost 5 % with tcgen05 for its large products: they stay here
+SKINNY_MAX_TOKENS = 16      # up to here every product goes to the weight-streaming kernel (gemm_skinny.cu).  Alone, the
+                            # tcgen05 kernel is the faster one for the large weights from 9 tokens on (us at 16 tokens,
+                            # 3072->16384 with SwiGLU, 8192->3072, 3072->5120, 3072->3072; weight-streaming / tcgen05:
+                            # 23.8 15.2 12.0 7.2 / 19.9 13.7 10.1 9.2), but a decode step is a chain of kernels that
+                            # overlap, and in the chain the weight-streaming kernels with the flags of parts/linear.py
+                            # win: 16 sequences of the 3B shape 2.11 ms a step against 2.38 with tcgen05 for the large
+                            # weights (12 sequences 2.06 / 2.36); the 1B shape lost 5 % with tcgen05 there as well
 
 
 def uses_skinny(M: int, N: int, K: int, kind: int) -> bool:
     """Whether a product of M tokens with an [N, K] weight goes to the weight-streaming kernel
     (kind: the epilogue, 1 = float32 store, the logits)."""
-    if M <= SKINNY_FULL_TOKENS:
-        return True
-    return M <= SKINNY_MAX_TOKENS and (kind == 1 or N * K * 2 <= SKINNY_SMALL_BYTES or min(N, K) < SKINNY_NARROW)
+    return M <= SKINNY_MAX_TOKENS
+
+
 PAIR_MIN_TOKENS = 256       # from here on the two-SM kernel (gemm_tcgen05_pair.cu); measured against the one-SM kernel
                             # at 2,048 / 4,096 tokens (us): 3072->16384 SwiGLU 134 / 150; 3072->3072 accumulate 39.2 /
                             # 40.9 and 64.5 / 72.5; 8192->3072 accumulate 90.2 / 95.5 and 165 / 183

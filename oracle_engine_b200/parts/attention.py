@@ -16,7 +16,7 @@ import math
 import torch
 
 from ..csrc import ops
-from .linear import START_EARLY, TRIGGER_LATE, matmul_nt
+from .linear import chain_flags, matmul_nt
 from .registry import MIXERS, Part
 from .spec import TensorDecl, attention_cache_need
 
@@ -85,12 +85,11 @@ class GQAAttention(Part):
         q_width = self.H * self.hd
         width = q_width + (2 * self.KVH * self.hd if owns_cache else 0)
         qkv = self.rt.empty(T, width)
-        # both products of the mixer may start while the kernel before them drains (measured: 2 % of a
-        # decode step; the feed-forward's products must not, see csrc/gemm_skinny.cu)
-        matmul_nt(self.rt, qkv, h, self.w_qkv[:width], early=START_EARLY)
+        # how the products are chained to their neighbours in the stream: parts/linear.py
+        matmul_nt(self.rt, qkv, h, self.w_qkv[:width], early=chain_flags("mixer_in", T))
         cos, sin = self.position.tables() if self.position is not None else (None, None)
         from . import attention_dispatch as ad
         o = self.rt.empty(T, q_width)
         ad.mixer_core(self.rt, o, qkv, cos, sin, cache, ctx, self.H, self.KVH, self.hd, self.window, self.scale,
                       owns_cache)
-        matmul_nt(self.rt, residual, o, self.w_o, accumulate=True, early=START_EARLY | TRIGGER_LATE)
+        matmul_nt(self.rt, residual, o, self.w_o, accumulate=True, early=chain_flags("mixer_out", T))

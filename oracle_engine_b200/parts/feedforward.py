@@ -6,7 +6,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
-from .linear import START_EARLY, TRIGGER_LATE, matmul_nt
+from .linear import chain_flags, matmul_nt
 from .registry import FEED_FORWARDS, Part
 from .spec import TensorDecl
 
@@ -52,11 +52,9 @@ class SwiGLU(Part):
         a = self.rt.empty(T, self.FF)
         if self.fused:
             from ..csrc import ops_tc
-            ops_tc.gemm(a, h, self.w_gu, swiglu=True, early=START_EARLY | TRIGGER_LATE)
+            ops_tc.gemm(a, h, self.w_gu, swiglu=True, early=chain_flags("ffn_in", T))
         else:
             gu = self.rt.empty(T, 2 * self.FF)
             matmul_nt(self.rt, gu, h, self.w_gu)
             ops.swiglu(a, gu)
-        # what follows the down product is a norm (few small CTAs): it may be scheduled from the product's
-        # top (measured inside the 28-layer step, 1 / 2 / 4 / 8 sequences: 1.8 / 0.8 / 1.0 / 0 % faster)
-        matmul_nt(self.rt, residual, a, self.w_down, accumulate=True, early=START_EARLY)
+        matmul_nt(self.rt, residual, a, self.w_down, accumulate=True, early=chain_flags("ffn_out", T))

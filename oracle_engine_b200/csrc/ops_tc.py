@@ -267,6 +267,10 @@ def _attn_tc5_lib(head_dim: int):
     return lib
 
 
+# Context classes (engine/batch.py: the longest sequence of a step is up to 768, 1,536, 4,096 tokens, or longer)
+MID_CONTEXT, LONG_CONTEXT, VERY_LONG_CONTEXT = 1, 2, 3
+
+
 def decode_splits(n_seqs: int, n_kv_heads: int, sm_count: int, max_pages: int, context_class: int = 0,
                   ctas_per_sm: int = 3) -> int:
     """How many CTAs share one (sequence, KV head) of a decode step, never more than the pages a
@@ -280,7 +284,7 @@ def decode_splits(n_seqs: int, n_kv_heads: int, sm_count: int, max_pages: int, c
         return max(1, min(max_pages, 32, KNOBS.decode_splits))
     ctas = max(1, n_seqs * n_kv_heads)
     cap = max(1, min(max_pages, 32))
-    if context_class <= 0:
+    if context_class < LONG_CONTEXT:
         return max(1, min(cap, (2 * sm_count + ctas - 1) // ctas))
     resident = max(1, ctas_per_sm) * sm_count
     best, best_fill = 1, 0.0
@@ -296,7 +300,7 @@ def decode_splits(n_seqs: int, n_kv_heads: int, sm_count: int, max_pages: int, c
 
 def decode_splits_for(n_seqs: int, n_kv_heads: int, tables, context_class: int = 0, head_dim: int = 0) -> int:
     sms = torch.cuda.get_device_properties(tables.device).multi_processor_count
-    per_sm = _decode_ctas_per_sm(head_dim) if head_dim and context_class > 0 else 3
+    per_sm = _decode_ctas_per_sm(head_dim) if head_dim and context_class >= LONG_CONTEXT else 3
     return decode_splits(n_seqs, n_kv_heads, sms, tables.shape[1], context_class, per_sm)
 
 
@@ -412,12 +416,12 @@ def decode_warps_shape(n_seqs: int, context_class: int, head_dim: int, n_kv_head
             forms.append((shape, per_sm * sms))
     if not forms:
         raise KernelError(f"attention_decode_warps: no form of the kernel fits an SM at head size {head_dim}")
-    if context_class > 0 and len(forms) > 1:
+    if context_class >= LONG_CONTEXT and len(forms) > 1:
         forms = forms[:-1]
     for shape, slots in forms:
         if pairs <= slots:
             return shape
-    if context_class <= 0:
+    if context_class < LONG_CONTEXT:
         return forms[-1][0]
     best, best_fill = forms[0][0], 0.0
     for shape, slots in forms:
@@ -430,16 +434,18 @@ def decode_warps_shape(n_seqs: int, context_class: int, head_dim: int, n_kv_head
 def decode_warps_cluster(n_seqs: int, context_class: int, n_kv_heads: int, sm_count: int | None = None) -> int:
     """How many CTAs (a thread-block cluster) of the warps kernel share one (sequence, KV head).
 
-    One where the context is short or the pairs alone fill the SMs.  Past 1,536 keys, few sequences are
+    One where the context is short or the pairs alone fill the SMs.  Past 768 keys, few sequences are
     streamed by 2 or 4 CTAs each (8 for a single sequence past 4,096 keys), which add up through the
-    cluster's shared memory, as long as all clusters are resident at once.  Measured alone (us; 24 heads over
+    cluster's shared memory, as long as all clusters are resident at once (ms a step of the 28-layer model
+    with 1 / 2 / 4 CTAs per pair at 1,400 tokens: 1 sequence 1.79 / 1.68 / 1.64, 4 sequences 1.85 / 1.77 / 2.56;
+    at 512 tokens 1.595 / 1.578 / 1.582 and 1.66 / 1.67 / 2.53, at 128 tokens 1.51 / 1.54 / 1.57).  Measured alone (us; 24 heads over
     8 KV heads of 128, six warps x two tiles; 1 / 2 / 4 / 8 CTAs, and the split kernels + merge):
     2,100 keys: 1 sequence 18.4 / 12.5 / 8.8 / 9.6 (12), 4: 19.0 / 13.3 / 12.3 / 29 , 8: 19.5 / 16.1 / 23.8 / 51 (22);
     8,000 keys: 1: 61 / 34 / 21 / 15.6 (18), 2: 62 / 35 / 21.5 / 30, 4: 63 / 36 / 27.5 / 46, 8: 64 / 44.8 / 52 / 80 (56),
     16: 88 / 85 / 101 / 149 (90).  530 keys, 8 sequences: 7.0 / 9.0 / 15.4 / 41."""
     if KNOBS.decode_warps_cluster > 0:
         return int(KNOBS.decode_warps_cluster)
-    if context_class <= 0:
+    if context_class < MID_CONTEXT:
         return 1
     # Inside the decode step the attention's CTAs (a whole SM's shared memory and two thirds of its
     # registers each) must leave SMs to the products before and after it, which overlap it: with more than
@@ -448,7 +454,7 @@ def decode_warps_cluster(n_seqs: int, context_class: int, n_kv_heads: int, sm_co
     # 2.62, 8: 2.05 / 2.93 / 3.13; 6,000 tokens: 2: 2.77 / 2.20 / 1.95, 4: 2.82 / 2.27 / 2.93, 8: 2.88 / 3.49 / 3.68).
     budget = (sm_count or _sm_count()) * 7 // 16
     pairs = max(1, n_seqs * n_kv_heads)
-    for cr in ((8, 4, 2) if context_class >= 2 else (4, 2)):
+    for cr in ((8, 4, 2) if context_class >= VERY_LONG_CONTEXT else (4, 2)):
         if pairs * cr <= budget:
             return cr
     return 1

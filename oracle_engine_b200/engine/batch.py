@@ -87,7 +87,7 @@ def build_plan(seqs: list, starts: list, pad_seqs: int = 0, pad_tokens: int = 0,
 
 # Steps are classed by the longest sequence they touch: kernels may be chosen by the class, and a
 # captured decode graph is kept per class, so the choice stays valid as sequences grow.
-CONTEXT_CLASS_TOKENS = [1536, 4096]      # class 0 up to the first, 1 up to the second, 2 beyond
+CONTEXT_CLASS_TOKENS = [768, 1536, 4096]     # class 0 up to the first, 1 up to the second, 2 up to the third, 3 beyond
 
 
 def context_class(n_tokens: int) -> int:

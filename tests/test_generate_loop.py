@@ -221,29 +221,32 @@ def test_decode_kernel_rules_depend_on_sizes_only():
     the context classes cut where they say."""
     from oracle_engine_b200.csrc import ops_tc
     from oracle_engine_b200.engine import batch
-    assert [batch.context_class(n) for n in (1, 1536, 1537, 4096, 4097, 100000)] == [0, 0, 1, 1, 2, 2]
+    assert [batch.context_class(n) for n in (1, 768, 769, 1536, 1537, 4096, 4097, 100000)] == [0, 0, 1, 1, 2, 2, 3, 3]
     uses = lambda n_seqs, cls: ops_tc.decode_uses_warps(n_seqs, cls, 128, 24, 8, sm_count=148)
-    assert [uses(b, c) for c in (0, 1, 2) for b in (1, 8, 64, 500)] == [True] * 12          # wherever it can be used
-    # few sequences with long contexts: 2, 4 or 8 CTAs (a cluster) per (sequence, KV head), at most about 64 CTAs in all
+    assert [uses(b, c) for c in (0, 1, 2, 3) for b in (1, 8, 64, 500)] == [True] * 16       # wherever it can be used
+    # few sequences past 768 tokens: 2, 4 or 8 CTAs (a cluster) per (sequence, KV head), at most about 64 CTAs in all
     cluster = lambda n_seqs, cls: ops_tc.decode_warps_cluster(n_seqs, cls, 8, sm_count=148)
     assert [cluster(b, 0) for b in (1, 4, 8, 64)] == [1, 1, 1, 1]
     assert [cluster(b, 1) for b in (1, 2, 3, 4, 5, 8, 64)] == [4, 4, 2, 2, 1, 1, 1]
-    assert [cluster(b, 2) for b in (1, 2, 3, 4, 5, 8, 64)] == [8, 4, 2, 2, 1, 1, 1]
+    assert [cluster(b, 2) for b in (1, 2, 3, 4, 5, 8, 64)] == [4, 4, 2, 2, 1, 1, 1]
+    assert [cluster(b, 3) for b in (1, 2, 3, 4, 5, 8, 64)] == [8, 4, 2, 2, 1, 1, 1]
     with ops_tc.knobs(decode_warps_cluster=2):
         assert cluster(64, 0) == 2
     # its form, (warps, tiles in a warp's ring): the most warps whose CTAs are all resident at once (1, 2 or 4 an SM)
     shape = lambda n_seqs, cls, hd=128, kvh=8: ops_tc.decode_warps_shape(n_seqs, cls, hd, kvh, sm_count=148)
     assert [shape(b, 0) for b in (1, 18, 19, 37, 38, 64, 74, 75, 128)] == \
         [(6, 2), (6, 2), (2, 3), (2, 3), (1, 3), (1, 3), (1, 3), (1, 3), (1, 3)]
+    assert [shape(b, 1) for b in (18, 19, 38, 128)] == [(6, 2), (2, 3), (1, 3), (1, 3)]         # up to 1,536 tokens alike
     # long contexts: no one-warp form; past one round of CTAs the fullest last round, equal ones to the smaller CTAs
-    assert [shape(b, 1) for b in (18, 19, 37, 38, 48, 64, 96, 128)] == \
+    assert [shape(b, c) for c in (2, 3) for b in (18, 19, 37, 38, 48, 64, 96, 128)] == 2 * \
         [(6, 2), (2, 3), (2, 3), (6, 2), (6, 2), (2, 3), (2, 3), (6, 2)]
-    assert shape(4, 0, hd=256, kvh=2) == (2, 3) and shape(100, 1, hd=256, kvh=2) == (2, 3)     # 6 x 2 does not fit an SM there
+    assert shape(4, 0, hd=256, kvh=2) == (2, 3) and shape(100, 2, hd=256, kvh=2) == (2, 3)     # 6 x 2 does not fit an SM there
     assert shape(30, 0, hd=64, kvh=8) == (6, 2) and shape(40, 0, hd=64, kvh=8) == (2, 3)       # two CTAs of 6 x 2 an SM
     with ops_tc.knobs(decode_warps_shape=(4, 3)):
         assert shape(64, 0) == (4, 3)
     assert not ops_tc.decode_uses_warps(8, 0, 128, 64, 2, sm_count=148)                      # 32 heads per KV head
     splits = lambda n_seqs, cls, pages=128: ops_tc.decode_splits(n_seqs, 8, 148, pages, cls, 3)
     assert [splits(b, 0) for b in (1, 8, 24, 64)] == [32, 5, 2, 1]                            # about two CTAs an SM
-    assert [splits(b, 2) for b in (1, 8, 24, 32, 40, 64)] == [32, 6, 2, 3, 4, 3]              # the last round filled
-    assert splits(8, 2, pages=4) == 4 and splits(1, 0, pages=3) == 3                          # never more than the pages
+    assert [splits(b, 1) for b in (1, 8, 24, 64)] == [32, 5, 2, 1]
+    assert [splits(b, 3) for b in (1, 8, 24, 32, 40, 64)] == [32, 6, 2, 3, 4, 3]              # the last round filled
+    assert splits(8, 3, pages=4) == 4 and splits(1, 0, pages=3) == 3                          # never more than the pages

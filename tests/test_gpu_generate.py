@@ -166,7 +166,7 @@ def test_long_decoding_from_the_first_token(model_dirs, plain_models, tmp_path, 
 def test_decoding_across_the_context_classes(model_dirs, plain_models, tmp_path, monkeypatch):
     """Decode graphs are kept per context class (kernels may be chosen by it): sequences that grow
     across the boundaries while they decode, with the boundaries moved down to 96 and 170 tokens so
-    that the tiny model crosses them; both decode attention kernels run in one generation."""
+    that the tiny model crosses them."""
     from oracle_engine_b200.engine import batch, step
     from oracle_engine_b200.engine.engine import Engine
     monkeypatch.setattr(batch, "CONTEXT_CLASS_TOKENS", [96, 170])
@@ -224,15 +224,15 @@ def test_few_sequences_decoding_across_the_context_classes(n, model_dirs, plain_
     from oracle_engine_b200.csrc import ops_tc
     from oracle_engine_b200.engine import batch
     from oracle_engine_b200.engine.engine import Engine
-    monkeypatch.setattr(batch, "CONTEXT_CLASS_TOKENS", [96, 170])
+    monkeypatch.setattr(batch, "CONTEXT_CLASS_TOKENS", [64, 96, 170])
     plain = plain_models["E"]
     kvh = plain.cfg["num_key_value_heads"]
-    sizes = [ops_tc.decode_warps_cluster(n, c, kvh) for c in (0, 1, 2)]
-    assert sizes[0] == 1 and sizes[1] > 1 and sizes[2] >= sizes[1]
+    sizes = [ops_tc.decode_warps_cluster(n, c, kvh) for c in (0, 1, 2, 3)]
+    assert sizes[0] == 1 and sizes[1] > 1 and sizes[2] == sizes[1] and sizes[3] >= sizes[2]
     eng = Engine.from_pretrained(model_dirs["E"], dtype="bfloat16", max_tokens=n * 256)
     lens = [230 - 7 * i for i in range(n)]
     requests = [helpers.random_tokens(m, plain.cfg["vocab_size"], 700 + i) for i, m in enumerate(lens)]
-    steps = helpers.batched_steps(requests, [50 + 3 * i for i in range(n)], n)
+    steps = helpers.batched_steps(requests, [40 + 3 * i for i in range(n)], n)
     out = helpers.TraceRunner(eng, tmp_path / "few").run(steps)
     got = helpers.collect(steps, out, requests)
     for i, toks in enumerate(requests):
@@ -240,7 +240,7 @@ def test_few_sequences_decoding_across_the_context_classes(n, model_dirs, plain_
         err = np.abs(got[i] - want).max(axis=1)
         assert err.max() < TOL["bfloat16"], f"request {i}: first bad position {int((err >= TOL['bfloat16']).argmax())}"
     classes = {key[1] for key, g in eng.stepper._graphs.items() if g.graph is not None}
-    assert classes == {0, 1, 2}
+    assert classes == {0, 1, 2, 3}
     eng.cache.check()
 
 

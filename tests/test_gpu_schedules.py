@@ -136,7 +136,7 @@ def test_one_sequence_across_both_context_class_boundaries(real_heads, tmp_path)
     from oracle_engine_b200.csrc import ops, ops_tc
     from oracle_engine_b200.engine import batch
     from oracle_engine_b200.engine.engine import Engine
-    assert batch.CONTEXT_CLASS_TOKENS == [1536, 4096]
+    assert batch.CONTEXT_CLASS_TOKENS == [768, 1536, 4096]
     folder, plain = real_heads
     toks = helpers.random_tokens(4300, 512, 77)
     plan = [1500] + [1] * 100 + [2450] + [1] * 250
@@ -154,25 +154,25 @@ def test_one_sequence_across_both_context_class_boundaries(real_heads, tmp_path)
     tol = _tolerance(want)
     assert err.max() < tol, f"first bad position {int((err >= tol).argmax())}: {err.max()} (tolerance {tol})"
     eng.check_device_errors()
-    # which decode kernel ran in each class: the one whose warps split the keys, with one CTA per
-    # (sequence, KV head) in class 0 and, 8 pairs being few, clusters of 4 and of 8 CTAs in the longer classes
+    # which decode kernel ran in each class (the decoding here runs in classes 1 to 3): the one whose warps
+    # split the keys, and, 8 (sequence, KV head) pairs being few, with clusters of 4 CTAs and, past 4,096 tokens, of 8
     kinds = set(seen.attention())
     clusters = sorted(c for w, c in kinds if w == "attention_decode_warps")
-    assert clusters == [ops_tc.decode_warps_cluster(1, c, 8) for c in (0, 1, 2)] == [1, 4, 8]
+    assert clusters == sorted({ops_tc.decode_warps_cluster(1, c, 8) for c in (1, 2, 3)}) == [4, 8]
     assert not any(w == "attention_mma" for w, _ in kinds)
     assert ("attention_tcgen05", None) in kinds            # the prompt pieces
 
 
 def test_sixty_four_sequences_across_the_first_boundary(real_heads, tmp_path):
     """64 sequences of 1,460 to 1,523 tokens decode 90 tokens each, across 1,536: 512 (sequence, KV
-    head) pairs go to one-warp CTAs with rings of three tiles in class 0 (four CTAs an SM) and to
-    two-warp CTAs in class 1.  CUDA
+    head) pairs go to one-warp CTAs with rings of three tiles up to 1,536 tokens (four CTAs an SM) and to
+    two-warp CTAs beyond.  CUDA
     graphs on, as in serving; every decoded position against the plain model."""
     from oracle_engine_b200.csrc import ops_tc
     from oracle_engine_b200.engine.engine import Engine
     folder, plain = real_heads
     n = 64
-    assert ops_tc.decode_warps_shape(n, 0, 128, 8) == (1, 3) and ops_tc.decode_warps_shape(n, 1, 128, 8) == (2, 3)
+    assert ops_tc.decode_warps_shape(n, 1, 128, 8) == (1, 3) and ops_tc.decode_warps_shape(n, 2, 128, 8) == (2, 3)
     lens = [1460 + i + 90 for i in range(n)]
     requests = [helpers.random_tokens(m, 512, 900 + i) for i, m in enumerate(lens)]
     steps = helpers.batched_steps(requests, [1460 + i for i in range(n)], n)
@@ -181,7 +181,7 @@ def test_sixty_four_sequences_across_the_first_boundary(real_heads, tmp_path):
     eng = Engine.from_pretrained(folder, dtype="bfloat16", max_tokens=n * 1664)
     out = helpers.TraceRunner(eng, tmp_path / "b64").run(steps)
     classes = {key[1] for key, g in eng.stepper._graphs.items() if g.graph is not None}
-    assert classes == {0, 1}
+    assert classes == {1, 2}
     eng.check_device_errors()
     worst = 0.0
     for i, toks in enumerate(requests):

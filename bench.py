@@ -255,6 +255,32 @@ def time_prefill(engine, lengths, vocab, runs=9, warmup=3):
     return statistics.median(times), engine.model.step_flops([0] * len(lengths), lengths, len(lengths))
 
 
+GRID_BATCHES = (1, 2, 3, 4, 6, 8, 10, 12, 16, 17, 24, 32, 33, 48, 64, 96, 128)
+GRID_CONTEXTS = (128, 512, 1400, 2048, 6000)
+
+
+def decode_grid(cfg, dtype, warmup, settle_ms, file):
+    """The decode step over batch sizes and contexts: ms a step and, in brackets, the step's bytes over
+    its time as a fraction of the measured HBM figure.  A cliff between neighbours in this table is how the
+    faults of the launch chain were found (a kernel timed alone does not show them)."""
+    from oracle_engine_b200.engine.engine import Engine
+    pk = peaks()
+    print("sequences  " + "  ".join(f"{c:>6d} tokens" for c in GRID_CONTEXTS), file=file, flush=True)
+    for batch in GRID_BATCHES:
+        cells = []
+        for plen in GRID_CONTEXTS:
+            if batch * (plen + 128) > 420000:            # keeps the cache under 50 GB
+                cells.append("       -     ")
+                continue
+            engine = Engine.from_config(cfg, seed=SEED, dtype=dtype, max_tokens=batch * (plen + 128),
+                                        max_seq_len=8192, n_slots=batch)
+            d = time_decode(engine, [plen] * batch, 30, warmup, cfg.vocab_size, 3, settle_ms)
+            frac = d["step_bytes"] / (d["ms_per_step"] * 1e-3) / 1e9 / pk["hbm_gbs"]
+            cells.append(f"{d['ms_per_step']:6.3f} ({frac:4.2f})")
+            del engine
+        print(f"{batch:9d}  " + "  ".join(cells), file=file, flush=True)
+
+
 def profile_decode(engine, lengths, vocab, file):
     """Device time per kind of kernel of the prompt step (events between the launches) and of one
     decode step (events inside the captured graph), as tables on `file`.  An event between two
@@ -418,6 +444,9 @@ def main():
     ap.add_argument("--regions", type=int, default=5, help="timed regions of --steps steps; the median is reported")
     ap.add_argument("--settle-ms", type=int, default=100,
                     help="idle time between a region's prompt step and its warm-up steps (see time_decode; 0: none)")
+    ap.add_argument("--grid", action="store_true",
+                    help="print the decode step's time over batch sizes and context lengths on standard error, "
+                         "and nothing else")
     ap.add_argument("--profile", action="store_true",
                     help="print device time per kind of kernel of a prompt step and a decode step on standard error, "
                          "and nothing else")
@@ -444,6 +473,9 @@ def main():
         raw["num_hidden_layers"] = args.layers
     cfg = LlamaConfig.from_dict(raw)
     pk = peaks()
+    if args.grid:
+        decode_grid(cfg, args.dtype, args.warmup, args.settle_ms, sys.stderr)
+        return 0
     points_wanted = not args.no_points and not baseline_load and not args.profile
     max_batch = max(batch, 64) if points_wanted else batch
     engine = Engine.from_config(cfg, seed=SEED, dtype=args.dtype, max_tokens=max_batch * context,

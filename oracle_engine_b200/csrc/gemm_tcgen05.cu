@@ -180,6 +180,8 @@ struct GemmArgs {
     float* workspace;           // [splits][tiles_a][tiles_b][n_tile][128] float32 when splits > 1
     int* counters;              // [tiles_a * tiles_b], zero between launches
     unsigned long long wait_ns; // after this long a wait on an mbarrier gives up (error flag, the kernel returns)
+    const uint8_t* pf_ptr;      // the weights of the product after this one: their first pf_bytes are asked into the L2
+    long long pf_bytes;         // by this kernel's TMA role once its own loads are out (0: none)
     int withhold_release;       // tests of that path: the epilogue never hands an accumulator back, so that the
                                 // MMA role's wait for one runs out (0 in every other use)
 };
@@ -473,6 +475,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (++s == g.stages) { s = 0; phase ^= 1u; }
                 }
             }
+            // This CTA's own loads are on their way.  While its last MMAs, its epilogue and the next kernel's
+            // set-up run, the memory would idle: the first bytes of the next product's weights go to the L2.
+            if (g.pf_bytes > 0 && elect_one()) {
+                const long long per = ((g.pf_bytes / gridDim.x) + 127) & ~127ll;
+                const long long begin = (long long)blockIdx.x * per;
+                const long long n = min(per, g.pf_bytes - begin);
+                for (long long off = 0; off < n; off += 32768) {
+                    const uint32_t sz = (uint32_t)min(32768ll, n - off) & ~15u;
+                    if (sz) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(g.pf_ptr + begin + off), "r"(sz) : "memory");
+                }
+            }
+            __syncwarp();
         }
     } else if (warp == 1) {
         // ---------------- MMA issue ----------------
@@ -781,6 +795,8 @@ inline long long kb_ns(int n_tile) { return n_tile <= 128 ? 330 : n_tile <= 192 
 int g_force_tile = 0;       // measurements only: tile width and schedule for many tokens (0, -1: chosen here)
 int g_force_streamk = -1;
 int g_force_narrow = -1;      // 48..128 tokens: 1 narrow tiles, 0 swap-AB with split K, -1 by the shape
+const uint8_t* g_pf_ptr = nullptr;   // set by oe_gemm_tc_prefetch for the next launch
+long long g_pf_bytes = 0;
 int g_force_cluster = -1;     // 0: K splits add up through the workspace even where a cluster could
 int g_force_atoms = -1;       // up to 128 tokens, swap-AB: 64-deep atoms per k-block (1 or 2; -1 by the shape)
 unsigned long long g_wait_ns = WAIT_LIMIT_NS;   // the limit the next launches give their waits
@@ -862,6 +878,7 @@ int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, 
     g.workspace = workspace; g.counters = counters; g.splits = 1; g.streamk = 0; g.sk_tiles = 0; g.cluster = 1;
     g.atoms = 1;
     g.wait_ns = g_wait_ns; g.withhold_release = g_withhold_release;
+    g.pf_ptr = g_pf_ptr; g.pf_bytes = g_pf_bytes; g_pf_ptr = nullptr; g_pf_bytes = 0;
     CUtensorMap map_a, map_b;
     dim3 grid;
     int n_kb = (K + BLOCK_K - 1) / BLOCK_K;
@@ -1010,6 +1027,9 @@ int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, 
 // (cluster = 0) K splits of few tokens through the workspace instead of a cluster, and (narrow = 1 / 0)
 // up to 128 tokens narrow tiles without a split or swap-AB with split K, and (atoms = 1 / 2) how many
 // 64-deep swizzle atoms a k-block of those products holds.
+// The next launch asks the first `bytes` bytes at `ptr` (the weights of the product that follows it) into the L2.
+void oe_gemm_tc_prefetch(const void* ptr, long long bytes) { g_pf_ptr = (const uint8_t*)ptr; g_pf_bytes = bytes > 0 ? bytes : 0; }
+
 void oe_gemm_tc_force(int n_tile, int streamk, int cluster, int narrow, int atoms) {
     g_force_tile = n_tile; g_force_streamk = streamk; g_force_cluster = cluster; g_force_narrow = narrow;
     g_force_atoms = atoms;

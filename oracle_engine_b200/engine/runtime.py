@@ -31,6 +31,10 @@ class Runtime:
     dtype: torch.dtype
     device: torch.device
     tensor_cores: bool = True          # bf16 only: use the tcgen05 / mma kernels where they take the shape
+    # A hint for the part that runs now: the weight matrix that the part after it streams first (or
+    # None).  The model and the block set it before they call a part; a part's last product may ask
+    # the first megabytes of it into the L2 while its own epilogue runs (csrc/ops_tc.py: gemm(then=)).
+    next_weights: torch.Tensor | None = None
 
     def empty(self, *shape, dtype=None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)

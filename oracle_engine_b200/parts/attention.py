@@ -80,6 +80,9 @@ class GQAAttention(Part):
             seen = tri(first, last)
         return count * products + 4.0 * self.H * self.hd * seen                  # q.k and p.v
 
+    def first_weights(self):
+        return self.w_qkv
+
     def forward(self, h, residual, ctx, cache, state, owns_cache=True):
         T = h.shape[0]
         q_width = self.H * self.hd
@@ -92,4 +95,5 @@ class GQAAttention(Part):
         o = self.rt.empty(T, q_width)
         ad.mixer_core(self.rt, o, qkv, cos, sin, cache, ctx, self.H, self.KVH, self.hd, self.window, self.scale,
                       owns_cache)
-        matmul_nt(self.rt, residual, o, self.w_o, accumulate=True, early=chain_flags("mixer_out", T))
+        matmul_nt(self.rt, residual, o, self.w_o, accumulate=True, early=chain_flags("mixer_out", T),
+                  then=self.rt.next_weights)

@@ -17,9 +17,26 @@ class PreNormBlock:
     def parts(self):
         return [p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward) if p is not None]
 
+    def first_weights(self):
+        """The weight matrix this block streams first (a hint for the part that runs before it), or None."""
+        return _first_weights(self.mixer)
+
     def forward(self, x, ctx, cache, state, owns_cache=True):
+        rt = getattr(self.mixer, "rt", None)
+        after = getattr(rt, "next_weights", None)          # what the model says comes after this block
         h = self.mixer_norm.forward(x)
+        if rt is not None:
+            rt.next_weights = _first_weights(self.feed_forward) if self.feed_forward is not None else after
         self.mixer.forward(h, x, ctx, cache, state, owns_cache)
         if self.feed_forward is not None:
             h = self.ffn_norm.forward(x)
+            if rt is not None:
+                rt.next_weights = after
             self.feed_forward.forward(h, x, ctx)
+        if rt is not None:
+            rt.next_weights = None
+
+
+def _first_weights(part):
+    f = getattr(part, "first_weights", None)
+    return f() if f is not None else None

@@ -47,14 +47,18 @@ class SwiGLU(Part):
     def flops(self, start, count):
         return count * 2.0 * 3 * self.D * self.FF
 
+    def first_weights(self):
+        return self.w_gu
+
     def forward(self, h, residual, ctx):
         T = h.shape[0]
         a = self.rt.empty(T, self.FF)
         if self.fused:
             from ..csrc import ops_tc
-            ops_tc.gemm(a, h, self.w_gu, swiglu=True, early=chain_flags("ffn_in", T))
+            ops_tc.gemm(a, h, self.w_gu, swiglu=True, early=chain_flags("ffn_in", T), then=self.w_down)
         else:
             gu = self.rt.empty(T, 2 * self.FF)
             matmul_nt(self.rt, gu, h, self.w_gu)
             ops.swiglu(a, gu)
-        matmul_nt(self.rt, residual, a, self.w_down, accumulate=True, early=chain_flags("ffn_out", T))
+        matmul_nt(self.rt, residual, a, self.w_down, accumulate=True, early=chain_flags("ffn_out", T),
+                  then=self.rt.next_weights)

@@ -38,11 +38,12 @@ def chain_flags(product: str, n_tokens: int) -> int:
 
 
 def matmul_nt(rt, out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool = False,
-              early: int = 0) -> None:
-    """early: START_EARLY and TRIGGER_LATE flags (above); other kernels ignore them."""
+              early: int = 0, then: torch.Tensor | None = None) -> None:
+    """early: START_EARLY and TRIGGER_LATE flags (above); other kernels ignore them.
+    then: the weight matrix of the product that runs after this one (a hint, see ops_tc.gemm)."""
     if rt.dtype == torch.bfloat16 and rt.tensor_cores:
         from ..csrc import ops_tc
         if ops_tc.gemm_supported(a, w, out):
-            ops_tc.gemm(out, a, w, accumulate=accumulate, early=int(early))
+            ops_tc.gemm(out, a, w, accumulate=accumulate, early=int(early), then=then)
             return
     ops.gemm_simple(out, a, w, accumulate=accumulate)

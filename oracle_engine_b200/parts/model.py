@@ -123,7 +123,12 @@ class DecoderModel:
         for i in range(lo, hi):
             e = self.schedule[i]
             owner = i if e.cache_from is None else e.cache_from
+            # a hint for the entry's last product: the weights the next entry streams first
+            nxt = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
+            first = getattr(nxt, "first_weights", None)
+            self.rt.next_weights = first() if first is not None else None
             self.layers[e.layer].forward(x, ctx, cache_views[owner], state_views[i], e.cache_from is None)
+        self.rt.next_weights = None
 
     def logits(self, x, ctx):
         if ctx.n_want == 0:

@@ -24,6 +24,12 @@ from ..csrc import ops
 from .batch import SequenceStep, StepBuffers, build_plan, context_class
 
 _BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+# A step of up to this many tokens that is no decode step (a short prompt, a piece of one, prompts and single
+# tokens mixed) is captured as well, per padded token count, padded batch size and context class: launched
+# one by one its 230 kernels cost the host 3.1 ms, twice what the device needs for them.
+GRAPH_STEP_TOKENS = 128
+MAX_TOKEN_GRAPHS = 64
+_TOKEN_BUCKETS = (16, 32, 64, 128)
 
 
 class StepError(ValueError):
@@ -70,6 +76,7 @@ class Stepper:
         self._stages = model.stages()
         self.use_graphs = bool(use_graphs and any(safe for safe, _, _ in self._stages))
         self._graphs: dict[tuple, _DecodeGraph] = {}      # (padded batch size, long context) -> graph
+        self._token_graphs: dict[tuple, _DecodeGraph] = {}    # (padded tokens, batch size, wanted rows; context class) -> graph
         self._eager_buffers: dict[tuple, StepBuffers] = {}
         self.launch_counter = None         # set by the bench to count kernel launches
 
@@ -122,8 +129,11 @@ class Stepper:
         for s, st in zip(seqs, starts):
             tables_changed |= self.cache.reserve(s.slot, st + len(s.tokens))
         decode = all(len(s.tokens) == 1 for s in seqs)
+        n_tokens = sum(len(s.tokens) for s in seqs)
         if decode and self.use_graphs:
             logits = self._step_graph(seqs, starts, tables_changed, device_tokens)
+        elif self.use_graphs and device_tokens is None and n_tokens <= GRAPH_STEP_TOKENS:
+            logits = self._step_graph_tokens(seqs, starts, n_tokens)
         else:
             logits = self._step_eager(seqs, starts, device_tokens)
         for s, st in zip(seqs, starts):
@@ -147,29 +157,9 @@ class Stepper:
         self.last_h2d_bytes = buf.bytes()
         return self.model.forward(ctx, self._cache_views(ctx), self._state_views)
 
-    def _step_graph(self, seqs, starts, tables_changed=True, device_tokens=None):
-        B = len(seqs)
-        bucket = _bucket(B)
-        # one graph per padded batch size and context class: kernels chosen by the class stay right
-        gkey = (bucket, context_class(max(starts) + 1))
-        g = self._graphs.get(gkey)
-        if g is None:
-            g = _DecodeGraph(bucket, StepBuffers(bucket, bucket, bucket, self._table_shapes(bucket), self.rt.device))
-            self._graphs[gkey] = g
-        key = tuple(s.slot for s in seqs)
-        if key == g.key and g.version == self.cache.version:
-            # the same sequences one token further: only tokens and positions change
-            g.buffers.update_decode(None if device_tokens is not None else [s.tokens[0] for s in seqs], starts, B)
-            ctx = g.ctx
-        else:
-            plan = build_plan(seqs, starts, pad_seqs=bucket, pad_tokens=bucket, want_all_rows=True)
-            tables = [self.cache.tables_for(gr.index, plan.seq_slot) for gr in self.cache.groups]
-            ctx = g.buffers.upload(plan, tables)
-            g.key, g.ctx, g.version = key, ctx, self.cache.version
-        if device_tokens is not None:         # after the copy of the step's tables, before the kernels
-            ctx.token_ids[:B].copy_(device_tokens[:B])
-        self.last_h2d_bytes = g.buffers.bytes()
-        g.runs += 1
+    def _run_graph(self, g, ctx):
+        """The forward pass of a step whose shapes are those of `g`: directly at the first use (loads the
+        kernels' modules), captured at the second, replayed from then on.  Returns the head's output."""
         views = self._cache_views(ctx)
         if g.graph is None and g.runs == 1:
             # first use of this batch size: run directly (loads the kernels' modules)
@@ -205,6 +195,62 @@ class Stepper:
                     graph.replay()
             ops.LAUNCHES[0] += g.n_kernels
             all_logits = logits_now if logits_now is not None else g.logits
+        return all_logits
+
+    def _step_graph_tokens(self, seqs, starts, n_tokens: int):
+        """A short step that is no decode step, through a graph of its padded shape.  Everything a kernel's
+        launch depends on is the graph's: the token count and the batch size are padded (padding tokens
+        belong to no sequence, padding sequences bring no token), the longest sequence's share of the
+        step counts as the whole padded step, and the wanted rows are padded with row 0 (to the padded
+        batch size when at most one row per sequence is wanted, as in generation, else to the padded
+        token count)."""
+        tb = next(b for b in _TOKEN_BUCKETS if n_tokens <= b)
+        bb = min(_bucket(len(seqs)), tb)
+        plan = build_plan(seqs, starts, pad_seqs=bb, pad_tokens=tb)
+        n_want = int(plan.want_rows.size)
+        wb = bb if n_want <= bb else tb
+        gkey = (tb, bb, wb, context_class(plan.max_kvlen))
+        g = self._token_graphs.get(gkey)
+        if g is None:
+            if len(self._token_graphs) >= MAX_TOKEN_GRAPHS:     # shapes beyond these run directly
+                return self._step_eager(seqs, starts)
+            g = _DecodeGraph(tb, StepBuffers(tb, bb, wb, self._table_shapes(bb), self.rt.device))
+            self._token_graphs[gkey] = g
+        want = np.zeros(wb, dtype=np.int32)
+        want[:n_want] = plan.want_rows
+        plan.want_rows = want
+        plan.max_qlen = tb
+        tables = [self.cache.tables_for(gr.index, plan.seq_slot) for gr in self.cache.groups]
+        ctx = g.buffers.upload(plan, tables)
+        self.last_h2d_bytes = g.buffers.bytes()
+        g.runs += 1
+        all_logits = self._run_graph(g, ctx)
+        return all_logits[:n_want] if n_want else None
+
+    def _step_graph(self, seqs, starts, tables_changed=True, device_tokens=None):
+        B = len(seqs)
+        bucket = _bucket(B)
+        # one graph per padded batch size and context class: kernels chosen by the class stay right
+        gkey = (bucket, context_class(max(starts) + 1))
+        g = self._graphs.get(gkey)
+        if g is None:
+            g = _DecodeGraph(bucket, StepBuffers(bucket, bucket, bucket, self._table_shapes(bucket), self.rt.device))
+            self._graphs[gkey] = g
+        key = tuple(s.slot for s in seqs)
+        if key == g.key and g.version == self.cache.version:
+            # the same sequences one token further: only tokens and positions change
+            g.buffers.update_decode(None if device_tokens is not None else [s.tokens[0] for s in seqs], starts, B)
+            ctx = g.ctx
+        else:
+            plan = build_plan(seqs, starts, pad_seqs=bucket, pad_tokens=bucket, want_all_rows=True)
+            tables = [self.cache.tables_for(gr.index, plan.seq_slot) for gr in self.cache.groups]
+            ctx = g.buffers.upload(plan, tables)
+            g.key, g.ctx, g.version = key, ctx, self.cache.version
+        if device_tokens is not None:         # after the copy of the step's tables, before the kernels
+            ctx.token_ids[:B].copy_(device_tokens[:B])
+        self.last_h2d_bytes = g.buffers.bytes()
+        g.runs += 1
+        all_logits = self._run_graph(g, ctx)
         # rows wanted by the caller, in order
         rows = [b for b, s in enumerate(seqs) if s.want]
         if not rows:

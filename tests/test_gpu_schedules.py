@@ -239,3 +239,48 @@ def test_real_widths_against_plain(tmp_path, hidden, heads, kv_heads, head_dim, 
         worst = max(worst, float(np.abs(got[i] - want).max()))
     assert scale > 0.5 and worst < 0.03 * scale + 0.02, f"max abs err {worst} at logit scale {scale}"
     eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_short_steps_run_as_captured_graphs(model_dirs, plain_models, tmp_path, dtype):
+    """Steps of up to 128 tokens that are no decode steps (short prompts, pieces, prompts mixed with
+    single tokens) run as CUDA graphs of their padded shape: four rounds of the same shapes with other
+    tokens, so that each shape is run directly, captured and replayed; wanted rows as in generation (the
+    last of a prompt) and all rows.  Every wanted row against the plain model, and the engine without
+    graphs gives the same float32 bits."""
+    from oracle_engine_b200.engine.engine import Engine
+    plain = plain_models["B"]
+    vocab = plain.cfg["vocab_size"]
+    shapes = [[23, 1, 1, 40, 1], [60, 1, 1], [1, 9, 1, 1, 30], [100, 1, 1, 1]]      # pieces of the requests of a round
+    requests, plans = [], []
+    for r in range(4):
+        for j, shape in enumerate(shapes):
+            requests.append(helpers.random_tokens(sum(shape), vocab, 1000 + 10 * r + j))
+            plans.append(shape)
+    steps = helpers.piece_steps(requests, plans, batch_size=len(shapes))
+    per_round = max(len(shape) for shape in shapes)
+    assert len(steps) == 4 * per_round
+    for k, s in enumerate(steps):                          # every other step of a round wants only each entry's last row
+        if (k % per_round) % 2 == 0:
+            s["entries"] = [dict(e, want=[len(e["tokens"]) - 1]) for e in s["entries"]]
+    outs = {}
+    for graphs in (True, False):
+        eng = Engine.from_pretrained(model_dirs["B"], dtype=dtype, max_tokens=1024, use_graphs=graphs)
+        outs[graphs] = helpers.TraceRunner(eng, tmp_path / f"g{int(graphs)}").run(steps)
+        if graphs:
+            used = [g for g in eng.stepper._token_graphs.values() if g.graph is not None]
+            assert used and max(g.runs for g in used) >= 3, "no short step was captured and replayed"
+        eng.cache.check()
+    logits = [plain.logits(toks).numpy() for toks in requests]
+    pos = [0] * len(requests)
+    for s in steps:
+        row = 0
+        for e in s["entries"]:
+            i = int(e["id"][1:])
+            for w in e["want"]:
+                got, want = outs[True][s["step"]][row], logits[i][pos[i] + w]
+                assert np.abs(got - want).max() < TOL[dtype], f"step {s['step']} request {i} position {pos[i] + w}"
+                if dtype == "float32":
+                    assert np.array_equal(got, outs[False][s["step"]][row])
+                row += 1
+            pos[i] += len(e["tokens"])

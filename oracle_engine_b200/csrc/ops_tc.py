@@ -40,6 +40,8 @@ KNOBS = _Knobs()
 @contextlib.contextmanager
 def knobs(**kw):
     """with knobs(prompt_kernel="mma", decode_splits=4): ...   pins choices inside the block.
+    (A CUDA graph keeps the choices its kernels were captured with: pin them around the engine's whole
+    life, or use an engine without graphs.)
 
     gemm_schedule = (n_tile, stream_k, cluster, narrow[, atoms]) of the one-SM tcgen05 product: its tile
     width for many tokens (0: chosen by the shape), its schedule (1: stream-K wherever the tiles

@@ -27,9 +27,9 @@ _BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 # A step of up to this many tokens that is no decode step (a short prompt, a piece of one, prompts and single
 # tokens mixed) is captured as well, per padded token count, padded batch size and context class: launched
 # one by one its 230 kernels cost the host 3.1 ms, twice what the device needs for them.
-GRAPH_STEP_TOKENS = 128
+GRAPH_STEP_TOKENS = 256
 MAX_TOKEN_GRAPHS = 64
-_TOKEN_BUCKETS = (16, 32, 64, 128)
+_TOKEN_BUCKETS = (16, 32, 64, 128, 256)
 
 
 class StepError(ValueError):

@@ -243,7 +243,7 @@ def test_real_widths_against_plain(tmp_path, hidden, heads, kv_heads, head_dim, 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_short_steps_run_as_captured_graphs(model_dirs, plain_models, tmp_path, dtype):
-    """Steps of up to 128 tokens that are no decode steps (short prompts, pieces, prompts mixed with
+    """Steps of up to 256 tokens that are no decode steps (short prompts, pieces, prompts mixed with
     single tokens) run as CUDA graphs of their padded shape: four rounds of the same shapes with other
     tokens, so that each shape is run directly, captured and replayed; wanted rows as in generation (the
     last of a prompt) and all rows.  Every wanted row against the plain model, and the engine without
@@ -252,6 +252,7 @@ def test_short_steps_run_as_captured_graphs(model_dirs, plain_models, tmp_path, 
     plain = plain_models["B"]
     vocab = plain.cfg["vocab_size"]
     shapes = [[23, 1, 1, 40, 1], [60, 1, 1], [1, 9, 1, 1, 30], [100, 1, 1, 1]]      # pieces of the requests of a round
+    # (the first step of a round has 184 tokens: the 256-token shape; the others the smaller ones)
     requests, plans = [], []
     for r in range(4):
         for j, shape in enumerate(shapes):

@@ -993,9 +993,29 @@ int oe_gemm_tc_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int K, 
                 }
             }
         }
+        g.tiles_b = (N + g.n_tile - 1) / g.n_tile;
+        // A few hundred tokens: tiles of 128 x 256 fill less than half of the SMs.  K is split over the CTAs
+        // of a cluster per tile, as for few tokens (8192 -> 3072 at 512 tokens: 48 tiles, 3 CTAs each).
+        // The caller that wants no split (workspace == nullptr) gets none.
+        const long long tiles_wide = (long long)g.tiles_a * ((N + 255) / 256);
+        if (!g.streamk && g_force_cluster != 0 && workspace != nullptr && N >= 256 && tiles_wide * 2 <= sm_count &&
+            n_kb >= 8 && g_force_tile == 0) {
+            int want = (int)(sm_count / tiles_wide);
+            if (want > n_kb / 4) want = n_kb / 4;
+            for (int cs = want < 8 ? want : 8; cs >= 2; cs--) {
+                const int fit = max_clusters(cs);
+                if (fit < 0) return -fit;
+                if (fit < tiles_wide) continue;
+                const int kb_per = (n_kb + cs - 1) / cs;
+                g.splits = (n_kb + kb_per - 1) / kb_per;
+                g.cluster = g.splits;
+                g.n_tile = 256;
+                g.tiles_b = (N + 255) / 256;
+                break;
+            }
+        }
         if ((rc = make_map(&map_a, A, M, K, lda, BLOCK_M))) return rc;
         if ((rc = make_map(&map_b, W, N, K, K, g.n_tile))) return rc;
-        g.tiles_b = (N + g.n_tile - 1) / g.n_tile;
     }
     const long long n_work = (long long)g.tiles_a * g.tiles_b * g.splits;
     if (n_work > 2147483647LL) return OE_ERR_UNSUPPORTED;

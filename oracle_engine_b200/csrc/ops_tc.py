@@ -128,9 +128,23 @@ def uses_skinny(M: int, N: int, K: int, kind: int) -> bool:
     return M <= SKINNY_MAX_TOKENS
 
 
-PAIR_MIN_TOKENS = 256       # from here on the two-SM kernel (gemm_tcgen05_pair.cu); measured against the one-SM kernel
-                            # at 2,048 / 4,096 tokens (us): 3072->16384 SwiGLU 134 / 150; 3072->3072 accumulate 39.2 /
-                            # 40.9 and 64.5 / 72.5; 8192->3072 accumulate 90.2 / 95.5 and 165 / 183
+PAIR_MIN_TOKENS = 129       # from here on the two-SM kernel (gemm_tcgen05_pair.cu), except where the one-SM kernel can
+                            # split K four ways or more over the CTAs of a cluster (few tiles, see uses_pair).  Measured
+                            # alone (us; pair / one-SM): 192 tokens 3072->5120 16.0 / 17.0, 3072->16384 SwiGLU 29.8 / 34.1,
+                            # 8192->3072 30.8 / 21.5, 3072->3072 15.6 / 14.7; 384 tokens 8192->3072 33.4 / 26.4, 3072->3072
+                            # 16.7 / 16.1; 512 tokens 34.2 / 33.4 and 17.4 / 18.6; 2,048 tokens 3072->16384 132 / 149,
+                            # 8192->3072 74 / 91
+
+
+def uses_pair(M: int, N: int, K: int, sm_count: int | None = None) -> bool:
+    """Whether a product of M tokens with an [N, K] weight goes to the two-SM kernel."""
+    if M < PAIR_MIN_TOKENS or N < 32:
+        return False
+    if M <= 384 and N >= 256 and K >= 2048:
+        tiles = -(-M // 128) * -(-N // 256)              # tiles of 128 x 256 of the one-SM kernel
+        if tiles * 4 <= (sm_count or _sm_count()):       # it splits K over a cluster of 4 to 8 CTAs per tile
+            return False
+    return True
 
 
 def _pair():
@@ -199,7 +213,7 @@ def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool =
                                              out.stride(0), kind, int(early), ops._stream())
         ops._check(code, "gemm_skinny", (M, N, K))
         return
-    if kernel == "pair" or (kernel == "auto" and M >= PAIR_MIN_TOKENS and N >= 32):
+    if kernel == "pair" or (kernel == "auto" and uses_pair(M, N, K, KNOBS.sm_count or None)):
         code = _pair().oe_gemm_pair_bf16(out.data_ptr(), a.data_ptr(), w.data_ptr(), M, N, K, a.stride(0), out.stride(0),
                                          kind, int(KNOBS.pair_max_tile), ops._stream())
         ops._check(code, "gemm_pair", (M, N, K))

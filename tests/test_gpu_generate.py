@@ -346,9 +346,9 @@ def test_generate_raises_when_a_kernel_reports_an_error(model_dirs):
     from oracle_engine_b200.csrc import ops_tc
     # without graphs: a captured graph would keep the arguments its kernels were captured with, the knob's too
     eng = _engine(model_dirs, "E", "bfloat16", max_tokens=2048, use_graphs=False)
-    prompts = [helpers.random_tokens(200, 389, 5)]                      # fewer than 256 tokens: the one-SM tcgen05 products
+    prompts = [helpers.random_tokens(100, 389, 5)]                      # up to 128 tokens: the one-SM tcgen05 products
     good = eng.generate(prompts, GenParams.greedy(3, ignore_eos=True))
-    with ops_tc.knobs(sm_count=1, gemm_waits=(2_000_000, 1)):           # six and eight tiles of the prompt's products on one CTA
+    with ops_tc.knobs(sm_count=1, gemm_waits=(2_000_000, 1)):           # the tiles of the prompt's products on one CTA
         with pytest.raises(RuntimeError, match="bounded wait"):
             eng.generate(prompts, GenParams.greedy(3, ignore_eos=True))
     assert eng.cache.slots.n_free == eng.cache.n_slots                  # the slots came back

@@ -257,6 +257,7 @@ def time_prefill(engine, lengths, vocab, runs=9, warmup=3):
 
 GRID_BATCHES = (1, 2, 3, 4, 6, 8, 10, 12, 16, 17, 24, 32, 33, 48, 64, 96, 128)
 GRID_CONTEXTS = (128, 512, 1400, 2048, 6000)
+GRID_PROMPTS = (16, 64, 128, 192, 256, 384, 512, 768, 1024, 1536, 2048, 4096, 8192)
 
 
 def decode_grid(cfg, dtype, warmup, settle_ms, file):
@@ -279,6 +280,12 @@ def decode_grid(cfg, dtype, warmup, settle_ms, file):
             cells.append(f"{d['ms_per_step']:6.3f} ({frac:4.2f})")
             del engine
         print(f"{batch:9d}  " + "  ".join(cells), file=file, flush=True)
+    # one prompt alone, over its length: ms of the step and its flops over the measured bf16 figure
+    engine = Engine.from_config(cfg, seed=SEED, dtype=dtype, max_tokens=2 * 8192, max_seq_len=8192, n_slots=2)
+    print("prompt tokens      ms   tokens/s   of the bf16 figure", file=file, flush=True)
+    for n in GRID_PROMPTS:
+        ms, flops = time_prefill(engine, [n], cfg.vocab_size, runs=5, warmup=3)
+        print(f"{n:13d}  {ms:6.2f}  {n / ms * 1e3:9.0f}   {flops / (ms * 1e-3) / 1e12 / pk['bf16_tflops']:.3f}", file=file, flush=True)
 
 
 def profile_decode(engine, lengths, vocab, file):

@@ -157,14 +157,23 @@ int oe_gemm_skinny_bf16(void* C, const bf16* A, const bf16* W, int M, int N, int
     // from there (timed steps of 1.714 ms, the device idle before them): only down triggering at its
     // top is as fast or faster (1 sequence 1.606 -> 1.577 ms); o starting early and triggering at its
     // top: 2.44 ms.  The caller decides.
-    // Warps and loads in flight per shape, from a sweep on B200 at 8 tokens: matrices with
-    // very many rows do best with small CTAs, long rows with more loads in flight.
+    // Warps and loads in flight per shape: matrices with many rows do best with small CTAs, long rows
+    // with more loads in flight.
 #define OE_SKINNY_LAUNCH(NT, WARPS, UNROLL)                                                                        \
     return oe_launch_ex((early & 1) != 0, gemm_skinny_kernel<NT, WARPS, UNROLL>, dim3(blocks), dim3(WARPS * 32), 0, st, C, A, \
                         W, M, N, K, lda, ldc, out_kind, (early >> 1) & 1)
-    if (M > 8) OE_SKINNY_LAUNCH(2, 8, 3);
-    if (blocks >= 4 * 148) OE_SKINNY_LAUNCH(1, 4, 3);
-    if (K > 4096) OE_SKINNY_LAUNCH(1, 8, 3);
+    if (M > 8) {
+        // 9 to 16 tokens, chosen inside the 28-layer decode step (16 sequences: 2.11 ms with 8 warps x 3 loads
+        // for every shape, 1.96 ms with these)
+        if (blocks >= 4 * 148) OE_SKINNY_LAUNCH(2, 4, 4);
+        if (blocks >= 256) OE_SKINNY_LAUNCH(2, 8, 2);
+        OE_SKINNY_LAUNCH(2, 8, 3);
+    }
+    // up to 8 tokens, chosen shape by shape inside the 28-layer decode step (8 sequences: 1.713 ms with the
+    // forms a sweep of the kernels alone had given, 4 warps x 3 loads for very many rows, 8 x 3 for long rows,
+    // 8 x 2 else; 1.670 ms with these)
+    if (blocks >= 256) OE_SKINNY_LAUNCH(1, 4, 4);
+    if (K > 4096) OE_SKINNY_LAUNCH(1, 8, 4);
     OE_SKINNY_LAUNCH(1, 8, 2);
 #undef OE_SKINNY_LAUNCH
 }

@@ -62,8 +62,8 @@ template <> struct Out4<bf16> {
     }
 };
 
-template <typename T>
-__global__ void __launch_bounds__(256)
+template <typename T, int NT>
+__global__ void __launch_bounds__(NT)
 rmsnorm_vec_kernel(T* y, const float* x, const float* __restrict__ w, int D, float eps) {
     __shared__ float red[32];
     constexpr int KEEP = 4;
@@ -77,11 +77,11 @@ rmsnorm_vec_kernel(T* y, const float* x, const float* __restrict__ w, int D, flo
     float ss = 0.f;
 #pragma unroll
     for (int j = 0; j < KEEP; j++) {
-        const int i = threadIdx.x + j * 256;
+        const int i = threadIdx.x + j * NT;
         keep[j] = i < n4 ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
         ss += keep[j].x * keep[j].x + keep[j].y * keep[j].y + keep[j].z * keep[j].z + keep[j].w * keep[j].w;
     }
-    for (int i = threadIdx.x + KEEP * 256; i < n4; i += 256) {
+    for (int i = threadIdx.x + KEEP * NT; i < n4; i += NT) {
         const float4 v = xr[i];
         ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
@@ -89,13 +89,13 @@ rmsnorm_vec_kernel(T* y, const float* x, const float* __restrict__ w, int D, flo
     const float s = 1.f / sqrtf(ss / (float)D + eps);
 #pragma unroll
     for (int j = 0; j < KEEP; j++) {
-        const int i = threadIdx.x + j * 256;
+        const int i = threadIdx.x + j * NT;
         if (i < n4) {
             const float4 g = wr[i];
             Out4<T>::store(yr + 4 * i, (keep[j].x * s) * g.x, (keep[j].y * s) * g.y, (keep[j].z * s) * g.z, (keep[j].w * s) * g.w);
         }
     }
-    for (int i = threadIdx.x + KEEP * 256; i < n4; i += 256) {
+    for (int i = threadIdx.x + KEEP * NT; i < n4; i += NT) {
         const float4 v = xr[i], g = wr[i];
         Out4<T>::store(yr + 4 * i, (v.x * s) * g.x, (v.y * s) * g.y, (v.z * s) * g.z, (v.w * s) * g.w);
     }
@@ -338,7 +338,7 @@ int oe_embed_gather_bf16(float* x, const bf16* table, const int* ids, int n_toke
 int oe_rmsnorm_f32(float* y, const float* x, const float* w, int rows, int D, float eps, cudaStream_t st) {
     if (rows <= 0) return 0;
     if (D % 4 == 0 && !(((uintptr_t)y | (uintptr_t)x | (uintptr_t)w) & 15))
-        return oe_launch(rmsnorm_vec_kernel<float>, dim3(rows), dim3(256), 0, st, y, x, w, D, eps);
+        return oe_launch(rmsnorm_vec_kernel<float, 256>, dim3(rows), dim3(256), 0, st, y, x, w, D, eps);
     const int launch_rc = oe_launch(rmsnorm_kernel<float>, dim3(rows), dim3(256), 0, st, y, x, w, D, eps);
     return launch_rc;
 }
@@ -352,7 +352,8 @@ int oe_rmsnorm_bf16(bf16* y, const float* x, const float* w, int rows, int D, fl
             if (D <= 3072) return oe_launch(rmsnorm_rows_kernel<bf16, 24>, grid, dim3(256), 0, st, y, x, w, rows, D, eps);
             return oe_launch(rmsnorm_rows_kernel<bf16, 32>, grid, dim3(256), 0, st, y, x, w, rows, D, eps);
         }
-        return oe_launch(rmsnorm_vec_kernel<bf16>, dim3(rows), dim3(256), 0, st, y, x, w, D, eps);
+        // 512 threads a row: inside the 28-layer decode step 1.4 % faster than 256 at 8 sequences (128: 4 % slower)
+        return oe_launch(rmsnorm_vec_kernel<bf16, 512>, dim3(rows), dim3(512), 0, st, y, x, w, D, eps);
     }
     const int launch_rc = oe_launch(rmsnorm_kernel<bf16>, dim3(rows), dim3(256), 0, st, y, x, w, D, eps);
     return launch_rc;

@@ -16,14 +16,15 @@ def mixer_core(rt, out, qkv, cos, sin, cache, ctx, H, KVH, hd, window, scale, ow
     """Rotation, cache write and attention of one attention mixer for the step's tokens."""
     if rt.dtype == torch.bfloat16 and rt.tensor_cores and ctx.all_decode and ctx.n_tokens == ctx.n_seqs:
         from ..csrc import ops_tc
-        # One CTA per (sequence, KV head) whose warps split the keys: one launch for rotation, cache
-        # write, attention and the merge, no scratch in global memory.
+        # One CTA (or, for few long sequences, one cluster of CTAs) per (sequence, KV head) whose warps
+        # split the keys: one launch for rotation, cache write, attention and the merge, no scratch in
+        # global memory.  Every model whose groups have up to 16 heads of a multiple of 32 dims goes here.
         if ops_tc.decode_uses_warps(ctx.n_seqs, getattr(ctx, "context_class", 0), hd, H, KVH):
             ops_tc.attention_decode_warps(out, qkv, cos, sin, cache.kv, cache.tables, ctx, H, KVH, hd, window,
                                           scale, owns_cache)
             return
-        # One kernel when the batch alone fills the GPU (no split over the keys); for small
-        # batches the split kernels plus a parallel merge are faster (measured).
+        # Larger groups: one kernel when the batch alone fills the GPU (no split over the keys), else
+        # rotation, the kernel that splits the keys over CTAs, and a merge.
         if ops_tc.decode_fused_supported(hd, H, KVH) and \
                 ops_tc.decode_splits_for(ctx.n_seqs, KVH, cache.tables, getattr(ctx, "context_class", 0), hd) == 1:
             ops_tc.attention_decode_fused(out, qkv, cos, sin, cache.kv, cache.tables, ctx, H, KVH, hd, window,

@@ -249,4 +249,15 @@ def test_decode_kernel_rules_depend_on_sizes_only():
     assert [splits(b, 0) for b in (1, 8, 24, 64)] == [32, 5, 2, 1]                            # about two CTAs an SM
     assert [splits(b, 1) for b in (1, 8, 24, 64)] == [32, 5, 2, 1]
     assert [splits(b, 3) for b in (1, 8, 24, 32, 40, 64)] == [32, 6, 2, 3, 4, 3]              # the last round filled
-    assert splits(8, 3, pages=4) == 4 and splits(1, 0, pages=3) == 3                          # never more than the pages
+    assert splits(8, 3, pages=4) == 4 and splits(1, 0, pages=3) == 3
+    # the products: the weight-streaming kernel up to 16 tokens; the two-SM kernel from 129 tokens on, except
+    # for weights with few tiles at up to 384 tokens, which the one-SM kernel splits over clusters
+    assert [ops_tc.uses_skinny(m, 3072, 3072, 0) for m in (1, 8, 9, 16, 17)] == [True, True, True, True, False]
+    shapes = ((3072, 8192), (3072, 3072), (5120, 3072), (16384, 3072))
+    assert [ops_tc.uses_pair(128, n, k, 148) for n, k in shapes] == [False] * 4
+    assert [ops_tc.uses_pair(200, n, k, 148) for n, k in shapes] == [False, False, True, True]
+    assert [ops_tc.uses_pair(385, n, k, 148) for n, k in shapes] == [True] * 4
+    # and their places in the launch chain: flags per product and token count
+    from oracle_engine_b200.parts.linear import START_EARLY, TRIGGER_LATE, chain_flags
+    assert chain_flags("mixer_out", 8) == START_EARLY | TRIGGER_LATE and chain_flags("mixer_out", 9) == TRIGGER_LATE
+    assert chain_flags("ffn_out", 1) == START_EARLY and chain_flags("ffn_out", 16) == START_EARLY | TRIGGER_LATE                          # never more than the pages

@@ -232,9 +232,14 @@ def time_e2e(engine, lengths, steps, warmup, vocab, lookahead=True):
             "checksum": f"{fnv1a(tokens):016x}", "tokens": len(tokens)}
 
 
-def time_prefill(engine, lengths, vocab, runs=9, warmup=3):
+def time_prefill(engine, lengths, vocab, runs=9, warmup=3, settle_ms=0):
     """Median device time of ONE step that takes prompts of the given lengths (packed, no padding),
-    wanting the last place of each; returns (ms, flops of that step)."""
+    wanting the last place of each; returns (ms, flops of that step).
+
+    settle_ms: the device is left idle that long before every step, so that each is timed alone, at the
+    clocks a lone prompt step gets.  Back to back (0) a dozen steps of 10 ms are a sustained load under the
+    power cap (2,048 tokens: 11.6 against 10.1 ms), which is what the measured bf16 figures distinguish as
+    "sustained" (1,354 TFLOP/s) and "burst" (1,631, the denominator used here)."""
     import torch
     from oracle_engine_b200 import SequenceStep
     prompts = random_prompts(lengths, vocab, 3000)
@@ -242,6 +247,8 @@ def time_prefill(engine, lengths, vocab, runs=9, warmup=3):
     for r in range(warmup + runs):
         slots = [engine.alloc() for _ in prompts]
         torch.cuda.synchronize()
+        if settle_ms > 0:
+            time.sleep(settle_ms / 1e3)
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         engine.step([SequenceStep(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
@@ -450,7 +457,8 @@ def main():
                          "(1b: 16 prompts of 64..2,048 tokens, 128 steps; 8b: 32 prompts of 128..4,096 tokens, 256 steps)")
     ap.add_argument("--regions", type=int, default=5, help="timed regions of --steps steps; the median is reported")
     ap.add_argument("--settle-ms", type=int, default=100,
-                    help="idle time between a region's prompt step and its warm-up steps (see time_decode; 0: none)")
+                    help="idle time between a region's prompt step and its warm-up steps, and before every timed "
+                         "prompt step (see time_decode, time_prefill; 0: none)")
     ap.add_argument("--grid", action="store_true",
                     help="print the decode step's time over batch sizes and context lengths on standard error, "
                          "and nothing else")
@@ -503,9 +511,13 @@ def main():
     prefill = None
     if not args.no_prefill:
         pre_lengths = lengths if baseline_load else [PREFILL_TOKENS]
-        ms, fl = time_prefill(engine, pre_lengths, cfg.vocab_size)
+        ms, fl = time_prefill(engine, pre_lengths, cfg.vocab_size, settle_ms=args.settle_ms)
         prefill = {"value": round(sum(pre_lengths) / (ms / 1e3), 1), "tokens": sum(pre_lengths), "ms": round(ms, 3),
                    "frac": round(fl / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+        if args.settle_ms > 0:                     # the same steps back to back: a sustained load under the power cap
+            ms_b2b, _ = time_prefill(engine, pre_lengths, cfg.vocab_size, runs=5)
+            prefill["ms_back_to_back"] = round(ms_b2b, 3)
+            prefill["settle_ms"] = args.settle_ms
 
     achieved = dec["step_bytes"] / (dec["ms_per_step"] / 1e3) / 1e9
     names = {"3b": "Llama 3.2 3B shape", "1b": "Llama 3.2 1B shape", "8b": "Llama 3.1 8B shape"}

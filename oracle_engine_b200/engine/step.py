@@ -29,6 +29,7 @@ _BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 # one by one its 230 kernels cost the host 3.1 ms, twice what the device needs for them.
 GRAPH_STEP_TOKENS = 256
 MAX_TOKEN_GRAPHS = 64
+MAX_GRAPH_WANTED_ROWS = 64
 _TOKEN_BUCKETS = (16, 32, 64, 128, 256)
 
 
@@ -208,7 +209,9 @@ class Stepper:
         bb = min(_bucket(len(seqs)), tb)
         plan = build_plan(seqs, starts, pad_seqs=bb, pad_tokens=tb)
         n_want = int(plan.want_rows.size)
-        wb = bb if n_want <= bb else tb
+        if n_want > max(bb, MAX_GRAPH_WANTED_ROWS):            # a graph keeps its logits buffer: [rows, vocabulary] float32
+            return self._step_eager(seqs, starts)
+        wb = bb if n_want <= bb else min(tb, MAX_GRAPH_WANTED_ROWS)
         gkey = (tb, bb, wb, context_class(plan.max_kvlen))
         g = self._token_graphs.get(gkey)
         if g is None:

@@ -5,6 +5,7 @@
     python -m oracle_engine_b200.csrc.microbench attention --batch 1 --prompt 2048
     python -m oracle_engine_b200.csrc.microbench attention --batch 8 --context 640 --decode warps
     python -m oracle_engine_b200.csrc.microbench norm --rows 2048 --width 3072
+    python -m oracle_engine_b200.csrc.microbench rope --tokens 4096
 
 In the manner of the reference's benchmark/micro_gemm.cpp (:97-128 correctness against a
 scalar double-precision product, :130-151 GFLOP/s), for the CUDA kernels of this library.
@@ -159,6 +160,38 @@ def run_norm(a):
     report(f"rmsnorm rows={rows} width={D}", us, rows * D * 6, 3.0 * rows * D, err)
 
 
+def run_rope(a):
+    """The rotation of q and k at each token's place and the write of k and v into the paged cache."""
+    dev = torch.device("cuda:0")
+    T, H, KVH, hd = a.tokens, a.heads, a.kv_heads, a.head_dim
+    half = hd // 2
+    width = (H + 2 * KVH) * hd
+    pages = (T + ops.PAGE - 1) // ops.PAGE
+    copies = max(2, (256 << 20) // (T * width * 2) + 1)
+    qkvs = [torch.randn(T, width, device=dev).bfloat16() for _ in range(copies)]
+    caches = [torch.zeros(pages, 2, KVH, ops.PAGE, hd, device=dev, dtype=torch.bfloat16) for _ in range(copies)]
+    tables = torch.arange(pages, device=dev, dtype=torch.int32)[None].contiguous()
+    tok_seq = torch.zeros(T, device=dev, dtype=torch.int32)
+    tok_pos = torch.arange(T, device=dev, dtype=torch.int32)
+    ang = torch.arange(T, dtype=torch.float64)[:, None] * (10000.0 ** (-torch.arange(half, dtype=torch.float64) / half))[None]
+    cos, sin = torch.cos(ang).float().to(dev), torch.sin(ang).float().to(dev)
+    # correctness: the last token's first query head and first key head
+    before = qkvs[0][T - 1].double().clone()
+    ops.rope_kv_write(qkvs[0], cos, sin, caches[0], tables, tok_seq, tok_pos, H, KVH, hd, True)
+    c, s_ = cos[T - 1].double(), sin[T - 1].double()
+
+    def rot(x):
+        return torch.cat([x[:half] * c - x[half:] * s_, x[:half] * s_ + x[half:] * c])
+    k_at = caches[0][(T - 1) // ops.PAGE, 0, 0, (T - 1) % ops.PAGE].double()
+    err = max((qkvs[0][T - 1, :hd].double() - rot(before[:hd])).abs().max().item(),
+              (k_at - rot(before[H * hd:(H + 1) * hd])).abs().max().item())
+    us = timed(lambda i: ops.rope_kv_write(qkvs[i % copies], cos, sin, caches[i % copies], tables, tok_seq, tok_pos,
+                                           H, KVH, hd, True), a.iters, a.once)
+    # reads q, k, v; writes q in place and k, v to the cache
+    report(f"rope_kv_write tokens={T} H={H} KVH={KVH} hd={hd}", us, T * (width + H * hd + 2 * KVH * hd) * 2,
+           3.0 * T * (H + KVH) * hd, err)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="microbench")
     sub = ap.add_subparsers(dest="what", required=True)
@@ -195,12 +228,17 @@ def main(argv=None):
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=2048)
     n.add_argument("--width", type=int, default=3072)
-    for p in (g, at, n):
+    r = sub.add_parser("rope")
+    r.add_argument("--tokens", type=int, default=4096)
+    r.add_argument("--heads", type=int, default=24)
+    r.add_argument("--kv-heads", type=int, default=8)
+    r.add_argument("--head-dim", type=int, default=128)
+    for p in (g, at, n, r):
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--once", action="store_true", help="run without graph or timing (for a profiler)")
     a = ap.parse_args(argv)
     ops.require_cuda()
-    {"gemm": run_gemm, "attention": run_attention, "norm": run_norm}[a.what](a)
+    {"gemm": run_gemm, "attention": run_attention, "norm": run_norm, "rope": run_rope}[a.what](a)
     return 0
 
 

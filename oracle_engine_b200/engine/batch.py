@@ -47,8 +47,9 @@ class StepPlan:
 
 
 def build_plan(seqs: list, starts: list, pad_seqs: int = 0, pad_tokens: int = 0,
-               want_all_rows: bool = False) -> StepPlan:
-    """seqs: SequenceStep list; starts: each sequence's cache length before the step."""
+               want_all_rows: bool = False, token_arrays: list | None = None) -> StepPlan:
+    """seqs: SequenceStep list; starts: each sequence's cache length before the step;
+    token_arrays: per sequence its tokens as an array where the caller has one already, else None."""
     B = len(seqs)
     qlens = [len(s.tokens) for s in seqs]
     T_real = sum(qlens)
@@ -64,7 +65,8 @@ def build_plan(seqs: list, starts: list, pad_seqs: int = 0, pad_tokens: int = 0,
     want = []
     row = 0
     for b, (s, st, n) in enumerate(zip(seqs, starts, qlens)):
-        token_ids[row:row + n] = s.tokens
+        ids = None if token_arrays is None else token_arrays[b]
+        token_ids[row:row + n] = s.tokens if ids is None else ids
         tok_seq[row:row + n] = b
         tok_pos[row:row + n] = np.arange(st, st + n, dtype=np.int32)
         seq_slot[b], seq_start[b], seq_qlen[b] = s.slot, st, n

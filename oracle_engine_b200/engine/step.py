@@ -93,6 +93,7 @@ class Stepper:
         if not seqs:
             raise StepError("a step needs at least one sequence")
         seen = set()
+        token_arrays = []
         for i, s in enumerate(seqs):
             if not self.cache.slots.is_held(s.slot):
                 raise StepError(f"sequence {i}: slot {s.slot} is not allocated")
@@ -101,9 +102,18 @@ class Stepper:
             seen.add(s.slot)
             if len(s.tokens) < 1:
                 raise StepError(f"sequence {i}: a step needs at least one token per sequence")
-            if not (0 <= min(s.tokens) and max(s.tokens) < self.vocab):
+            ids = None
+            if len(s.tokens) >= 64:       # a prompt: one pass over its list, and the plan reuses the array
+                ids = np.asarray(s.tokens, dtype=np.int64)
+                if ids.ndim != 1:
+                    raise StepError(f"sequence {i}: tokens must be a flat list of ids")
+                lo, hi = int(ids.min()), int(ids.max())
+            else:
+                lo, hi = min(s.tokens), max(s.tokens)
+            if not (0 <= lo and hi < self.vocab):
                 bad = [t for t in s.tokens if not 0 <= int(t) < self.vocab]
                 raise StepError(f"sequence {i}: token id {bad[0]} is outside the vocabulary [0, {self.vocab})")
+            token_arrays.append(ids)
             for w in s.want:
                 if not 0 <= int(w) < len(s.tokens):
                     raise StepError(f"sequence {i}: wanted place {w} is outside its {len(s.tokens)} tokens")
@@ -112,6 +122,7 @@ class Stepper:
             if self.cache.length(s.slot) + len(s.tokens) > self.model.spec.max_positions:
                 raise StepError(f"sequence {i}: {self.cache.length(s.slot)} + {len(s.tokens)} tokens exceed the "
                                 f"{self.model.spec.max_positions} positions the model was built for")
+        return token_arrays
 
     # ------------------------------------------------------------------ the step
     def step(self, seqs: list[SequenceStep], device_tokens: torch.Tensor | None = None) -> torch.Tensor | None:
@@ -122,7 +133,7 @@ class Stepper:
         device_tokens (int32 on the device, one per sequence; only for steps of one token
         each): the tokens are taken from there instead of from `seqs`, whose token values
         are placeholders; the host need not have seen them yet."""
-        self._validate(seqs)
+        token_arrays = self._validate(seqs)
         if device_tokens is not None and not all(len(s.tokens) == 1 for s in seqs):
             raise StepError("tokens on the device can only feed a step of one token per sequence")
         starts = [self.cache.length(s.slot) for s in seqs]
@@ -134,15 +145,15 @@ class Stepper:
         if decode and self.use_graphs:
             logits = self._step_graph(seqs, starts, tables_changed, device_tokens)
         elif self.use_graphs and device_tokens is None and n_tokens <= GRAPH_STEP_TOKENS:
-            logits = self._step_graph_tokens(seqs, starts, n_tokens)
+            logits = self._step_graph_tokens(seqs, starts, n_tokens, token_arrays)
         else:
-            logits = self._step_eager(seqs, starts, device_tokens)
+            logits = self._step_eager(seqs, starts, device_tokens, token_arrays)
         for s, st in zip(seqs, starts):
             self.cache.commit(s.slot, st + len(s.tokens))
         return logits
 
-    def _step_eager(self, seqs, starts, device_tokens=None):
-        plan = build_plan(seqs, starts)
+    def _step_eager(self, seqs, starts, device_tokens=None, token_arrays=None):
+        plan = build_plan(seqs, starts, token_arrays=token_arrays)
         key = (plan.n_tokens, plan.n_seqs, plan.want_rows.size)
         buf = self._eager_buffers.get(key)
         if buf is None:
@@ -198,7 +209,7 @@ class Stepper:
             all_logits = logits_now if logits_now is not None else g.logits
         return all_logits
 
-    def _step_graph_tokens(self, seqs, starts, n_tokens: int):
+    def _step_graph_tokens(self, seqs, starts, n_tokens: int, token_arrays=None):
         """A short step that is no decode step, through a graph of its padded shape.  Everything a kernel's
         launch depends on is the graph's: the token count and the batch size are padded (padding tokens
         belong to no sequence, padding sequences bring no token), the longest sequence's share of the
@@ -207,16 +218,16 @@ class Stepper:
         token count)."""
         tb = next(b for b in _TOKEN_BUCKETS if n_tokens <= b)
         bb = min(_bucket(len(seqs)), tb)
-        plan = build_plan(seqs, starts, pad_seqs=bb, pad_tokens=tb)
+        plan = build_plan(seqs, starts, pad_seqs=bb, pad_tokens=tb, token_arrays=token_arrays)
         n_want = int(plan.want_rows.size)
         if n_want > max(bb, MAX_GRAPH_WANTED_ROWS):            # a graph keeps its logits buffer: [rows, vocabulary] float32
-            return self._step_eager(seqs, starts)
+            return self._step_eager(seqs, starts, None, token_arrays)
         wb = bb if n_want <= bb else min(tb, MAX_GRAPH_WANTED_ROWS)
         gkey = (tb, bb, wb, context_class(plan.max_kvlen))
         g = self._token_graphs.get(gkey)
         if g is None:
             if len(self._token_graphs) >= MAX_TOKEN_GRAPHS:     # shapes beyond these run directly
-                return self._step_eager(seqs, starts)
+                return self._step_eager(seqs, starts, None, token_arrays)
             g = _DecodeGraph(tb, StepBuffers(tb, bb, wb, self._table_shapes(bb), self.rt.device))
             self._token_graphs[gkey] = g
         want = np.zeros(wb, dtype=np.int32)

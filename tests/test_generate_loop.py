@@ -261,3 +261,29 @@ def test_decode_kernel_rules_depend_on_sizes_only():
     from oracle_engine_b200.parts.linear import START_EARLY, TRIGGER_LATE, chain_flags
     assert chain_flags("mixer_out", 8) == START_EARLY | TRIGGER_LATE and chain_flags("mixer_out", 9) == TRIGGER_LATE
     assert chain_flags("ffn_out", 1) == START_EARLY and chain_flags("ffn_out", 16) == START_EARLY | TRIGGER_LATE                          # never more than the pages
+
+
+def test_step_plan_packs_unequal_sequences_with_padding():
+    """The packed plan of a step: rows in the order of the sequences, places counted per sequence, padding
+    tokens that belong to no sequence and padding sequences that bring no token; a prompt's tokens given as
+    an array (what the step's validation hands over) pack to the same plan as the list."""
+    import numpy as np
+    from oracle_engine_b200.engine.batch import SequenceStep, build_plan
+    seqs = [SequenceStep(4, [11, 12, 13], [0, 2]), SequenceStep(1, [21], []), SequenceStep(7, [31, 32], [1])]
+    starts = [0, 9, 64]
+    plan = build_plan(seqs, starts, pad_seqs=4, pad_tokens=8)
+    assert plan.n_seqs == 4 and plan.n_tokens == 8 and plan.n_real_tokens == 6
+    assert plan.token_ids.tolist() == [11, 12, 13, 21, 31, 32, 0, 0]
+    assert plan.tok_seq.tolist() == [0, 0, 0, 1, 2, 2, -1, -1]
+    assert plan.tok_pos.tolist() == [0, 1, 2, 9, 64, 65, 0, 0]
+    assert plan.seq_slot.tolist() == [4, 1, 7, -1] and plan.seq_qlen.tolist() == [3, 1, 2, 0]
+    assert plan.cu_q.tolist() == [0, 3, 4, 6, 6]
+    assert plan.want_rows.tolist() == [0, 2, 5]
+    assert (plan.max_qlen, plan.max_kvlen, plan.all_decode) == (3, 66, False)
+    arrays = [np.asarray(s.tokens, dtype=np.int64) if len(s.tokens) > 1 else None for s in seqs]
+    same = build_plan(seqs, starts, pad_seqs=4, pad_tokens=8, token_arrays=arrays)
+    for name in ("token_ids", "tok_seq", "tok_pos", "seq_slot", "seq_start", "seq_qlen", "cu_q", "want_rows"):
+        assert np.array_equal(getattr(plan, name), getattr(same, name)), name
+    with pytest.raises(ValueError, match="outside its 1 tokens"):
+        build_plan([SequenceStep(0, [5], [1])], [0])
+    assert build_plan([SequenceStep(0, [5], [0]), SequenceStep(1, [6], [])], [3, 4]).all_decode

@@ -453,6 +453,51 @@ def test_rope_kv_write():
         assert torch.equal(q_only, orig[:, :H * hd])
 
 
+@pytest.mark.parametrize("H,KVH,hd", [(3, 2, 32), (40, 8, 128), (5, 1, 48)])
+def test_rope_kv_write_many_tokens(H, KVH, hd):
+    """From 512 tokens on the rows are staged in shared memory, 4, 2 or 1 tokens to a block: the same bits as the
+    kernel for few tokens (the same step in pieces of under 512 tokens), with a token count that is no multiple
+    of 4, padding tokens in between, three sequences at different places, and with and without rotation."""
+    from oracle_engine_b200.csrc import ops
+    T, B, pages_per_seq = 771, 3, 8
+    g = torch.Generator().manual_seed(hd)
+    tok_seq = torch.randint(0, B, (T,), generator=g, dtype=torch.int32)
+    tok_seq[torch.randperm(T, generator=g)[:40]] = -1                     # padding tokens
+    tok_seq[T - 1] = 2
+    tok_pos = torch.zeros(T, dtype=torch.int32)
+    nxt = [5, 64, 200]
+    for t in range(T):
+        b = int(tok_seq[t])
+        if b >= 0:
+            tok_pos[t] = nxt[b]
+            nxt[b] += 1
+    assert max(nxt) <= pages_per_seq * 64
+    tables = torch.randperm(B * pages_per_seq, generator=g).reshape(B, pages_per_seq).to(torch.int32)
+    ang = torch.arange(pages_per_seq * 64, dtype=torch.float64)[:, None] * (10000.0 ** (-torch.arange(hd // 2, dtype=torch.float64) / (hd // 2)))[None]
+    cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
+    tok_seq, tok_pos, tables = tok_seq.to(DEV), tok_pos.to(DEV), tables.to(DEV)
+    for dtype in (torch.bfloat16, torch.float32):
+        for rotate in (True, False):
+            orig = _rand(T, (H + 2 * KVH) * hd, dtype=dtype, seed=4)
+            outs = []
+            for pieces in ((T,), (300, 300, 171)):
+                qkv = orig.clone()
+                cache = torch.zeros(B * pages_per_seq, 2, KVH, 64, hd, dtype=dtype, device=DEV)
+                at = 0
+                for n in pieces:
+                    ops.rope_kv_write(qkv[at:at + n], cos if rotate else None, sin if rotate else None, cache, tables,
+                                      tok_seq[at:at + n], tok_pos[at:at + n], H, KVH, hd, True)
+                    at += n
+                outs.append((qkv, cache))
+            assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1]), (dtype, rotate)
+            if rotate:
+                assert not torch.equal(outs[0][0][:, :H * hd], orig[:, :H * hd])
+                pad = (tok_seq < 0)
+                assert torch.equal(outs[0][0][pad], orig[pad])
+            else:
+                assert torch.equal(outs[0][0], orig)
+
+
 def test_argmax_and_sampling():
     from oracle_engine_b200.csrc import ops
     V, R = 1003, 6

@@ -95,10 +95,10 @@ def generate(engine, n_prompts: int, tokens: int, lens: int, n_predict: int, tem
     if on_token:
         fn = _ON_TOKEN(on_token)
         callback = lambda i, tok: fn(int(i), int(tok), user or None)      # noqa: E731
+    got = _ints(out_tokens, n_prompts * n_predict)          # refused before anything runs if a pointer is null
+    counts = _ints(out_lens, n_prompts)
     outs = engine.generate(prompts, params, batch_size=batch_size or None, on_token=callback,
                            max_step_tokens=max_step_tokens or None)
-    got = _ints(out_tokens, n_prompts * n_predict)
-    counts = _ints(out_lens, n_prompts)
     for i, new in enumerate(outs):
         counts[i] = len(new)
         got[i * n_predict:i * n_predict + len(new)] = new

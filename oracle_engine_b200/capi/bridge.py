@@ -63,12 +63,12 @@ def step(engine, n_seqs: int, slots: int, tokens: int, q_lens: int, want: int, n
         seqs.append(SequenceStep(int(slot), toks[t:t + lens[i]].tolist(), places[w:w + wants[i]].tolist()))
         t += int(lens[i])
         w += int(wants[i])
+    if w and not out:
+        raise ValueError("logits_out is null but logits are wanted")
     logits = engine.step(seqs)
     if logits is None:
         return 0
     rows, vocab = logits.shape
-    if not out:
-        raise ValueError("logits_out is null but logits are wanted")
     host = logits.float().cpu().contiguous().numpy()
     ctypes.memmove(out, host.ctypes.data, host.nbytes)
     return int(rows)
